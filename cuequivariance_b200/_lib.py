@@ -1,0 +1,95 @@
+"""ctypes binding of ``libcueq_b200.so`` (declarations mirror ``include/cueq_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcueq_b200.so"
+
+F32, F64, BF16, F16 = 0, 1, 2, 3
+SHARED, BATCHED, INDEXED = 0, 1, 2
+MAX_BUFFERS, MAX_OPERANDS = 16, 8
+
+
+class U1dDesc(C.Structure):
+    _fields_ = [
+        ("operand_extent", C.c_int32),
+        ("num_inputs", C.c_int32),
+        ("num_outputs", C.c_int32),
+        ("buffer_dim", C.POINTER(C.c_int32)),
+        ("buffer_num_segments", C.POINTER(C.c_int32)),
+        ("num_operations", C.c_int32),
+        ("num_operands", C.POINTER(C.c_int32)),
+        ("operations", C.POINTER(C.c_int32)),
+        ("num_paths", C.POINTER(C.c_int32)),
+        ("path_indices", C.POINTER(C.c_int32)),
+        ("path_coefficients", C.POINTER(C.c_double)),
+        ("math_dtype", C.c_int32),
+    ]
+
+
+class Buffer(C.Structure):
+    _fields_ = [
+        ("ptr", C.c_void_p),
+        ("rows", C.c_int64),
+        ("mode", C.c_int32),
+        ("dtype", C.c_int32),
+        ("index", C.c_void_p),
+        ("index_is_64", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+class CueqError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Loads the CUDA library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise CueqError(
+            f"{LIB_PATH} is missing: build it with `python -m cuequivariance_b200.build` "
+            "(there is no CPU or PyTorch fallback for the CUDA executor)"
+        )
+    L = C.CDLL(str(LIB_PATH))
+    L.cueq_b200_abi_version.restype = C.c_int
+    L.cueq_b200_last_error.restype = C.c_char_p
+    L.cueq_b200_u1d_plan_create.argtypes = [C.POINTER(U1dDesc), C.POINTER(C.c_void_p)]
+    L.cueq_b200_plan_destroy.argtypes = [C.c_void_p]
+    L.cueq_b200_plan_destroy.restype = None
+    L.cueq_b200_plan_table_bytes.argtypes = [C.c_void_p]
+    L.cueq_b200_plan_table_bytes.restype = C.c_size_t
+    L.cueq_b200_plan_table_data.argtypes = [C.c_void_p]
+    L.cueq_b200_plan_table_data.restype = C.c_void_p
+    L.cueq_b200_u1d_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(Buffer), C.c_int32, C.c_void_p]
+    L.cueq_b200_segmented_transpose.argtypes = [
+        C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+    ]
+    if L.cueq_b200_abi_version() != 1:
+        raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise CueqError(lib().cueq_b200_last_error().decode())
+
+
+def int32_array(values):
+    values = list(values)
+    return (C.c_int32 * max(len(values), 1))(*values)
+
+
+def double_array(values):
+    values = list(values)
+    return (C.c_double * max(len(values), 1))(*values)

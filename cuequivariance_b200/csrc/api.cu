@@ -1,0 +1,22 @@
+// C ABI housekeeping: version, thread-local error text.
+#include "common.cuh"
+
+namespace cueq {
+
+char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+}  // namespace cueq
+
+extern "C" int cueq_b200_abi_version(void) { return CUEQ_B200_ABI_VERSION; }
+extern "C" const char* cueq_b200_last_error(void) { return cueq::error_buffer(); }

@@ -1,0 +1,10 @@
+from .tp_channel_wise import ChannelWiseTensorProduct
+from .tp_fully_connected import FullyConnectedTensorProduct
+from .symmetric_contraction import SymmetricContraction
+from .spherical_harmonics import SphericalHarmonics, spherical_harmonics
+from .equivariant import EquivariantTensorProduct
+
+__all__ = [
+    "ChannelWiseTensorProduct", "FullyConnectedTensorProduct", "SymmetricContraction",
+    "SphericalHarmonics", "spherical_harmonics", "EquivariantTensorProduct",
+]
