@@ -1,0 +1,236 @@
+"""GPU parity tests: the CUDA executor (called through the C-ABI library) against the
+reference-generated golden fixtures and against the CPU oracle on seeded inputs.
+
+Tolerances: float64 1e-12 relative+absolute; float32 1e-5 relative / 2e-6 absolute on
+outputs (x10 for first derivatives, x100 for the second-order check, following the
+reference tests' scaling, cuequivariance_torch/tests/primitives/segmented_polynomial_test.py:174-175).
+"""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import cuequivariance_b200 as cb
+from cuequivariance_b200 import descriptors as D
+from oracle import naive
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {"f64": (1e-12, 1e-12), "f32": (1e-5, 2e-6)}
+DT = {"f64": torch.float64, "f32": torch.float32}
+
+
+def _t(a, device=DEV):
+    return torch.from_numpy(np.array(a)).to(device)
+
+
+def _derivatives(fn, inputs, cot):
+    xs = [x.clone().requires_grad_(True) for x in inputs]
+    out = fn(*xs)
+    g1 = torch.autograd.grad((out * cot).sum(), xs, retain_graph=True, allow_unused=True)
+    gg = torch.autograd.grad(out.pow(2).sum(), xs, create_graph=True, allow_unused=True)
+    tot = sum(g.pow(2).sum() for g in gg if g is not None)
+    g2 = torch.autograd.grad(tot, xs, allow_unused=True)
+    return out.detach(), g1, g2
+
+
+def _close(a, b, rtol, atol, what=""):
+    a = a.detach().cpu().double().numpy() if torch.is_tensor(a) else np.asarray(a, dtype=np.float64)
+    b = b.detach().cpu().double().numpy() if torch.is_tensor(b) else np.asarray(b, dtype=np.float64)
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    err = np.abs(a - b) - (atol + rtol * np.abs(b))
+    assert np.all(err <= 0), f"{what}: max abs diff {np.abs(a - b).max():.3e}, worst excess {err.max():.3e}"
+
+
+def _check_golden(g, out, g1, g2, rtol, atol):
+    _close(out, g["out"], rtol, atol, "out")
+    for i, (a, b) in enumerate(zip(g1, g2)):
+        _close(a, g[f"grad{i}"], 10 * rtol, 10 * atol, f"grad{i}")
+        _close(b, g[f"gradgrad{i}"], 100 * rtol, 100 * atol, f"gradgrad{i}")
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+@pytest.mark.parametrize("name,s1", [("cw_l2", "8x0e+8x1o+8x2e"), ("cw_l3", "8x0e+8x1o+8x2e+8x3o")])
+def test_channelwise_module_golden(golden, name, s1, tag):
+    g = golden(f"{name}_module_{tag}.npz")
+    m = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", ["0e", "1o", "2e", "3o"], layout=cb.mul_ir,
+                                    shared_weights=False, internal_weights=False)
+    N = g["x1"].shape[0]
+    for idx_dtype in (torch.int64, torch.int32):
+        snd, rcv = _t(g["senders"]).to(idx_dtype), _t(g["receivers"]).to(idx_dtype)
+        out, g1, g2 = _derivatives(
+            lambda w, a, b: m(a, b, w, indices_1=snd, indices_out=rcv, size_out=N),
+            [_t(g["w"]), _t(g["x1"]), _t(g["x2"])], _t(g["cot"]))
+        _check_golden(g, out, g1, g2, *TOL[tag])
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+def test_uniform1d_index_modes_golden(golden, tag):
+    e = D.channelwise_tensor_product("16x0e+16x1o", "0e+1o+2e", "0e+1o")
+    f = cb.SegmentedPolynomial(e.polynomial, method="uniform_1d")
+    g = golden(f"u1d_indexed_{tag}.npz")
+    ia, io = _t(g["ia"]), _t(g["io"])
+    out, g1, g2 = _derivatives(
+        lambda a, b, c: f([a, b, c], {0: ia}, {0: torch.empty(3, 1, device=DEV)}, {0: io})[0],
+        [_t(g["a"]), _t(g["b"]), _t(g["c"])], _t(g["cot"]))
+    _check_golden(g, out, g1, g2, *TOL[tag])
+    g = golden(f"u1d_sum_{tag}.npz")
+    a = _t(g["a"])
+    out, g1, g2 = _derivatives(
+        lambda b, c: f([a, b, c], {}, {0: torch.empty(1, 1, device=DEV)}, {})[0], [_t(g["b"]), _t(g["c"])], _t(g["cot"]))
+    _check_golden(g, out, g1, g2, *TOL[tag])
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+def test_symmetric_contraction_module_golden(golden, tag):
+    g = golden(f"symmetric_contraction_module_{tag}.npz")
+    m = cb.SymmetricContraction("4x0e+4x1o+4x2e+4x3o", "4x0e+4x1o", 3, 10, layout=cb.mul_ir, dtype=DT[tag], device=DEV)
+    sp = _t(g["species"])
+
+    def fn(w, x):
+        out = m.f([w.flatten(1), m.transpose_in(x)], input_indices={0: sp})
+        return m.transpose_out(out[0])
+
+    out, g1, g2 = _derivatives(fn, [_t(g["weight"]), _t(g["x"])], _t(g["cot"]))
+    _check_golden(g, out, g1, g2, *TOL[tag])
+    # and through the module's own forward with its parameter
+    with torch.no_grad():
+        m.weight.copy_(_t(g["weight"]))
+    _close(m(_t(g["x"]), sp.to(torch.int32)), g["out"], *TOL[tag])
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+def test_fully_connected_module_golden(golden, tag):
+    g = golden(f"fully_connected_module_{tag}.npz")
+    s = "4x0e+4x1o+4x2e"
+    m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.mul_ir, internal_weights=False, shared_weights=True)
+    out, g1, g2 = _derivatives(lambda w, a, b: m(a, b, w), [_t(g["weight"]), _t(g["x1"]), _t(g["x2"])], _t(g["cot"]))
+    _check_golden(g, out, g1, g2, *TOL[tag])
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+def test_spherical_harmonics_golden(golden, tag):
+    g = golden(f"spherical_harmonics_{tag}.npz")
+    sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)
+    out, g1, g2 = _derivatives(lambda v: sh(v), [_t(g["vec"])], _t(g["cot"]))
+    _check_golden(g, out, g1, g2, *TOL[tag])
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+def test_transpose_golden(golden, tag):
+    g = golden(f"transpose_{tag}.npz")
+    t = cb.TransposeIrrepsLayout("3x0e+5x1o+2x2e", source=cb.mul_ir, target=cb.ir_mul)
+    x = _t(g["x"]).requires_grad_(True)
+    y = t(x)
+    assert np.array_equal(y.detach().cpu().numpy(), g["y"])
+    back = cb.TransposeIrrepsLayout("3x0e+5x1o+2x2e", source=cb.ir_mul, target=cb.mul_ir)
+    assert torch.equal(back(y), x)
+    (gx,) = torch.autograd.grad((y * y).sum(), x)
+    assert torch.equal(gx, 2 * x.detach())
+
+
+# ---- every shared / batched / indexed combination against the oracle (the matrix of the
+# ---- reference's executor tests, segmented_polynomial_test.py:286-301) ------------------
+MODES = ["shared", "batched", "indexed"]
+
+
+def _make_operand(mode, size, batch, rows, gen, dtype):
+    if mode == "shared":
+        return torch.randn(1, size, generator=gen, dtype=torch.float64).to(dtype), None
+    if mode == "batched":
+        return torch.randn(batch, size, generator=gen, dtype=torch.float64).to(dtype), None
+    idx = torch.sort(torch.randint(0, rows, (batch,), generator=gen)).values
+    return torch.randn(rows, size, generator=gen, dtype=torch.float64).to(dtype), idx
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+@pytest.mark.parametrize("out_mode", MODES)
+@pytest.mark.parametrize("in_modes", list(itertools.product(MODES, repeat=3)))
+def test_index_mode_matrix_against_oracle(in_modes, out_mode, tag):
+    if all(m == "shared" for m in in_modes) and out_mode == "batched":
+        pytest.skip("no batch axis anywhere")
+    dtype = DT[tag]
+    e = D.channelwise_tensor_product("8x0e+8x1o", "0e+1o+2e", "0e+1o")
+    poly = e.polynomial.flatten_coefficient_modes().squeeze_modes()
+    f = cb.SegmentedPolynomial(poly, method="uniform_1d")
+    gen = torch.Generator().manual_seed(hash((in_modes, out_mode)) % 2**31)
+    batch, rows = 7, 3
+    xs, idx = [], {}
+    for k, mode in enumerate(in_modes):
+        x, i = _make_operand(mode, poly.inputs[k].size, batch, rows, gen, dtype)
+        xs.append(x)
+        if i is not None:
+            idx[k] = i
+    has_batch = any(m != "shared" for m in in_modes)
+    oshape, oidx = {}, {}
+    if out_mode == "shared":
+        oshape = {0: 1}
+    elif out_mode == "indexed":
+        if not has_batch:
+            pytest.skip("an indexed output needs a batch")
+        oshape = {0: rows}
+        oidx = {0: torch.randint(0, rows, (batch,), generator=gen)}
+    cot_rows = {"shared": 1, "batched": batch if has_batch else 1, "indexed": rows}[out_mode]
+    cot = torch.randn(cot_rows, poly.outputs[0].size, generator=gen, dtype=torch.float64).to(dtype)
+
+    ref = _derivatives(lambda *a: naive.segmented_polynomial(poly, list(a), idx, oshape, oidx)[0], xs, cot)
+    dev_idx = {k: v.to(DEV) for k, v in idx.items()}
+    dev_oidx = {k: v.to(DEV).to(torch.int32) for k, v in oidx.items()}
+    dev_shape = {k: torch.empty(v, 1, device=DEV) for k, v in oshape.items()}
+    got = _derivatives(lambda *a: f(list(a), dev_idx, dev_shape, dev_oidx)[0], [x.to(DEV) for x in xs], cot.to(DEV))
+    rtol, atol = TOL[tag]
+    _close(got[0], ref[0], rtol, atol, "out")
+    for a, b in zip(got[1], ref[1]):
+        _close(a, b, 10 * rtol, 10 * atol, "grad")
+    for a, b in zip(got[2], ref[2]):
+        _close(a, b, 100 * rtol, 100 * atol, "gradgrad")
+
+
+def test_empty_batch():
+    e = D.channelwise_tensor_product("8x0e+8x1o", "0e+1o", "0e+1o")
+    f = cb.SegmentedPolynomial(e.polynomial, method="uniform_1d")
+    p = e.polynomial
+    xs = [torch.randn(0, o.size, device=DEV) for o in p.inputs]
+    (out,) = f(xs)
+    assert out.shape == (0, p.outputs[0].size)
+    # empty edge list scattered into a non-empty node array gives zeros
+    x1 = torch.randn(5, p.inputs[1].size, device=DEV)
+    empty = torch.zeros(0, dtype=torch.int64, device=DEV)
+    (out,) = f([xs[0], x1, xs[2]], {1: empty}, {0: torch.empty(5, 1, device=DEV)}, {0: empty})
+    assert out.shape == (5, p.outputs[0].size) and torch.count_nonzero(out) == 0
+
+
+def test_mixed_precision_inputs_float32_math():
+    """bf16/fp16 inputs with float32 math: compared with the oracle run with math_dtype."""
+    torch.manual_seed(3)
+    e = D.channelwise_tensor_product("8x0e+8x1o", "0e+1o", "0e+1o")
+    p = e.polynomial.flatten_coefficient_modes().squeeze_modes()
+    for dt, tol in ((torch.bfloat16, 2e-2), (torch.float16, 3e-3)):
+        xs = [torch.randn(9, o.size).to(dt) for o in p.inputs]
+        f = cb.SegmentedPolynomial(p, method="uniform_1d", math_dtype=torch.float32)
+        (got,) = f([x.to(DEV) for x in xs])
+        assert got.dtype == dt
+        (ref,) = naive.segmented_polynomial(p, [x.float() for x in xs])
+        assert torch.allclose(got.float().cpu(), ref, rtol=tol, atol=tol)
+
+
+def test_gather_scatter_indexing_is_exact():
+    """One-hot inputs: every output entry is a single product, so the result must equal
+    the oracle bit for bit, which pins the gather/scatter index arithmetic."""
+    e = D.channelwise_tensor_product("4x0e", "0e", "0e")
+    p = e.polynomial.flatten_coefficient_modes().squeeze_modes()
+    f = cb.SegmentedPolynomial(p, method="uniform_1d")
+    E, N = 257, 31
+    gen = torch.Generator().manual_seed(5)
+    snd, rcv = torch.randint(0, N, (E,), generator=gen), torch.arange(E) % N
+    w = torch.ones(E, p.inputs[0].size)
+    x1 = torch.arange(N * p.inputs[1].size, dtype=torch.float32).reshape(N, -1)
+    x2 = torch.ones(E, 1)
+    # make each receiver get exactly one edge contribution per slot: keep first edge per receiver
+    keep = torch.zeros(E, dtype=torch.bool)
+    keep[:N] = True
+    x2 = x2 * keep[:, None]
+    (ref,) = naive.segmented_polynomial(p, [w, x1, x2], {1: snd}, {0: N}, {0: rcv})
+    (got,) = f([w.to(DEV), x1.to(DEV), x2.to(DEV)], {1: snd.to(DEV).int()}, {0: torch.empty(N, 1, device=DEV)}, {0: rcv.to(DEV).int()})
+    assert torch.equal(got.cpu(), ref)
