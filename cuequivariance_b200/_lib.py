@@ -43,6 +43,21 @@ class Buffer(C.Structure):
     ]
 
 
+class CwArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("x1", C.c_void_p), ("x2", C.c_void_p), ("out", C.c_void_p),
+        ("gout", C.c_void_p), ("gw", C.c_void_p), ("gx1", C.c_void_p), ("gx2", C.c_void_p),
+        ("senders", C.c_void_p), ("order", C.c_void_p), ("rowptr", C.c_void_p),
+        ("tab_start", C.c_void_p), ("tab_j", C.c_void_p), ("tab_c", C.c_void_p),
+        ("bwd_coef", C.POINTER(C.c_float)),
+        ("w_stride", C.c_int64), ("x1_stride", C.c_int64), ("x2_stride", C.c_int64), ("out_stride", C.c_int64),
+        ("num_receivers", C.c_int64),
+        ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
+        ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
+        ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -74,6 +89,12 @@ def lib() -> C.CDLL:
     L.cueq_b200_segmented_transpose.argtypes = [
         C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
     ]
+    L.cueq_b200_cw_num_groups.restype = C.c_int
+    L.cueq_b200_cw_group_signature.argtypes = [C.c_int]
+    L.cueq_b200_cw_group_signature.restype = C.c_char_p
+    L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
+    L.cueq_b200_cw_forward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
+    L.cueq_b200_cw_backward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     _lib = L

@@ -1,7 +1,375 @@
-"""Matcher that routes channelwise tensor products to their specialised kernels."""
+"""Specialised execution of channelwise ("uvu") tensor products.
+
+The polynomial ``uv,iu,jv,kuv+ijk`` (reference descriptor:
+cuequivariance/group_theory/descriptors/irreps_tp.py:232-321) is split into *groups*: all
+paths that read the same irrep of the first operand.  Each group runs as one launch of a
+kernel whose Clebsch-Gordan arithmetic was written out at build time
+(``csrc/gen_cw_groups.py``); gather of the first operand, the multiply-add and the
+reduction over the edges of a receiver are fused, and layouts (mul_ir / ir_mul) are
+handled in the addressing.  This module holds the pattern functions shared by the code
+generator and the run-time matcher, and the matcher itself.
+"""
 from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .cg import so3_clebsch_gordan
+
+
+# ---- patterns shared with the code generator ---------------------------------------------
+def pair_pattern(l1: int, l2: int, l3: int, major: str) -> List[Tuple[int, int, List[Tuple[int, float]]]]:
+    """Non-zero ``(i, k)`` pairs of the coupling tensor of (l1, l2, l3) with their ``(j, C)``
+    terms; ``major='k'`` orders pairs by k then i (forward), ``'i'`` by i then k (backward)."""
+    c = so3_clebsch_gordan(l1, l2, l3)[0]
+    d1, d2, d3 = c.shape
+    order = [(i, k) for k in range(d3) for i in range(d1)] if major == "k" else [(i, k) for i in range(d1) for k in range(d3)]
+    out = []
+    for i, k in order:
+        js = [j for j in range(d2) if c[i, j, k] != 0.0]
+        if js:
+            out.append((i, k, [(j, float(c[i, j, k])) for j in js]))
+    return out
+
+
+def group_signature(l1: int, paths: Sequence[Tuple[int, int]]) -> str:
+    return f"{l1}:" + ",".join(f"{a}.{b}" for a, b in paths)
+
+
+# ---- run-time side ----------------------------------------------------------------------------
+class _CsrCache:
+    """Receiver index -> (order or None, rowptr).  Keyed on the tensor's storage address and
+    version counter, so in-place updates of the index are noticed; the cache holds a
+    reference to the tensor, which keeps that address from being recycled."""
+
+    def __init__(self, capacity: int = 8):
+        self.capacity = capacity
+        self.entries: list = []
+
+    def get(self, index, num_rows: int):
+        import torch
+
+        key = (index.data_ptr(), index.numel(), index.dtype, index._version, num_rows, index.device)
+        for k, ref, val in self.entries:
+            if k == key and ref is index:
+                return val
+        idx = index if index.dtype == torch.int32 else index.to(torch.int32)
+        if idx.numel() > 1 and not bool((idx[1:] >= idx[:-1]).all()):
+            sorted_idx, order = torch.sort(idx, stable=True)
+            order = order.to(torch.int32)
+        else:
+            sorted_idx, order = idx, None
+        bounds = torch.arange(num_rows + 1, device=index.device, dtype=torch.int32)
+        rowptr = torch.searchsorted(sorted_idx.contiguous(), bounds, right=False).to(torch.int32)
+        val = (order, rowptr)
+        self.entries.append((key, index, val))
+        if len(self.entries) > self.capacity:
+            self.entries.pop(0)
+        return val
+
+    def int32(self, index):
+        import torch
+
+        if index.dtype == torch.int32:
+            return index.contiguous()
+        key = ("i32", index.data_ptr(), index.numel(), index._version, index.device)
+        for k, ref, val in self.entries:
+            if k == key and ref is index:
+                return val
+        val = index.to(torch.int32).contiguous()
+        self.entries.append((key, index, val))
+        if len(self.entries) > self.capacity:
+            self.entries.pop(0)
+        return val
+
+
+_CSR = _CsrCache()
+_IDENTITY_ROWPTR: dict = {}
+
+
+def _library_groups() -> dict:
+    from . import _lib
+
+    L = _lib.lib()
+    return {L.cueq_b200_cw_group_signature(g).decode(): g for g in range(L.cueq_b200_cw_num_groups())}
+
+
+class ChannelwisePlan:
+    """What the kernels need for one channelwise polynomial: per group the library kernel
+    id, segment offsets and the M-tables (forward: k-major pairs, backward: i-major)."""
+
+    def __init__(self, groups, extent, row_sizes, x1_blocks, out_blocks):
+        self.groups = groups
+        self.extent = extent
+        self.row_sizes = row_sizes          # (w, x1, x2, out) elements per row
+        self.x1_blocks = x1_blocks          # ((mul, dim), ...) of x1
+        self.out_blocks = out_blocks
+        self._dev: dict = {}
+
+    def tables_on(self, device):
+        import torch
+
+        t = self._dev.get(device)
+        if t is None:
+            t = []
+            for g in self.groups:
+                t.append({
+                    k: (torch.tensor(g[k][0], dtype=torch.int32, device=device),
+                        torch.tensor(g[k][1], dtype=torch.int32, device=device),
+                        torch.tensor(g[k][2], dtype=torch.float32, device=device))
+                    for k in ("fwd_tab", "bwd_tab")
+                })
+            self._dev[device] = t
+        return t
+
+
+def match_channelwise(polynomial) -> Optional[ChannelwisePlan]:
+    """Recognises ``uv,iu,jv,kuv+ijk`` built from SO(3)/O(3) coupling tensors whose groups all
+    have a kernel in the library; returns None otherwise."""
+    if len(polynomial.operations) != 1 or polynomial.num_inputs != 3 or polynomial.num_outputs != 1:
+        return None
+    ope, d = polynomial.operations[0]
+    if d.subscripts != "uv,iu,jv,kuv+ijk" or tuple(ope.buffers) != (0, 1, 2, 3):
+        return None
+    w_op, x1_op, x2_op, out_op = d.operands
+    if not x1_op.segments or not x2_op.segments:
+        return None
+    extent = x1_op.segments[0][1]
+    if extent % 4 or any(s[1] != extent for s in x1_op.segments) or any(s[1] != 1 for s in x2_op.segments):
+        return None
+    if any(s[0] % 2 == 0 for s in x1_op.segments + x2_op.segments):
+        return None
+    l2s = [(s[0] - 1) // 2 for s in x2_op.segments]
+    if l2s != list(range(len(l2s))):
+        return None  # x2 must be one copy of l = 0, 1, 2, ... in order
+    x2_off = x2_op.offsets()
+    w_off, x1_off, out_off = w_op.offsets(), x1_op.offsets(), out_op.offsets()
+    by_i1: dict = {}
+    seen_w, seen_o = set(), set()
+    for path in d.paths:
+        sw, s1, s2, so = path.indices
+        c = path.coefficients
+        d1, d2, d3 = c.shape
+        if d3 % 2 == 0 or w_op.segments[sw] != (extent, 1) or out_op.segments[so] != (d3, extent, 1):
+            return None
+        if sw in seen_w or so in seen_o:
+            return None
+        seen_w.add(sw)
+        seen_o.add(so)
+        l1, l2, l3 = (d1 - 1) // 2, (d2 - 1) // 2, (d3 - 1) // 2
+        ref = so3_clebsch_gordan(l1, l2, l3)
+        if ref.shape[0] != 1:
+            return None
+        ref = ref[0]
+        nz = ref != 0
+        if not np.array_equal(nz, c != 0):
+            return None
+        alpha = float((c[nz] / ref[nz]).mean())
+        if not np.allclose(c, alpha * ref, rtol=1e-12, atol=1e-14):
+            return None
+        by_i1.setdefault(s1, []).append((l1, l2, l3, sw, so, c))
+    lib = _library_groups()
+    groups = []
+    for s1, plist in sorted(by_i1.items()):
+        l1 = plist[0][0]
+        sig = group_signature(l1, [(l2, l3) for _, l2, l3, _, _, _ in plist])
+        if sig not in lib:
+            return None
+        g = {"id": lib[sig], "x1_off": x1_off[s1], "w_off": [w_off[p[3]] for p in plist],
+             "out_off": [out_off[p[4]] for p in plist], "npath": len(plist), "out_segs": [p[4] for p in plist]}
+        for name, major in (("fwd_tab", "k"), ("bwd_tab", "i")):
+            start, tj, tc = [0], [], []
+            for l1_, l2, l3, _, _, c in plist:
+                for i, k, terms in pair_pattern(l1_, l2, l3, major):
+                    for j, _ref in terms:
+                        tj.append(x2_off[l2] + j)
+                        tc.append(float(c[i, j, k]))
+                    start.append(len(tj))
+            g[name] = (start, tj, tc)
+        g["nterm"] = len(g["bwd_tab"][1])
+        groups.append(g)
+    # every output segment must be produced by exactly one path (else rows would be incomplete)
+    if len(seen_o) != out_op.num_segments:
+        return None
+    x1_blocks = tuple((s[1], s[0]) for s in x1_op.segments)
+    out_blocks = tuple((s[1] * s[2], s[0]) for s in out_op.segments)
+    return ChannelwisePlan(groups, extent, (w_op.size, x1_op.size, x2_op.size, out_op.size), x1_blocks, out_blocks)
+
+
+def _is_mul_ir(layout, blocks) -> Optional[bool]:
+    """None if ``layout`` is something the kernels do not understand."""
+    if layout is None:
+        return False
+    return True if tuple(layout) == tuple(blocks) else None
+
+
+class _ChannelwiseBase:
+    def __init__(self, plan: ChannelwisePlan):
+        self.plan = plan
+
+    def _common(self, program, cfg, xs, n_in):
+        import torch
+
+        from . import _lib
+
+        plan = self.plan
+        if program.math_dtype != torch.float32 or any(x.dtype != torch.float32 for x in xs):
+            return None
+        w_s, x1_s, x2_s = cfg.inputs[0], cfg.inputs[1], cfg.inputs[2]
+        if w_s.mode != _lib.BATCHED or x2_s.mode != _lib.BATCHED or x1_s.mode == _lib.SHARED:
+            return None
+        if cfg.layout(0) is not None or cfg.layout(2) is not None:
+            return None
+        x1_mul_ir = _is_mul_ir(cfg.layout(1), plan.x1_blocks)
+        if x1_mul_ir is None or any(x.data_ptr() % 16 for x in xs):
+            return None
+        senders = _CSR.int32(x1_s.index) if x1_s.mode == _lib.INDEXED else None
+        return dict(x1_mul_ir=x1_mul_ir, senders=senders)
+
+    def _csr(self, spec, batch, device):
+        import torch
+
+        from . import _lib
+
+        if spec.mode == _lib.INDEXED:
+            order, rowptr = _CSR.get(spec.index, spec.rows)
+            return order, rowptr, spec.rows
+        if spec.mode == _lib.BATCHED:
+            key = (batch, device)
+            rp = _IDENTITY_ROWPTR.get(key)
+            if rp is None:
+                rp = torch.arange(batch + 1, dtype=torch.int32, device=device)
+                _IDENTITY_ROWPTR.clear()
+                _IDENTITY_ROWPTR[key] = rp
+            return None, rp, batch
+        return None
+
+    def _args(self, g, tabs, which, common, order, rowptr, nrecv, out_mul_ir, tensors):
+        import ctypes as C
+
+        from . import _lib
+
+        plan = self.plan
+        a = _lib.CwArgs()
+        for k, t in tensors.items():
+            setattr(a, k, t.data_ptr() if t is not None and t.numel() else None)
+        a.senders = common["senders"].data_ptr() if common["senders"] is not None else None
+        a.order = order.data_ptr() if order is not None else None
+        a.rowptr = rowptr.data_ptr()
+        ts, tj, tc = tabs[which]
+        a.tab_start, a.tab_j, a.tab_c = ts.data_ptr(), tj.data_ptr(), tc.data_ptr()
+        a.w_stride, a.x1_stride, a.x2_stride, a.out_stride = plan.row_sizes
+        a.num_receivers = nrecv
+        a.extent = plan.extent
+        a.x1_offset = g["x1_off"]
+        a.num_paths = g["npath"]
+        a.num_terms = g["nterm"]
+        for q in range(g["npath"]):
+            a.w_offset[q] = g["w_off"][q]
+            a.out_offset[q] = g["out_off"][q]
+        a.x1_mul_ir = 1 if common["x1_mul_ir"] else 0
+        a.out_mul_ir = 1 if out_mul_ir else 0
+        keep = None
+        if which == "bwd_tab":
+            keep = (C.c_float * g["nterm"])(*g["bwd_tab"][2])
+            a.bwd_coef = C.cast(keep, C.POINTER(C.c_float))
+        return a, keep
+
+
+class ChannelwiseForward(_ChannelwiseBase):
+    """``try_run`` returns the outputs, or None when the call is outside what the kernels
+    cover (the generic executor then takes it)."""
+
+    def try_run(self, program, cfg, xs):
+        import ctypes as C
+
+        import torch
+
+        from . import _lib, profiling
+
+        common = self._common(program, cfg, xs, 3)
+        if common is None:
+            return None
+        plan = self.plan
+        out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
+        csr = self._csr(cfg.outputs[0], cfg.batch, xs[0].device)
+        if out_mul_ir is None or csr is None:
+            return None
+        order, rowptr, nrecv = csr
+        w, x1, x2 = xs
+        out = torch.empty((nrecv, plan.row_sizes[3]), dtype=torch.float32, device=w.device)
+        tabs = plan.tables_on(w.device)
+        stream = C.c_void_p(torch.cuda.current_stream(w.device).cuda_stream)
+        with torch.cuda.device(w.device):
+            for g, t in zip(plan.groups, tabs):
+                a, _ = self._args(g, t, "fwd_tab", common, order, rowptr, nrecv, out_mul_ir, dict(w=w, x1=x1, x2=x2, out=out))
+                with profiling.kernel(f"cw_fwd[{g['id']}]", stream):
+                    _lib.check(_lib.lib().cueq_b200_cw_forward(g["id"], C.byref(a), stream))
+        return [out]
+
+    def derive(self, requires_gradient, has_cotangent):
+        if not has_cotangent[0]:
+            return None
+        return ChannelwiseBackward(self.plan, tuple(requires_gradient))
+
+
+class ChannelwiseBackward(_ChannelwiseBase):
+    """Inputs (w, x1, x2, gout) -> gradients of the flagged inputs."""
+
+    def __init__(self, plan, needs):
+        super().__init__(plan)
+        self.needs = needs
+
+    def try_run(self, program, cfg, xs):
+        import ctypes as C
+
+        import torch
+
+        from . import _lib, profiling
+
+        common = self._common(program, cfg, xs, 4)
+        if common is None:
+            return None
+        plan = self.plan
+        out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
+        csr = self._csr(cfg.inputs[3], cfg.batch, xs[0].device)
+        if out_mul_ir is None or csr is None:
+            return None
+        # gradient layouts must mirror the input layouts
+        k = 4
+        for i, need in enumerate(self.needs):
+            if need:
+                if cfg.layout(k) != cfg.layout(i) or cfg.outputs[k - 4].mode != cfg.inputs[i].mode:
+                    return None
+                k += 1
+        order, rowptr, nrecv = csr
+        w, x1, x2, gout = xs
+        dev = w.device
+        gw = torch.empty_like(w) if self.needs[0] else None
+        gx1 = torch.zeros_like(x1) if self.needs[1] else None
+        gx2 = torch.zeros_like(x2) if self.needs[2] else None
+        tabs = plan.tables_on(dev)
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            for g, t in zip(plan.groups, tabs):
+                a, keep = self._args(g, t, "bwd_tab", common, order, rowptr, nrecv, out_mul_ir,
+                                     dict(w=w, x1=x1, x2=x2, gout=gout, gw=gw, gx1=gx1, gx2=gx2))
+                with profiling.kernel(f"cw_bwd[{g['id']}]", stream):
+                    _lib.check(_lib.lib().cueq_b200_cw_backward(g["id"], C.byref(a), stream))
+                del keep
+        return [t for t, need in zip((gw, gx1, gx2), self.needs) if need]
+
+    def derive(self, requires_gradient, has_cotangent):
+        return None  # second derivatives run on the generic executor
 
 
 def attach_specialisation(program) -> None:
-    """No specialised kernel registered yet: the generic executor handles every call."""
-    return None
+    """Routes a matching program to the channelwise kernels (float32 math only)."""
+    import torch
+
+    if program.math_dtype != torch.float32:
+        return
+    plan = match_channelwise(program.original)
+    if plan is not None:
+        program._special = ChannelwiseForward(plan)

@@ -1,0 +1,203 @@
+"""Generates ``generated/cw_groups.cuh``: straight-line arithmetic for channelwise tensor
+products, one struct per *group* (all paths that read the same irrep of the first operand).
+
+Why generated code: the Clebsch-Gordan tensors are sparse with a pattern known at build
+time.  Written out as straight-line FMAs every accumulator and every operand stays in a
+register (registers cannot be indexed dynamically), and no multiply is spent on a zero.
+
+For a path (l1, l2, l3) with coupling tensor C[i, j, k] the kernels use, per edge,
+    M[i, k] = sum_j C[i, j, k] * x2[j]                  (channel independent)
+    forward : out[k, u] += w[u] * sum_i M[i, k] * x1[i, u]
+    backward: S[i, u]   = sum_k M[i, k] * g[k, u]
+              gx1[i, u] += w[u] * S[i, u];   gw[u] = sum_i S[i, u] * x1[i, u]
+              gx2[j]    += sum_{i,k} C[i, j, k] * sum_u w[u] x1[i, u] g[k, u]
+Only the non-zero (i, k) pairs appear.  The numeric value of every M entry is computed at
+run time from a small term table (the kernel needs only the *pattern* at compile time), so
+normalisation factors of the descriptor can change without regenerating anything.
+
+    python cuequivariance_b200/csrc/gen_cw_groups.py        # rewrites generated/cw_groups.cuh
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import numpy as np  # noqa: E402
+
+from cuequivariance_b200.channelwise import group_signature as _signature, pair_pattern  # noqa: E402
+
+# Groups to build: (l1, [(l2, l3), ...]).  The list below is the family used by MACE-style
+# models: second operand 0e+1o+..+L2 (spherical harmonics), outputs filtered to natural
+# parity irreps up to L3.
+FAMILIES = [(3, 3)]  # (L2, L3) : l1 ranges over 0..3
+
+
+def group_paths(l1: int, L2: int, L3: int) -> list[tuple[int, int]]:
+    """(l2, l3) of every path of the group, in the descriptor's path order (l2 ascending,
+    then l3 ascending) with l1+l2+l3 even (natural parity in, natural parity out)."""
+    out = []
+    for l2 in range(L2 + 1):
+        for l3 in range(abs(l1 - l2), min(l1 + l2, L3) + 1):
+            if (l1 + l2 + l3) % 2 == 0:
+                out.append((l2, l3))
+    return out
+
+
+def group_name(l1: int, paths) -> str:
+    return f"CwGroup_l{l1}_" + "_".join(f"{a}{b}" for a, b in paths)
+
+
+def group_signature(l1: int, paths) -> str:
+    return _signature(l1, paths)
+
+
+def emit_group(l1: int, paths) -> str:
+    d1 = 2 * l1 + 1
+    name = group_name(l1, paths)
+    pats = [pair_pattern(l1, l2, l3, "k") for l2, l3 in paths]
+    pats_i = [pair_pattern(l1, l2, l3, "i") for l2, l3 in paths]
+    d3s = [2 * l3 + 1 for _, l3 in paths]
+    d2s = [2 * l2 + 1 for l2, _ in paths]
+    npair = [len(p) for p in pats]
+    pair_off = np.concatenate([[0], np.cumsum(npair)]).tolist()
+    out_off = np.concatenate([[0], np.cumsum(d3s)]).tolist()
+    ptot = pair_off[-1]
+    ptot_pad = (ptot + 3) // 4 * 4
+    L = []
+    A = L.append
+    A(f"struct {name} {{")
+    A(f"  static constexpr int L1 = {l1};")
+    A(f"  static constexpr int D1 = {d1};")
+    A(f"  static constexpr int NPATH = {len(paths)};")
+    A(f"  static constexpr int NPAIR = {ptot};")
+    A(f"  static constexpr int NPAIR_PAD = {ptot_pad};")
+    A(f"  static constexpr int SUMD3 = {out_off[-1]};")
+    A(f"  static constexpr int MAXD3 = {max(d3s)};")
+    A(f"  static constexpr int NX2 = {max(l2 for l2, _ in paths) ** 2 + 2 * max(l2 for l2, _ in paths) + 1};")
+    A("  static constexpr const char* signature() { return \"%s\"; }" % group_signature(l1, paths))
+    A("  __host__ __device__ static constexpr int d3(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, d3s)))
+    A("  __host__ __device__ static constexpr int out_offset(int p) { constexpr int t[NPATH + 1] = {%s}; return t[p]; }" % ", ".join(map(str, out_off)))
+    A("  __host__ __device__ static constexpr int pair_offset(int p) { constexpr int t[NPATH + 1] = {%s}; return t[p]; }" % ", ".join(map(str, pair_off)))
+
+    # ---- forward ------------------------------------------------------------------------
+    A("  // acc[out_offset(p) + k][c] += W[p][c] * sum_i M[q(i,k)] * X[i][c]")
+    A("  template <int P>")
+    A("  __device__ __forceinline__ static void fwd_path(const float (&X)[D1][4], const float (&W)[4], const float* __restrict__ M,")
+    A("                                                  float (&acc)[SUMD3][4]) {")
+    for p, (pat, d3) in enumerate(zip(pats, d3s)):
+        A(f"    if constexpr (P == {p}) {{")
+        # load the M entries of this path as float4 where aligned
+        q0 = pair_off[p]
+        A(f"      float m[{len(pat)}];")
+        A(f"      cw_load_m<{q0}, {len(pat)}>(M, m);")
+        by_k: dict[int, list] = {}
+        for q, (i, k, _) in enumerate(pat):
+            by_k.setdefault(k, []).append((q, i))
+        for k in range(d3):
+            terms = by_k.get(k, [])
+            if not terms:
+                continue
+            A("      {")
+            A("        float t[4];")
+            q, i = terms[0]
+            A(f"        CW_MUL4(t, m[{q}], X[{i}]);")
+            for q, i in terms[1:]:
+                A(f"        CW_FMA4(t, m[{q}], X[{i}]);")
+            A(f"        CW_FMAV4(acc[{out_off[p] + k}], W, t);")
+            A("      }")
+        A("    }")
+    A("  }")
+
+    # ---- backward -----------------------------------------------------------------------
+    A("  // per path, pairs ordered by i: S[i] = sum_k M[q] G[k];  gX[i] += W*S[i];  gw = sum_i S[i] X[i];")
+    A("  //           r[j] += c * dot4(W*X[i], G[k]) over the non-zero (i, j, k)")
+    A("  template <int P, class Coef>")
+    A("  __device__ __forceinline__ static void bwd_path(const float (&X)[D1][4], const float (&W)[4], const float* __restrict__ M,")
+    A("                                                  const float (&G)[MAXD3][4], const Coef& coef,")
+    A("                                                  float (&gX)[D1][4], float (&gw)[4], float (&r)[NX2]) {")
+    term_cursor = 0
+    for p, (pat, d3, d2) in enumerate(zip(pats_i, d3s, d2s)):
+        l2 = paths[p][0]
+        j_base = l2 * l2  # offset of irrep l2 inside x2 = 0e+1o+2e+...
+        A(f"    if constexpr (P == {p}) {{")
+        q0 = pair_off[p]
+        A("      gw[0] = gw[1] = gw[2] = gw[3] = 0.f;")
+        by_i: dict[int, list] = {}
+        for q, (i, k, terms) in enumerate(pat):
+            by_i.setdefault(i, []).append((q, k, terms))
+        t = term_cursor
+        for i in range(d1):
+            lst = by_i.get(i, [])
+            if not lst:
+                continue
+            qa = lst[0][0]
+            A("      {")
+            A(f"        float m[{len(lst)}];")
+            A(f"        cw_load_m<{q0 + qa}, {len(lst)}>(M, m);")
+            A("        float s[4], xw[4];")
+            A(f"        CW_MULV4(xw, W, X[{i}]);")
+            for n, (q, k, terms) in enumerate(lst):
+                if n == 0:
+                    A(f"        CW_MUL4(s, m[{q - qa}], G[{k}]);")
+                else:
+                    A(f"        CW_FMA4(s, m[{q - qa}], G[{k}]);")
+                A(f"        {{ const float v = CW_DOT4(xw, G[{k}]);")
+                for j, _c in terms:
+                    A(f"          r[{j_base + j}] = fmaf(coef.c[{t}], v, r[{j_base + j}]);")
+                    t += 1
+                A("        }")
+            A(f"        CW_FMAV4(gX[{i}], W, s);")
+            A(f"        CW_FMAV4(gw, s, X[{i}]);")
+            A("      }")
+        term_cursor = t
+        A("    }")
+    A("  }")
+    A(f"  static constexpr int NTERM = {term_cursor};")
+    A("};")
+    return "\n".join(L)
+
+
+def all_groups():
+    seen, out = set(), []
+    for L2, L3 in FAMILIES:
+        for l1 in range(4):
+            paths = group_paths(l1, L2, L3)
+            if not paths:
+                continue
+            key = (l1, tuple(paths))
+            if key not in seen:
+                seen.add(key)
+                out.append((l1, paths))
+    return out
+
+
+def main():
+    groups = all_groups()
+    parts = [
+        "// GENERATED by gen_cw_groups.py - do not edit.  Straight-line Clebsch-Gordan arithmetic of the",
+        "// channelwise tensor product, one struct per group of paths sharing an irrep of operand 1.",
+        "#pragma once",
+        '#include "../cw_macros.cuh"',
+        "",
+    ]
+    for l1, paths in groups:
+        parts.append(emit_group(l1, paths))
+        parts.append("")
+    names = [group_name(l1, p) for l1, p in groups]
+    parts.append("#define CW_FOR_EACH_GROUP(X) \\")
+    parts.append(" \\\n".join(f"  X({n})" for n in names))
+    parts.append("")
+    os.makedirs(os.path.join(HERE, "generated"), exist_ok=True)
+    path = os.path.join(HERE, "generated", "cw_groups.cuh")
+    text = "\n".join(parts)
+    if not os.path.exists(path) or open(path).read() != text:
+        open(path, "w").write(text)
+    return [(group_signature(l1, p), n) for (l1, p), n in zip(groups, names)]
+
+
+if __name__ == "__main__":
+    for sig, n in main():
+        print(sig, n)

@@ -53,9 +53,18 @@ class BufferSpec:
 
 @dataclass(frozen=True)
 class CallConfig:
+    """``layouts[b]`` (b over inputs then outputs) is None when buffer b is exchanged in the
+    polynomial's own component-major (ir_mul) layout, or a tuple of ``(mul, dim)`` blocks
+    when the caller holds it channel-major (mul_ir): specialised kernels fold the
+    transposition into their addressing, the generic path transposes explicitly."""
+
     batch: int
     inputs: Tuple[BufferSpec, ...]
     outputs: Tuple[BufferSpec, ...]
+    layouts: Tuple[Optional[tuple], ...] = ()
+
+    def layout(self, b: int) -> Optional[tuple]:
+        return self.layouts[b] if self.layouts else None
 
 
 class Uniform1dProgram:
@@ -174,6 +183,8 @@ class Uniform1dProgram:
             # gradient of input i takes the dtype of input i (same position in the new inputs)
             dmap = [i for i, r in enumerate(requires_gradient) if r]
             prog = Uniform1dProgram(bwd, self.math_dtype, dmap, name=self.name + "_bwd")
+            if self._special is not None:
+                prog._special = self._special.derive(requires_gradient, has_cotangent)
             self._derivatives[key] = prog
         return prog
 
@@ -192,16 +203,25 @@ class Uniform1dProgram:
             if x.shape[0] != cfg.inputs[i].rows:
                 raise ValueError(f"Input {i} has {x.shape[0]} rows, the call was configured for {cfg.inputs[i].rows}.")
             xs.append(x.contiguous())
-        outs = [
-            torch.zeros((spec.rows, self.row_sizes[self.num_inputs + j]), dtype=self.math_dtype, device=device)
-            for j, spec in enumerate(cfg.outputs)
-        ]
-        if cfg.batch > 0:
-            handled = False
-            if self._special is not None:
-                handled = self._special(self, cfg, xs, outs)
-            if not handled:
+        outs = None
+        if self._special is not None and cfg.batch > 0:
+            outs = self._special.try_run(self, cfg, xs)
+        if outs is None:
+            from .transpose import transpose_blocks
+
+            for i in range(self.num_inputs):
+                if cfg.layout(i) is not None:
+                    xs[i] = transpose_blocks(xs[i], cfg.layout(i), to_ir_mul=True)
+            outs = [
+                torch.zeros((spec.rows, self.row_sizes[self.num_inputs + j]), dtype=self.math_dtype, device=device)
+                for j, spec in enumerate(cfg.outputs)
+            ]
+            if cfg.batch > 0:
                 self._launch_generic(cfg, xs, outs, device)
+            for j in range(self.num_outputs):
+                lay = cfg.layout(self.num_inputs + j)
+                if lay is not None:
+                    outs[j] = transpose_blocks(outs[j], lay, to_ir_mul=False)
         result = []
         for j, o in enumerate(outs):
             m = self.output_dtype_map[j]
@@ -231,7 +251,9 @@ class Uniform1dProgram:
                 bufs[b].index_is_64 = 0
         tables = self.tables_on(device)
         stream = torch.cuda.current_stream(device).cuda_stream
-        with torch.cuda.device(device):
+        from . import profiling
+
+        with torch.cuda.device(device), profiling.kernel(f"u1d_generic[{self.name}]"):
             _lib.check(
                 _lib.lib().cueq_b200_u1d_launch(self.plan(), tables.data_ptr(), cfg.batch, bufs, nb, C.c_void_p(stream))
             )
@@ -300,7 +322,10 @@ def derivative_config(cfg: CallConfig, requires_gradient: Sequence[bool], has_co
     """A cotangent is addressed like the output it belongs to, a gradient like its input."""
     ins = list(cfg.inputs) + [s for s, h in zip(cfg.outputs, has_cotangent) if h]
     outs = [s for s, r in zip(cfg.inputs, requires_gradient) if r]
-    return CallConfig(cfg.batch, tuple(ins), tuple(outs))
+    n_in = len(cfg.inputs)
+    lay = [cfg.layout(b) for b in range(n_in + len(cfg.outputs))]
+    lays = lay[:n_in] + [l for l, h in zip(lay[n_in:], has_cotangent) if h] + [l for l, r in zip(lay[:n_in], requires_gradient) if r]
+    return CallConfig(cfg.batch, tuple(ins), tuple(outs), tuple(lays))
 
 
 class PolynomialFunction(torch.autograd.Function):
@@ -335,7 +360,9 @@ class PolynomialFunction(torch.autograd.Function):
         return (None, None, *grads)
 
 
-def evaluate(program: Uniform1dProgram, inputs, input_indices=None, output_shapes=None, output_indices=None):
+def evaluate(program: Uniform1dProgram, inputs, input_indices=None, output_shapes=None, output_indices=None, layouts=None):
+    """``layouts``: optional {buffer id (inputs then outputs): ((mul, dim), ...)} for buffers
+    held channel-major (mul_ir) by the caller."""
     input_indices = dict(input_indices or {})
     output_shapes = dict(output_shapes or {})
     output_indices = dict(output_indices or {})
@@ -343,6 +370,16 @@ def evaluate(program: Uniform1dProgram, inputs, input_indices=None, output_shape
     if len(inputs) != program.num_inputs:
         raise ValueError("the number of inputs must match the number of inputs of the polynomial")
     cfg, expand = make_config(program, inputs, input_indices, output_shapes, output_indices)
+    if layouts:
+        nb = program.num_inputs + program.num_outputs
+        lays = []
+        for b in range(nb):
+            blocks = layouts.get(b)
+            if blocks is not None and all(m == 1 or d == 1 for m, d in blocks):
+                blocks = None  # both layouts coincide
+            lays.append(None if blocks is None else tuple((int(m), int(d)) for m, d in blocks))
+        if any(l is not None for l in lays):
+            cfg = CallConfig(cfg.batch, cfg.inputs, cfg.outputs, tuple(lays))
     outs = list(PolynomialFunction.apply(program, cfg, *inputs))
     for j, rows in expand.items():
         outs[j] = outs[j].expand(rows, outs[j].shape[1]).clone()

@@ -9,7 +9,6 @@ import torch
 from .. import descriptors
 from ..irreps import Irreps, IrrepsLayout
 from ..segmented_polynomial import SegmentedPolynomial
-from ..transpose import TransposeIrrepsLayout
 
 
 class ChannelWiseTensorProduct(torch.nn.Module):
@@ -62,9 +61,14 @@ class ChannelWiseTensorProduct(torch.nn.Module):
         if method not in (None, "uniform_1d"):
             raise ValueError(f"method {method!r} is not available for ChannelWiseTensorProduct (only 'uniform_1d')")
         self.method = "uniform_1d"
-        self.transpose_in1 = TransposeIrrepsLayout(irreps_in1, source=IrrepsLayout.parse(layout_in1 or layout), target=e.inputs[1].layout, device=device)
-        self.transpose_in2 = TransposeIrrepsLayout(irreps_in2, source=IrrepsLayout.parse(layout_in2 or layout), target=e.inputs[2].layout, device=device)
-        self.transpose_out = TransposeIrrepsLayout(self.irreps_out, source=e.outputs[0].layout, target=IrrepsLayout.parse(layout_out or layout), device=device)
+        # layouts are handed to the executor, which folds them into kernel addressing when it
+        # can and transposes explicitly otherwise (the reference always transposes,
+        # tp_channel_wise.py:221-222,258)
+        self._layouts = {}
+        for b, (irreps, lay) in {1: (irreps_in1, layout_in1 or layout), 2: (irreps_in2, layout_in2 or layout),
+                                 3: (self.irreps_out, layout_out or layout)}.items():
+            if IrrepsLayout.parse(lay) is IrrepsLayout.mul_ir:
+                self._layouts[b] = tuple((mul, ir.dim) for mul, ir in irreps)
         self.f = SegmentedPolynomial(e.polynomial, method=self.method, math_dtype=math_dtype, name="channelwise_tensor_product")
 
     def extra_repr(self) -> str:
@@ -80,8 +84,6 @@ class ChannelWiseTensorProduct(torch.nn.Module):
         indices_out: Optional[torch.Tensor] = None,
         size_out: Optional[int] = None,
     ) -> torch.Tensor:
-        x1 = self.transpose_in1(x1)
-        x2 = self.transpose_in2(x2)
         indices_in: Dict[int, torch.Tensor] = {}
         if indices_1 is not None:
             indices_in[1] = indices_1
@@ -100,5 +102,6 @@ class ChannelWiseTensorProduct(torch.nn.Module):
             weight = self.weight
         elif weight is None:
             raise ValueError("Internal weights are not used, weight should not be None")
-        out = self.f([weight, x1, x2], input_indices=indices_in, output_shapes=sizes_out, output_indices=idx_out)
-        return self.transpose_out(out[0])
+        out = self.f([weight, x1, x2], input_indices=indices_in, output_shapes=sizes_out, output_indices=idx_out,
+                     layouts=self._layouts)
+        return out[0]

@@ -141,7 +141,10 @@ class SegmentedPolynomial(nn.Module):
         input_indices: Optional[Dict[int, torch.Tensor]] = None,
         output_shapes: Optional[Dict[int, torch.Tensor]] = None,
         output_indices: Optional[Dict[int, torch.Tensor]] = None,
+        layouts: Optional[Dict[int, tuple]] = None,
     ) -> List[torch.Tensor]:
+        """Reference signature plus ``layouts``: {buffer id (inputs, then outputs):
+        ((mul, dim), ...)} for buffers the caller holds channel-major (mul_ir)."""
         input_indices = dict(input_indices or {})
         output_shapes = dict(output_shapes or {})
         output_indices = dict(output_indices or {})
@@ -164,4 +167,4 @@ class SegmentedPolynomial(nn.Module):
             md = inputs[0].dtype
         else:
             md = torch.float32
-        return evaluate(self._program(md), inputs, input_indices, output_shapes, output_indices)
+        return evaluate(self._program(md), inputs, input_indices, output_shapes, output_indices, layouts)

@@ -103,3 +103,22 @@ class TransposeIrrepsLayout(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.f is None else self.f(x)
+
+
+_INFO_CACHE: dict = {}
+
+
+def transpose_blocks(x: torch.Tensor, blocks, to_ir_mul: bool) -> torch.Tensor:
+    """Explicit layout change of a row-major ``[rows, sum(mul*dim)]`` tensor (no autograd):
+    ``blocks`` = ((mul, dim), ...); mul_ir -> ir_mul when ``to_ir_mul`` else the reverse."""
+    key = (tuple(blocks), bool(to_ir_mul), x.device)
+    info = _INFO_CACHE.get(key)
+    if info is None:
+        rows, off = [], 0
+        for mul, dim in blocks:
+            u, v = (mul, dim) if to_ir_mul else (dim, mul)
+            rows.append([off, u, v, -1] if (u > 1 and v > 1) else [off, 1, u * v, -1])
+            off += mul * dim
+        info = torch.tensor(rows, dtype=torch.int32, device=x.device).reshape(-1, 4)
+        _INFO_CACHE[key] = info
+    return _launch(x, info)

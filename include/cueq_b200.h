@@ -100,6 +100,57 @@ int cueq_b200_segmented_transpose(const void* x, void* y, int64_t rows, int64_t 
                                   const int32_t* info_dev, int32_t num_blocks, int32_t dtype,
                                   void* stream);
 
+
+/* ---- channelwise ("uvu") tensor product, specialised kernels --------------------------------
+ *
+ * Replace the uniform_1d op for the polynomial uv,iu,jv,kuv+ijk of
+ * cue.descriptors.channelwise_tensor_product (cuequivariance/group_theory/descriptors/irreps_tp.py:232-321)
+ * as called by ChannelWiseTensorProduct.forward (cuequivariance_torch/operations/tp_channel_wise.py:186-258),
+ * float32, with the gather of x1 by sender, the scatter-add to receivers and the mul_ir<->ir_mul
+ * transpositions (tp_channel_wise.py:221-222,258) fused.  One call handles one *group*: the paths
+ * that read the same irrep of x1.  Built-in groups are enumerated with cueq_b200_cw_num_groups /
+ * cueq_b200_cw_group_signature ("l1:l2.l3,l2.l3,..." in descriptor path order).
+ *
+ * Edges are addressed through a CSR over receivers: rowptr[n]..rowptr[n+1] are the positions
+ * of receiver n, order[pos] the edge id at a position (NULL: positions are edge ids, i.e. the
+ * edge list is sorted by receiver), senders[edge] the x1 row (NULL: the edge id).
+ * The tables describe M[i,k] = sum_j C[i,j,k] x2[j]: pair q owns terms tab_start[q]..tab_start[q+1],
+ * each term a coefficient tab_c[t] and an x2 element tab_j[t]; pairs are ordered path by path,
+ * k-major for the forward call and i-major for the backward call.  bwd_coef (host memory,
+ * num_terms floats) lists the coefficients in the backward term order. */
+typedef struct {
+  const void* w;        /* [E, w_stride]    per-edge weights                                  */
+  const void* x1;       /* [N1, x1_stride]  node features                                     */
+  const void* x2;       /* [E, x2_stride]   per-edge second operand (one scalar per component) */
+  void* out;            /* forward: [num_receivers, out_stride], every row is overwritten       */
+  const void* gout;     /* backward: cotangent of out                                           */
+  void* gw;             /* backward: [E, w_stride], overwritten; NULL to skip                   */
+  void* gx1;            /* backward: [N1, x1_stride], ACCUMULATED into (zero it first); NULL to skip */
+  void* gx2;            /* backward: [E, x2_stride], ACCUMULATED into (zero it first); NULL to skip  */
+  const int32_t* senders;
+  const int32_t* order;
+  const int32_t* rowptr;
+  const int32_t* tab_start;
+  const int32_t* tab_j;
+  const float* tab_c;
+  const float* bwd_coef;
+  int64_t w_stride, x1_stride, x2_stride, out_stride; /* row strides in elements               */
+  int64_t num_receivers;
+  int32_t extent;       /* channels per segment (multiple of 4)                                 */
+  int32_t x1_offset;    /* element offset of the group's irrep block in an x1 row               */
+  int32_t num_paths, num_terms;
+  int32_t w_offset[8];  /* element offset of each path's weight segment in a w row              */
+  int32_t out_offset[8];/* element offset of each path's output block in an out row             */
+  int32_t x1_mul_ir;    /* 1: x1/gx1 blocks are [channel][component], 0: [component][channel]   */
+  int32_t out_mul_ir;   /* same for out/gout                                                    */
+} cueq_cw_args;
+
+int cueq_b200_cw_num_groups(void);
+const char* cueq_b200_cw_group_signature(int group);
+int cueq_b200_cw_group_info(int group, int32_t* d1, int32_t* num_paths, int32_t* num_pairs, int32_t* num_terms);
+int cueq_b200_cw_forward(int group, const cueq_cw_args* args, void* stream);
+int cueq_b200_cw_backward(int group, const cueq_cw_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,7 +39,8 @@ def _close(a, b, rtol, atol, what=""):
     a = a.detach().cpu().double().numpy() if torch.is_tensor(a) else np.asarray(a, dtype=np.float64)
     b = b.detach().cpu().double().numpy() if torch.is_tensor(b) else np.asarray(b, dtype=np.float64)
     assert a.shape == b.shape, (what, a.shape, b.shape)
-    err = np.abs(a - b) - (atol + rtol * np.abs(b))
+    scale = max(1.0, float(np.abs(b).max())) if b.size else 1.0  # absolute term in units of the tensor's magnitude
+    err = np.abs(a - b) - (atol * scale + rtol * np.abs(b))
     assert np.all(err <= 0), f"{what}: max abs diff {np.abs(a - b).max():.3e}, worst excess {err.max():.3e}"
 
 
