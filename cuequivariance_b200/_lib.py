@@ -54,7 +54,7 @@ class CwArgs(C.Structure):
         ("num_receivers", C.c_int64),
         ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
         ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
-        ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32),
+        ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32), ("channels_per_lane", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

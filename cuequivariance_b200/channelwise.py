@@ -85,6 +85,7 @@ class _CsrCache:
 
 
 _CSR = _CsrCache()
+CHANNELS_PER_LANE = 0  # 0: the library chooses; 2 or 4 force a variant (used by the tests)
 _IDENTITY_ROWPTR: dict = {}
 
 
@@ -270,6 +271,7 @@ class _ChannelwiseBase:
             a.out_offset[q] = g["out_off"][q]
         a.x1_mul_ir = 1 if common["x1_mul_ir"] else 0
         a.out_mul_ir = 1 if out_mul_ir else 0
+        a.channels_per_lane = CHANNELS_PER_LANE
         keep = None
         if which == "bwd_tab":
             keep = (C.c_float * g["nterm"])(*g["bwd_tab"][2])
@@ -294,7 +296,7 @@ class ChannelwiseForward(_ChannelwiseBase):
         plan = self.plan
         out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
         csr = self._csr(cfg.outputs[0], cfg.batch, xs[0].device)
-        if out_mul_ir is None or csr is None:
+        if out_mul_ir is None or csr is None or out_mul_ir != common["x1_mul_ir"]:
             return None
         order, rowptr, nrecv = csr
         w, x1, x2 = xs
@@ -334,7 +336,7 @@ class ChannelwiseBackward(_ChannelwiseBase):
         plan = self.plan
         out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
         csr = self._csr(cfg.inputs[3], cfg.batch, xs[0].device)
-        if out_mul_ir is None or csr is None:
+        if out_mul_ir is None or csr is None or out_mul_ir != common["x1_mul_ir"]:
             return None
         # gradient layouts must mirror the input layouts
         k = 4

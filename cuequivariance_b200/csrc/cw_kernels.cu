@@ -63,304 +63,313 @@ struct CwParams {
   int need_gw, need_gx1, need_gx2;
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+template <int C> struct VecT;
+template <> struct VecT<4> { using type = float4; };
+template <> struct VecT<2> { using type = float2; };
+template <int C> using Vec = typename VecT<C>::type;
+
+__device__ __forceinline__ void to_array(const float4& v, float (&a)[4]) { a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+__device__ __forceinline__ void to_array(const float2& v, float (&a)[2]) { a[0] = v.x; a[1] = v.y; }
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+  if constexpr (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void red_add_v4(float* addr, const float (&v)[4]) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
-               : "memory");
+__device__ __forceinline__ void red_add(float* addr, const float (&v)[4]) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
 }
-__device__ __forceinline__ void st_stream_v4(float* addr, const float (&v)[4]) {
-  asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
-               : "memory");
+__device__ __forceinline__ void red_add(float* addr, const float (&v)[2]) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]) : "memory");
+}
+__device__ __forceinline__ void st_stream(float* addr, const float (&v)[4]) {
+  asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+}
+__device__ __forceinline__ void st_stream(float* addr, const float (&v)[2]) {
+  asm volatile("st.global.cs.v2.f32 [%0], {%1, %2};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]) : "memory");
 }
 
-// shared memory carve-up, in floats
-template <class G>
+// shared memory carve-up, in floats.  C = channels per lane.  Everything is per warp.
+template <class G, int C>
 struct Smem {
-  static constexpr int kTabInts = (G::NPAIR + 1) + G::NTERM;               // tab_start + tab_j
-  static constexpr int kTab = ((kTabInts + G::NTERM + 3) / 4) * 4;          // + tab_c
   static constexpr int kM = G::NPAIR_PAD;                                   // per stage
-  static constexpr int kStage = (G::D1 + G::NPATH) * 32 * 4;                // per stage: x1 block + weights
-  static constexpr int kPerWarpFwd = 2 * kM + 2 * kStage;
-  static constexpr int kGrow = G::SUMD3 * 32 * 4;                           // cotangent row of the receiver
+  static constexpr int kX2 = 16;                                            // per stage: x2 row (<= 16 floats)
+  static constexpr int kStage = (G::D1 + G::NPATH) * 32 * C;                // per stage: x1 block + weights
+  static constexpr int kPerStage = kM + kX2 + kStage;
+  static constexpr int kPerWarpFwd = 2 * kPerStage;
+  static constexpr int kGrow = G::SUMD3 * 32 * C;                           // cotangent row of the receiver
   static constexpr int kPerWarpBwd = kPerWarpFwd + kGrow;
-  static constexpr size_t bytes_fwd() { return sizeof(float) * (kTab + kWarps * kPerWarpFwd); }
-  static constexpr size_t bytes_bwd() { return sizeof(float) * (kTab + kWarps * kPerWarpBwd); }
+  static constexpr size_t bytes_fwd() { return sizeof(float) * (kWarps * kPerWarpFwd); }
+  static constexpr size_t bytes_bwd() { return sizeof(float) * (kWarps * kPerWarpBwd); }
 };
 
-// x1 block of one edge -> lane-private staging (D1 float4 per lane)
-template <class G, bool MUL_IR>
-__device__ __forceinline__ void stage_x1(float4* dst, const float* row, int extent, int c0, int lane) {
+// Block of D contiguous-per-component values of the C channels of this lane, between global
+// memory and lane-private staging.  ir_mul: component t of the lane's channels sits at
+// base + t*extent + ch;  mul_ir: the lane's C*D values are contiguous at base + ch*D.
+template <int D, int C, bool MUL_IR>
+__device__ __forceinline__ void stage_block(Vec<C>* dst, const float* base, int extent, int ch, int lane) {
 #pragma unroll
-  for (int t = 0; t < G::D1; ++t) {
-    const float* src = MUL_IR ? row + (int64_t)(c0 + 4 * lane) * G::D1 + 4 * t : row + (int64_t)t * extent + c0 + 4 * lane;
-    cp_async16(dst + t * 32 + lane, src);
+  for (int t = 0; t < D; ++t) {
+    const float* src = MUL_IR ? base + (int64_t)ch * D + C * t : base + (int64_t)t * extent + ch;
+    cp_async<4 * C>(dst + t * 32 + lane, src);
   }
 }
 
-// staging -> X[i][c]
-template <class G, bool MUL_IR>
-__device__ __forceinline__ void unstage_x1(const float4* src, int lane, float (&X)[G::D1][4]) {
-  float f[G::D1 * 4];
+template <int D, int C, bool MUL_IR, int ROWS>
+__device__ __forceinline__ void unstage_block(const Vec<C>* src, int lane, float (&X)[ROWS][C]) {
+  float f[D * C];
 #pragma unroll
-  for (int t = 0; t < G::D1; ++t) {
-    const float4 v = src[t * 32 + lane];
-    f[4 * t + 0] = v.x; f[4 * t + 1] = v.y; f[4 * t + 2] = v.z; f[4 * t + 3] = v.w;
+  for (int t = 0; t < D; ++t) {
+    float a[C];
+    to_array(src[t * 32 + lane], a);
+#pragma unroll
+    for (int c = 0; c < C; ++c) f[C * t + c] = a[c];
   }
 #pragma unroll
-  for (int i = 0; i < G::D1; ++i)
+  for (int i = 0; i < D; ++i)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) X[i][c] = MUL_IR ? f[c * G::D1 + i] : f[4 * i + c];
+    for (int c = 0; c < C; ++c) X[i][c] = MUL_IR ? f[c * D + i] : f[C * i + c];
 }
 
-// M[q] = sum_t c[t] * x2[j[t]] for every pair q of the group, spread over the lanes
-template <class G>
-__device__ __forceinline__ void compute_m(float* M, const int* tab_start, const int* tab_j, const float* tab_c,
-                                          const float* __restrict__ x2row, int lane) {
-  for (int q = lane; q < G::NPAIR; q += 32) {
-    const int t0 = tab_start[q], t1 = tab_start[q + 1];
-    float m = 0.f;
-    for (int t = t0; t < t1; ++t) m = fmaf(tab_c[t], __ldg(x2row + tab_j[t]), m);
-    M[q] = m;
-  }
-}
-
-template <class G>
-__device__ __forceinline__ void load_tables(float* smem, const CwParams& p, int*& tab_start, int*& tab_j, float*& tab_c) {
-  tab_start = reinterpret_cast<int*>(smem);
-  tab_j = tab_start + (G::NPAIR + 1);
-  tab_c = smem + Smem<G>::kTabInts;
-  for (int i = threadIdx.x; i < G::NPAIR + 1; i += blockDim.x) tab_start[i] = p.tab_start[i];
-  for (int i = threadIdx.x; i < G::NTERM; i += blockDim.x) {
-    tab_j[i] = p.tab_j[i];
-    tab_c[i] = p.tab_c[i];
-  }
-  __syncthreads();
-}
-
-template <class G, int P, bool X1_MUL_IR>
-struct FwdPaths {
-  __device__ __forceinline__ static void run(const float (&X)[G::D1][4], const float4* wst, int lane, const float* M,
-                                             float (&acc)[G::SUMD3][4]) {
-    const float4 v = wst[P * 32 + lane];
-    const float W[4] = {v.x, v.y, v.z, v.w};
-    G::template fwd_path<P>(X, W, M, acc);
-    if constexpr (P + 1 < G::NPATH) FwdPaths<G, P + 1, X1_MUL_IR>::run(X, wst, lane, M, acc);
-  }
-};
-
-template <class G, int P, bool OUT_MUL_IR>
-struct StoreOut {
-  __device__ __forceinline__ static void run(float* orow, const CwParams& p, int c0, int lane, const float (&acc)[G::SUMD3][4]) {
-    constexpr int D3 = G::d3(P);
-    constexpr int O = G::out_offset(P);
-    float* base = orow + p.out_off[P];
-    if (OUT_MUL_IR) {
-      float f[D3 * 4];
+// registers -> global, same two layouts; RED: vector reduction, else streaming store
+template <int D, int C, bool MUL_IR, bool RED, int ROWS>
+__device__ __forceinline__ void emit_block(float* base, int extent, int ch, const float (&V)[ROWS][C], int row0) {
+  if (MUL_IR) {
+    float f[D * C];
 #pragma unroll
-      for (int k = 0; k < D3; ++k)
+    for (int i = 0; i < D; ++i)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) f[c * D3 + k] = acc[O + k][c];
+      for (int c = 0; c < C; ++c) f[c * D + i] = V[row0 + i][c];
 #pragma unroll
-      for (int t = 0; t < D3; ++t) {
-        const float v[4] = {f[4 * t], f[4 * t + 1], f[4 * t + 2], f[4 * t + 3]};
-        st_stream_v4(base + (int64_t)(c0 + 4 * lane) * D3 + 4 * t, v);
-      }
-    } else {
+    for (int t = 0; t < D; ++t) {
+      float v[C];
 #pragma unroll
-      for (int k = 0; k < D3; ++k) st_stream_v4(base + (int64_t)k * p.extent + c0 + 4 * lane, acc[O + k]);
+      for (int c = 0; c < C; ++c) v[c] = f[C * t + c];
+      if (RED) red_add(base + (int64_t)ch * D + C * t, v); else st_stream(base + (int64_t)ch * D + C * t, v);
     }
-    if constexpr (P + 1 < G::NPATH) StoreOut<G, P + 1, OUT_MUL_IR>::run(orow, p, c0, lane, acc);
+  } else {
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+      if (RED) red_add(base + (int64_t)i * extent + ch, V[row0 + i]); else st_stream(base + (int64_t)i * extent + ch, V[row0 + i]);
+    }
+  }
+}
+
+// The channel-independent matrices M of one edge: M[q] = sum_t c[t] * x2[j[t]] for every
+// non-zero (i,k) pair q of the group.  Lane L owns the pairs L, L+32, ...; a pair has at most
+// two terms (true for every coupling with l <= 3), whose coefficients and x2 positions the
+// lane keeps in registers for the whole kernel, so the per-edge work is a handful of
+// shared-memory reads and FMAs without any loop or branch.
+template <class G>
+struct MTerms {
+  static constexpr int R = (G::NPAIR + 31) / 32;
+  float c[R][2];
+  unsigned j[R];  // two 16-bit x2 positions per pair
+
+  __device__ __forceinline__ void load(const CwParams& p, int lane) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int q = lane + 32 * r;
+      c[r][0] = c[r][1] = 0.f;
+      j[r] = 0;
+      if (q < G::NPAIR) {
+        const int t0 = __ldg(p.tab_start + q), t1 = __ldg(p.tab_start + q + 1);
+        if (t1 > t0) { c[r][0] = __ldg(p.tab_c + t0); j[r] = (unsigned)__ldg(p.tab_j + t0); }
+        if (t1 > t0 + 1) { c[r][1] = __ldg(p.tab_c + t0 + 1); j[r] |= (unsigned)__ldg(p.tab_j + t0 + 1) << 16; }
+      }
+    }
+  }
+  __device__ __forceinline__ void compute(float* M, const float* x2row, int lane) const {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float m = fmaf(c[r][1], x2row[j[r] >> 16], c[r][0] * x2row[j[r] & 0xffffu]);
+      if (G::NPAIR % 32 == 0 || r + 1 < R || lane + 32 * r < G::NPAIR_PAD) M[lane + 32 * r] = m;
+    }
   }
 };
 
-template <class G, bool X1_MUL_IR, bool OUT_MUL_IR>
+// asynchronous loads of everything edge `pos` needs into the stage at `st`; returns the edge id
+template <class G, int C, bool X1_MUL_IR>
+__device__ __forceinline__ int issue_edge(const CwParams& p, float* st, int pos, int ch, int lane, bool active) {
+  const int eid = p.order ? __ldg(p.order + pos) : pos;
+  float* x2s = st + Smem<G, C>::kM;
+  Vec<C>* stage = reinterpret_cast<Vec<C>*>(x2s + Smem<G, C>::kX2);
+  if (lane < (G::NX2 + 3) / 4) cp_async<16>(x2s + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane);
+  if (active) {
+    const int snd = p.senders ? __ldg(p.senders + eid) : eid;
+    stage_block<G::D1, C, X1_MUL_IR>(stage, p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, lane);
+    const float* wrow = p.w + (int64_t)eid * p.w_stride + ch;
+    Vec<C>* wst = stage + G::D1 * 32;
+#pragma unroll
+    for (int q = 0; q < G::NPATH; ++q) cp_async<4 * C>(wst + q * 32 + lane, wrow + p.w_off[q]);
+  }
+  cp_async_commit();
+  return eid;
+}
+
+template <class G, int C, int P>
+struct FwdPaths {
+  __device__ __forceinline__ static void run(const float (&X)[G::D1][C], const Vec<C>* wst, int lane, const float* M,
+                                             float (&acc)[G::SUMD3][C]) {
+    float W[C];
+    to_array(wst[P * 32 + lane], W);
+    G::template fwd_path<P, C>(X, W, M, acc);
+    if constexpr (P + 1 < G::NPATH) FwdPaths<G, C, P + 1>::run(X, wst, lane, M, acc);
+  }
+};
+
+template <class G, int C, int P, bool OUT_MUL_IR>
+struct StoreOut {
+  __device__ __forceinline__ static void run(float* orow, const CwParams& p, int ch, const float (&acc)[G::SUMD3][C]) {
+    emit_block<G::d3(P), C, OUT_MUL_IR, false>(orow + p.out_off[P], p.extent, ch, acc, G::out_offset(P));
+    if constexpr (P + 1 < G::NPATH) StoreOut<G, C, P + 1, OUT_MUL_IR>::run(orow, p, ch, acc);
+  }
+};
+
+template <class G, int C, bool MUL_IR>
 __global__ void __launch_bounds__(kWarps * 32) cw_fwd_kernel(const __grid_constant__ CwParams p) {
   extern __shared__ __align__(16) float smem[];
-  int *tab_start, *tab_j;
-  float* tab_c;
-  load_tables<G>(smem, p, tab_start, tab_j, tab_c);
+  using S = Smem<G, C>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* mine = smem + Smem<G>::kTab + warp * Smem<G>::kPerWarpFwd;
-  float* Msm[2] = {mine, mine + Smem<G>::kM};
-  float4* stage[2] = {reinterpret_cast<float4*>(mine + 2 * Smem<G>::kM),
-                      reinterpret_cast<float4*>(mine + 2 * Smem<G>::kM + Smem<G>::kStage)};
-  const int c0 = blockIdx.y * 128;
-  const bool active = c0 + 4 * lane < p.extent;
-
-  auto issue = [&](int pos, int s) {
-    const int eid = p.order ? __ldg(p.order + pos) : pos;
-    if (active) {
-      const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-      stage_x1<G, X1_MUL_IR>(stage[s], p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, c0, lane);
-      const float* wrow = p.w + (int64_t)eid * p.w_stride + c0 + 4 * lane;
-      float4* wst = stage[s] + G::D1 * 32;
-#pragma unroll
-      for (int q = 0; q < G::NPATH; ++q) cp_async16(wst + q * 32 + lane, wrow + p.w_off[q]);
-    }
-    cp_async_commit();
-    return eid;
-  };
+  float* mine = smem + warp * S::kPerWarpFwd;
+  const int ch = blockIdx.y * (32 * C) + C * lane;   // first channel of this lane
+  const bool active = ch < p.extent;
+  MTerms<G> mt;
+  mt.load(p, lane);
 
   const int total_warps = gridDim.x * kWarps;
   for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
     const int beg = __ldg(p.rowptr + n), end = __ldg(p.rowptr + n + 1);
-    float acc[G::SUMD3][4];
+    float acc[G::SUMD3][C];
 #pragma unroll
-    for (int a = 0; a < G::SUMD3; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
-    int eid = 0, eid_next = 0;
-    if (beg < end) eid_next = issue(beg, 0);
+    for (int a = 0; a < G::SUMD3; ++a)
+#pragma unroll
+      for (int c = 0; c < C; ++c) acc[a][c] = 0.f;
+    if (beg < end) issue_edge<G, C, MUL_IR>(p, mine, beg, ch, lane, active);
     for (int pos = beg; pos < end; ++pos) {
-      const int s = (pos - beg) & 1;
-      eid = eid_next;
-      if (pos + 1 < end) eid_next = issue(pos + 1, s ^ 1);
-      compute_m<G>(Msm[s], tab_start, tab_j, tab_c, p.x2 + (int64_t)eid * p.x2_stride, lane);
-      if (pos + 1 < end) cp_async_wait<1>(); else cp_async_wait<0>();
+      float* st = mine + ((pos - beg) & 1) * S::kPerStage;
+      if (pos + 1 < end) {
+        issue_edge<G, C, MUL_IR>(p, mine + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncwarp();
+      mt.compute(st, st + S::kM, lane);
       __syncwarp();
       if (active) {
-        float X[G::D1][4];
-        unstage_x1<G, X1_MUL_IR>(stage[s], lane, X);
-        FwdPaths<G, 0, X1_MUL_IR>::run(X, stage[s] + G::D1 * 32, lane, Msm[s], acc);
+        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kM + S::kX2);
+        float X[G::D1][C];
+        unstage_block<G::D1, C, MUL_IR>(stage, lane, X);
+        FwdPaths<G, C, 0>::run(X, stage + G::D1 * 32, lane, st, acc);
       }
       __syncwarp();
     }
-    if (active) StoreOut<G, 0, OUT_MUL_IR>::run(p.out + (int64_t)n * p.out_stride, p, c0, lane, acc);
+    if (active) StoreOut<G, C, 0, MUL_IR>::run(p.out + (int64_t)n * p.out_stride, p, ch, acc);
   }
 }
 
 // ---- backward ---------------------------------------------------------------------------------
-template <class G, int P, bool X1_MUL_IR, bool OUT_MUL_IR>
+template <class G, int C, int P, bool MUL_IR>
 struct BwdPaths {
-  __device__ __forceinline__ static void run(const float (&X)[G::D1][4], const float4* wst, const float4* grow, int lane,
-                                             const float* M, const CwCoef& coef, const CwParams& p, int64_t eid, int c0,
-                                             float (&gX)[G::D1][4], float (&r)[G::NX2]) {
-    constexpr int D3 = G::d3(P);
-    constexpr int O = G::out_offset(P);
-    const float4 v = wst[P * 32 + lane];
-    const float W[4] = {v.x, v.y, v.z, v.w};
-    float Gk[G::MAXD3][4];
-    {
-      float f[D3 * 4];
-#pragma unroll
-      for (int t = 0; t < D3; ++t) {
-        const float4 g = grow[(O + t) * 32 + lane];
-        f[4 * t + 0] = g.x; f[4 * t + 1] = g.y; f[4 * t + 2] = g.z; f[4 * t + 3] = g.w;
-      }
-#pragma unroll
-      for (int k = 0; k < D3; ++k)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) Gk[k][c] = OUT_MUL_IR ? f[c * D3 + k] : f[4 * k + c];
-    }
-    float gw[4];
-    G::template bwd_path<P>(X, W, M, Gk, coef, gX, gw, r);
-    if (p.need_gw) st_stream_v4(p.gw + eid * p.w_stride + p.w_off[P] + c0 + 4 * lane, gw);
-    if constexpr (P + 1 < G::NPATH)
-      BwdPaths<G, P + 1, X1_MUL_IR, OUT_MUL_IR>::run(X, wst, grow, lane, M, coef, p, eid, c0, gX, r);
+  __device__ __forceinline__ static void run(const float (&X)[G::D1][C], const Vec<C>* wst, const Vec<C>* grow, int lane,
+                                             const float* M, const CwCoef& coef, const CwParams& p, float* gwrow,
+                                             float (&gX)[G::D1][C], float (&r)[16]) {
+    float W[C];
+    to_array(wst[P * 32 + lane], W);
+    float Gk[G::MAXD3][C];
+    unstage_block<G::d3(P), C, MUL_IR>(grow + G::out_offset(P) * 32, lane, Gk);
+    float gw[C];
+    G::template bwd_path<P, C>(X, W, M, Gk, coef, gX, gw, r);
+    if (p.need_gw) st_stream(gwrow + p.w_off[P], gw);
+    if constexpr (P + 1 < G::NPATH) BwdPaths<G, C, P + 1, MUL_IR>::run(X, wst, grow, lane, M, coef, p, gwrow, gX, r);
   }
 };
 
-// cotangent row of a receiver -> lane-private staging; block P holds d3(P) float4 per lane
-template <class G, int P, bool OUT_MUL_IR>
+// cotangent row of a receiver -> lane-private staging; block P holds d3(P) vectors per lane
+template <class G, int C, int P, bool MUL_IR>
 struct StageG {
-  __device__ __forceinline__ static void run(float4* dst, const float* grow, const CwParams& p, int c0, int lane) {
-    constexpr int D3 = G::d3(P);
-    constexpr int O = G::out_offset(P);
-    const float* base = grow + p.out_off[P];
-#pragma unroll
-    for (int t = 0; t < D3; ++t) {
-      const float* src = OUT_MUL_IR ? base + (int64_t)(c0 + 4 * lane) * D3 + 4 * t : base + (int64_t)t * p.extent + c0 + 4 * lane;
-      cp_async16(dst + (O + t) * 32 + lane, src);
-    }
-    if constexpr (P + 1 < G::NPATH) StageG<G, P + 1, OUT_MUL_IR>::run(dst, grow, p, c0, lane);
+  __device__ __forceinline__ static void run(Vec<C>* dst, const float* grow, const CwParams& p, int ch, int lane) {
+    stage_block<G::d3(P), C, MUL_IR>(dst + G::out_offset(P) * 32, grow + p.out_off[P], p.extent, ch, lane);
+    if constexpr (P + 1 < G::NPATH) StageG<G, C, P + 1, MUL_IR>::run(dst, grow, p, ch, lane);
   }
 };
 
-template <class G, bool X1_MUL_IR, bool OUT_MUL_IR>
+// Sum of 16 per-lane values over the warp: on return lane L holds the total of r[L >> 1].
+// Each step exchanges half of the remaining values with the partner lane, so the whole
+// reduction costs about one shuffle per value instead of five.
+__device__ __forceinline__ float reduce16(float (&r)[16], int lane) {
+#pragma unroll
+  for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+    const bool up = lane & bit;
+#pragma unroll
+    for (int t = 0; t < half; ++t) {
+      const float send = up ? r[t] : r[t + half];
+      const float keep = up ? r[t + half] : r[t];
+      r[t] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+    }
+  }
+  return r[0] + __shfl_xor_sync(0xffffffffu, r[0], 1);
+}
+
+template <class G, int C, bool MUL_IR>
 __global__ void __launch_bounds__(kWarps * 32) cw_bwd_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
   extern __shared__ __align__(16) float smem[];
-  int *tab_start, *tab_j;
-  float* tab_c;
-  load_tables<G>(smem, p, tab_start, tab_j, tab_c);
+  using S = Smem<G, C>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* mine = smem + Smem<G>::kTab + warp * Smem<G>::kPerWarpBwd;
-  float* Msm[2] = {mine, mine + Smem<G>::kM};
-  float4* stage[2] = {reinterpret_cast<float4*>(mine + 2 * Smem<G>::kM),
-                      reinterpret_cast<float4*>(mine + 2 * Smem<G>::kM + Smem<G>::kStage)};
-  float4* grow = reinterpret_cast<float4*>(mine + Smem<G>::kPerWarpFwd);
-  const int c0 = blockIdx.y * 128;
-  const bool active = c0 + 4 * lane < p.extent;
-
-  auto issue = [&](int pos, int s) {
-    const int eid = p.order ? __ldg(p.order + pos) : pos;
-    if (active) {
-      const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-      stage_x1<G, X1_MUL_IR>(stage[s], p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, c0, lane);
-      const float* wrow = p.w + (int64_t)eid * p.w_stride + c0 + 4 * lane;
-      float4* wst = stage[s] + G::D1 * 32;
-#pragma unroll
-      for (int q = 0; q < G::NPATH; ++q) cp_async16(wst + q * 32 + lane, wrow + p.w_off[q]);
-    }
-    cp_async_commit();
-    return eid;
-  };
+  float* mine = smem + warp * S::kPerWarpBwd;
+  Vec<C>* grow = reinterpret_cast<Vec<C>*>(mine + S::kPerWarpFwd);
+  const int ch = blockIdx.y * (32 * C) + C * lane;
+  const bool active = ch < p.extent;
+  MTerms<G> mt;
+  mt.load(p, lane);
 
   const int total_warps = gridDim.x * kWarps;
   for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
     const int beg = __ldg(p.rowptr + n), end = __ldg(p.rowptr + n + 1);
     if (beg >= end) continue;
-    if (active) StageG<G, 0, OUT_MUL_IR>::run(grow, p.gout + (int64_t)n * p.out_stride, p, c0, lane);
+    if (active) StageG<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)n * p.out_stride, p, ch, lane);
     cp_async_commit();
-    int eid = 0, eid_next = issue(beg, 0);
+    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, mine, beg, ch, lane, active);
     for (int pos = beg; pos < end; ++pos) {
-      const int s = (pos - beg) & 1;
+      float* st = mine + ((pos - beg) & 1) * S::kPerStage;
       eid = eid_next;
-      if (pos + 1 < end) eid_next = issue(pos + 1, s ^ 1);
-      compute_m<G>(Msm[s], tab_start, tab_j, tab_c, p.x2 + (int64_t)eid * p.x2_stride, lane);
-      if (pos + 1 < end) cp_async_wait<1>(); else cp_async_wait<0>();
+      if (pos + 1 < end) {
+        eid_next = issue_edge<G, C, MUL_IR>(p, mine + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
       __syncwarp();
-      float r[G::NX2];
+      mt.compute(st, st + S::kM, lane);
+      __syncwarp();
+      float r[16];
 #pragma unroll
-      for (int j = 0; j < G::NX2; ++j) r[j] = 0.f;
+      for (int j = 0; j < 16; ++j) r[j] = 0.f;
       if (active) {
-        float X[G::D1][4], gX[G::D1][4];
-        unstage_x1<G, X1_MUL_IR>(stage[s], lane, X);
+        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kM + S::kX2);
+        float X[G::D1][C], gX[G::D1][C];
+        unstage_block<G::D1, C, MUL_IR>(stage, lane, X);
 #pragma unroll
-        for (int i = 0; i < G::D1; ++i) gX[i][0] = gX[i][1] = gX[i][2] = gX[i][3] = 0.f;
-        BwdPaths<G, 0, X1_MUL_IR, OUT_MUL_IR>::run(X, stage[s] + G::D1 * 32, grow, lane, Msm[s], coef, p, (int64_t)eid, c0, gX, r);
+        for (int i = 0; i < G::D1; ++i)
+#pragma unroll
+          for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
+        BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, st, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
           const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-          float* grow1 = p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off;
-          if (X1_MUL_IR) {
-            float f[G::D1 * 4];
-#pragma unroll
-            for (int i = 0; i < G::D1; ++i)
-#pragma unroll
-              for (int c = 0; c < 4; ++c) f[c * G::D1 + i] = gX[i][c];
-#pragma unroll
-            for (int t = 0; t < G::D1; ++t) {
-              const float v[4] = {f[4 * t], f[4 * t + 1], f[4 * t + 2], f[4 * t + 3]};
-              red_add_v4(grow1 + (int64_t)(c0 + 4 * lane) * G::D1 + 4 * t, v);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < G::D1; ++i) red_add_v4(grow1 + (int64_t)i * p.extent + c0 + 4 * lane, gX[i]);
-          }
+          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0);
         }
       }
       if (p.need_gx2) {
-#pragma unroll
-        for (int j = 0; j < G::NX2; ++j) r[j] = cueq::warp_sum(r[j]);
-        float mine_r = 0.f;
-#pragma unroll
-        for (int j = 0; j < G::NX2; ++j)
-          if (lane == j) mine_r = r[j];
-        if (lane < G::NX2) atomicAdd(p.gx2 + (int64_t)eid * p.x2_stride + lane, mine_r);
+        const float tot = reduce16(r, lane);
+        if (!(lane & 1) && (lane >> 1) < G::NX2) atomicAdd(p.gx2 + (int64_t)eid * p.x2_stride + (lane >> 1), tot);
       }
       __syncwarp();
     }
@@ -377,57 +386,65 @@ struct GroupEntry {
 
 int grid_x(int num_receivers) {
   const int want = (num_receivers + kWarps - 1) / kWarps;
-  const int cap = 148 * 16;
+  const int cap = 148 * 32;
   return want < 1 ? 1 : (want < cap ? want : cap);
 }
 
-template <class G, bool A, bool B>
+template <class G, int C, bool A>
 int launch_fwd_t(const CwParams& p, cudaStream_t st) {
-  const size_t smem = Smem<G>::bytes_fwd();
+  const size_t smem = Smem<G, C>::bytes_fwd();
   static bool configured = false;
   if (!configured) {
-    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_fwd_kernel<G, A, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_fwd_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid(grid_x(p.num_receivers), (p.extent + 127) / 128);
-  cw_fwd_kernel<G, A, B><<<grid, kWarps * 32, smem, st>>>(p);
+  dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
+  cw_fwd_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 template <class G>
-int launch_fwd(const CwParams& p, int x1_mul_ir, int out_mul_ir, cudaStream_t st) {
-  if (x1_mul_ir) return out_mul_ir ? launch_fwd_t<G, true, true>(p, st) : launch_fwd_t<G, true, false>(p, st);
-  return out_mul_ir ? launch_fwd_t<G, false, true>(p, st) : launch_fwd_t<G, false, false>(p, st);
+int launch_fwd(const CwParams& p, int mul_ir, int cpl, cudaStream_t st) {
+  if (cpl == 2) return mul_ir ? launch_fwd_t<G, 2, true>(p, st) : launch_fwd_t<G, 2, false>(p, st);
+  return mul_ir ? launch_fwd_t<G, 4, true>(p, st) : launch_fwd_t<G, 4, false>(p, st);
 }
 
-template <class G, bool A, bool B>
+template <class G, int C, bool A>
 int launch_bwd_t(const CwParams& p, const CwCoef& coef, cudaStream_t st) {
-  const size_t smem = Smem<G>::bytes_bwd();
+  const size_t smem = Smem<G, C>::bytes_bwd();
   static bool configured = false;
   if (!configured) {
-    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_kernel<G, A, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid(grid_x(p.num_receivers), (p.extent + 127) / 128);
-  cw_bwd_kernel<G, A, B><<<grid, kWarps * 32, smem, st>>>(p, coef);
+  dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
+  cw_bwd_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p, coef);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 template <class G>
-int launch_bwd(const CwParams& p, const CwCoef& coef, int x1_mul_ir, int out_mul_ir, cudaStream_t st) {
-  if (x1_mul_ir) return out_mul_ir ? launch_bwd_t<G, true, true>(p, coef, st) : launch_bwd_t<G, true, false>(p, coef, st);
-  return out_mul_ir ? launch_bwd_t<G, false, true>(p, coef, st) : launch_bwd_t<G, false, false>(p, coef, st);
+int launch_bwd(const CwParams& p, const CwCoef& coef, int mul_ir, int cpl, cudaStream_t st) {
+  if (cpl == 2) return mul_ir ? launch_bwd_t<G, 2, true>(p, coef, st) : launch_bwd_t<G, 2, false>(p, coef, st);
+  return mul_ir ? launch_bwd_t<G, 4, true>(p, coef, st) : launch_bwd_t<G, 4, false>(p, coef, st);
 }
 
 #define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, &launch_fwd<G>, &launch_bwd<G>},
 const GroupEntry kGroups[] = {CW_FOR_EACH_GROUP(CW_ENTRY)};
 constexpr int kNumGroups = sizeof(kGroups) / sizeof(kGroups[0]);
 
+int pick_cpl(const cueq_cw_args* a) {
+  if (a->channels_per_lane == 2 || a->channels_per_lane == 4) return a->channels_per_lane;
+  return a->extent >= 64 ? 2 : 4;
+}
+
 int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p) {
   if (!a) return cueq::fail("channelwise: null arguments");
   if (a->extent < 4 || a->extent % 4) return cueq::fail("channelwise: extent %d must be a positive multiple of 4", a->extent);
+  if (a->x1_mul_ir != a->out_mul_ir) return cueq::fail("channelwise: x1 and out must use the same layout");
+  if (a->channels_per_lane != 0 && a->channels_per_lane != 2 && a->channels_per_lane != 4)
+    return cueq::fail("channelwise: channels_per_lane must be 0 (auto), 2 or 4");
   if (a->num_paths != g.npath) return cueq::fail("channelwise: group has %d paths, got %d", g.npath, a->num_paths);
   if (a->num_terms != g.nterm) return cueq::fail("channelwise: group has %d terms, got %d", g.nterm, a->num_terms);
   if (!a->rowptr || !a->tab_start || !a->tab_j || !a->tab_c) return cueq::fail("channelwise: null table or rowptr");
@@ -446,7 +463,8 @@ int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p) {
   }
   if (p.x1_off & 3) return cueq::fail("channelwise: x1 offset must be a multiple of 4 elements");
   if ((p.w_stride | p.x1_stride | p.out_stride) & 3) return cueq::fail("channelwise: row strides must be multiples of 4 elements");
-  const uintptr_t ptrs = (uintptr_t)a->w | (uintptr_t)a->x1 | (uintptr_t)a->out | (uintptr_t)a->gout | (uintptr_t)a->gw | (uintptr_t)a->gx1;
+  const uintptr_t ptrs = (uintptr_t)a->w | (uintptr_t)a->x1 | (uintptr_t)a->x2 | (uintptr_t)a->out | (uintptr_t)a->gout | (uintptr_t)a->gw | (uintptr_t)a->gx1;
+  if (a->x2_stride & 3) return cueq::fail("channelwise: x2 row stride must be a multiple of 4 elements");
   if (ptrs & 15) return cueq::fail("channelwise: tensors must be 16-byte aligned");
   p.need_gw = a->gw != nullptr; p.need_gx1 = a->gx1 != nullptr; p.need_gx2 = a->gx2 != nullptr;
   return 0;
@@ -473,7 +491,7 @@ extern "C" int cueq_b200_cw_forward(int g, const cueq_cw_args* a, void* stream) 
   if (int rc = fill_params(a, kGroups[g], p)) return rc;
   if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise forward: null tensor");
   if (p.num_receivers == 0) return 0;
-  return kGroups[g].fwd(p, a->x1_mul_ir, a->out_mul_ir, reinterpret_cast<cudaStream_t>(stream));
+  return kGroups[g].fwd(p, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream) {
@@ -487,5 +505,5 @@ extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream)
   CwCoef coef;
   std::memset(&coef, 0, sizeof(coef));
   for (int t = 0; t < kGroups[g].nterm; ++t) coef.c[t] = a->bwd_coef[t];
-  return kGroups[g].bwd(p, coef, a->x1_mul_ir, a->out_mul_ir, reinterpret_cast<cudaStream_t>(stream));
+  return kGroups[g].bwd(p, coef, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }

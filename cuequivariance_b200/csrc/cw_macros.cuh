@@ -1,18 +1,40 @@
-// Four-channel helpers used by the generated channelwise bodies (generated/cw_groups.cuh).
-// A thread owns four consecutive channels; a[4] is one value per channel.
+// Per-thread channel-vector helpers used by the generated channelwise bodies
+// (generated/cw_groups.cuh).  A thread owns C consecutive channels (C = 2 or 4); a[C] holds
+// one value per channel.
 #pragma once
 
-#define CW_MUL4(d, s, a)                                                        \
-  { d[0] = (s) * a[0]; d[1] = (s) * a[1]; d[2] = (s) * a[2]; d[3] = (s) * a[3]; }
-#define CW_FMA4(d, s, a)                                                        \
-  { d[0] = fmaf((s), a[0], d[0]); d[1] = fmaf((s), a[1], d[1]);                  \
-    d[2] = fmaf((s), a[2], d[2]); d[3] = fmaf((s), a[3], d[3]); }
-#define CW_MULV4(d, a, b)                                                       \
-  { d[0] = a[0] * b[0]; d[1] = a[1] * b[1]; d[2] = a[2] * b[2]; d[3] = a[3] * b[3]; }
-#define CW_FMAV4(d, a, b)                                                       \
-  { d[0] = fmaf(a[0], b[0], d[0]); d[1] = fmaf(a[1], b[1], d[1]);                \
-    d[2] = fmaf(a[2], b[2], d[2]); d[3] = fmaf(a[3], b[3], d[3]); }
-#define CW_DOT4(a, b) fmaf(a[3], b[3], fmaf(a[2], b[2], fmaf(a[1], b[1], a[0] * b[0])))
+template <int C>
+__device__ __forceinline__ void cw_mul(float (&d)[C], float s, const float (&a)[C]) {
+#pragma unroll
+  for (int c = 0; c < C; ++c) d[c] = s * a[c];
+}
+template <int C>
+__device__ __forceinline__ void cw_fma(float (&d)[C], float s, const float (&a)[C]) {
+#pragma unroll
+  for (int c = 0; c < C; ++c) d[c] = fmaf(s, a[c], d[c]);
+}
+template <int C>
+__device__ __forceinline__ void cw_mulv(float (&d)[C], const float (&a)[C], const float (&b)[C]) {
+#pragma unroll
+  for (int c = 0; c < C; ++c) d[c] = a[c] * b[c];
+}
+template <int C>
+__device__ __forceinline__ void cw_fmav(float (&d)[C], const float (&a)[C], const float (&b)[C]) {
+#pragma unroll
+  for (int c = 0; c < C; ++c) d[c] = fmaf(a[c], b[c], d[c]);
+}
+template <int C>
+__device__ __forceinline__ float cw_dot(const float (&a)[C], const float (&b)[C]) {
+  float v = a[0] * b[0];
+#pragma unroll
+  for (int c = 1; c < C; ++c) v = fmaf(a[c], b[c], v);
+  return v;
+}
+#define CW_MUL4(d, s, a) cw_mul(d, s, a)
+#define CW_FMA4(d, s, a) cw_fma(d, s, a)
+#define CW_MULV4(d, a, b) cw_mulv(d, a, b)
+#define CW_FMAV4(d, a, b) cw_fmav(d, a, b)
+#define CW_DOT4(a, b) cw_dot(a, b)
 
 // Loads N consecutive floats starting at M[Q0] (M is 16-byte aligned shared memory, every
 // lane reads the same addresses: broadcast) using 128-bit loads where the alignment allows.

@@ -84,9 +84,9 @@ def emit_group(l1: int, paths) -> str:
 
     # ---- forward ------------------------------------------------------------------------
     A("  // acc[out_offset(p) + k][c] += W[p][c] * sum_i M[q(i,k)] * X[i][c]")
-    A("  template <int P>")
-    A("  __device__ __forceinline__ static void fwd_path(const float (&X)[D1][4], const float (&W)[4], const float* __restrict__ M,")
-    A("                                                  float (&acc)[SUMD3][4]) {")
+    A("  template <int P, int C>")
+    A("  __device__ __forceinline__ static void fwd_path(const float (&X)[D1][C], const float (&W)[C], const float* __restrict__ M,")
+    A("                                                  float (&acc)[SUMD3][C]) {")
     for p, (pat, d3) in enumerate(zip(pats, d3s)):
         A(f"    if constexpr (P == {p}) {{")
         # load the M entries of this path as float4 where aligned
@@ -101,7 +101,7 @@ def emit_group(l1: int, paths) -> str:
             if not terms:
                 continue
             A("      {")
-            A("        float t[4];")
+            A("        float t[C];")
             q, i = terms[0]
             A(f"        CW_MUL4(t, m[{q}], X[{i}]);")
             for q, i in terms[1:]:
@@ -114,17 +114,18 @@ def emit_group(l1: int, paths) -> str:
     # ---- backward -----------------------------------------------------------------------
     A("  // per path, pairs ordered by i: S[i] = sum_k M[q] G[k];  gX[i] += W*S[i];  gw = sum_i S[i] X[i];")
     A("  //           r[j] += c * dot4(W*X[i], G[k]) over the non-zero (i, j, k)")
-    A("  template <int P, class Coef>")
-    A("  __device__ __forceinline__ static void bwd_path(const float (&X)[D1][4], const float (&W)[4], const float* __restrict__ M,")
-    A("                                                  const float (&G)[MAXD3][4], const Coef& coef,")
-    A("                                                  float (&gX)[D1][4], float (&gw)[4], float (&r)[NX2]) {")
+    A("  template <int P, int C, class Coef>")
+    A("  __device__ __forceinline__ static void bwd_path(const float (&X)[D1][C], const float (&W)[C], const float* __restrict__ M,")
+    A("                                                  const float (&G)[MAXD3][C], const Coef& coef,")
+    A("                                                  float (&gX)[D1][C], float (&gw)[C], float (&r)[16]) {")
     term_cursor = 0
     for p, (pat, d3, d2) in enumerate(zip(pats_i, d3s, d2s)):
         l2 = paths[p][0]
         j_base = l2 * l2  # offset of irrep l2 inside x2 = 0e+1o+2e+...
         A(f"    if constexpr (P == {p}) {{")
         q0 = pair_off[p]
-        A("      gw[0] = gw[1] = gw[2] = gw[3] = 0.f;")
+        A("#pragma unroll")
+        A("      for (int c = 0; c < C; ++c) gw[c] = 0.f;")
         by_i: dict[int, list] = {}
         for q, (i, k, terms) in enumerate(pat):
             by_i.setdefault(i, []).append((q, k, terms))
@@ -137,7 +138,7 @@ def emit_group(l1: int, paths) -> str:
             A("      {")
             A(f"        float m[{len(lst)}];")
             A(f"        cw_load_m<{q0 + qa}, {len(lst)}>(M, m);")
-            A("        float s[4], xw[4];")
+            A("        float s[C], xw[C];")
             A(f"        CW_MULV4(xw, W, X[{i}]);")
             for n, (q, k, terms) in enumerate(lst):
                 if n == 0:

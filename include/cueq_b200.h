@@ -142,7 +142,9 @@ typedef struct {
   int32_t w_offset[8];  /* element offset of each path's weight segment in a w row              */
   int32_t out_offset[8];/* element offset of each path's output block in an out row             */
   int32_t x1_mul_ir;    /* 1: x1/gx1 blocks are [channel][component], 0: [component][channel]   */
-  int32_t out_mul_ir;   /* same for out/gout                                                    */
+  int32_t out_mul_ir;   /* same for out/gout (must equal x1_mul_ir)                             */
+  int32_t channels_per_lane; /* 0: automatic; 2 or 4: channels owned by one thread              */
+  int32_t reserved;
 } cueq_cw_args;
 
 int cueq_b200_cw_num_groups(void);
