@@ -186,6 +186,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--edges", type=int, default=E_TOTAL, help="total edges (default: the named configuration)")
     ap.add_argument("--nodes", type=int, default=N_TOTAL)
+    ap.add_argument("--cpl", type=int, default=0, help="force channels per lane (2 or 4) in the channelwise kernels; 0 = library default")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -211,6 +212,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.cpl:
+        from cuequivariance_b200 import channelwise
+
+        channelwise.CHANNELS_PER_LANE = args.cpl
     E, N = args.edges, args.nodes
     tp = cb.ChannelWiseTensorProduct(IRREPS1, IRREPS2, FILTER, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
     sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)

@@ -33,6 +33,23 @@ def pair_pattern(l1: int, l2: int, l3: int, major: str) -> List[Tuple[int, int, 
     return out
 
 
+SPLIT_GROUPS = False  # measured on B200: one launch per irrep beats two lighter launches
+
+
+def split_group(l1: int, paths: Sequence[Tuple[int, int]]) -> List[List[Tuple[int, int]]]:
+    """How the paths that read irrep ``l1`` are divided into kernel launches.  A launch keeps
+    one accumulator per output component of its paths in registers, so large groups are cut
+    in two parts of similar arithmetic weight (the two heaviest couplings form one part);
+    this keeps four channels per thread within the register budget."""
+    paths = list(paths)
+    if not SPLIT_GROUPS or (len(paths) <= 4 and sum(2 * l3 + 1 for _, l3 in paths) <= 16):
+        return [paths]
+    weight = {p: len(pair_pattern(l1, p[0], p[1], "k")) for p in paths}
+    heavy = sorted(paths, key=lambda p: -weight[p])[:2]
+    light = [p for p in paths if p not in heavy]
+    return [light, [p for p in paths if p in heavy]]
+
+
 def group_signature(l1: int, paths: Sequence[Tuple[int, int]]) -> str:
     return f"{l1}:" + ",".join(f"{a}.{b}" for a, b in paths)
 
@@ -172,7 +189,18 @@ def match_channelwise(polynomial) -> Optional[ChannelwisePlan]:
         by_i1.setdefault(s1, []).append((l1, l2, l3, sw, so, c))
     lib = _library_groups()
     groups = []
+    launches = []
     for s1, plist in sorted(by_i1.items()):
+        l1 = plist[0][0]
+        all_paths = [(l2, l3) for _, l2, l3, _, _, _ in plist]
+        if len(set(all_paths)) != len(all_paths):
+            return None
+        parts = split_group(l1, all_paths)
+        if any(group_signature(l1, part) not in lib for part in parts):
+            parts = [all_paths]
+        for part in parts:
+            launches.append((s1, [p for p in plist if (p[1], p[2]) in part]))
+    for s1, plist in launches:
         l1 = plist[0][0]
         sig = group_signature(l1, [(l2, l3) for _, l2, l3, _, _, _ in plist])
         if sig not in lib:

@@ -33,7 +33,13 @@ namespace {
 
 constexpr int kMaxPaths = 8;
 constexpr int kMaxTerms = 160;
-constexpr int kWarps = 4;  // warps per CTA
+#ifndef CW_WARPS
+#define CW_WARPS 4
+#endif
+constexpr int kWarps = CW_WARPS;  // warps per CTA
+#ifndef CW_MINBLOCKS
+#define CW_MINBLOCKS 4
+#endif
 
 struct CwCoef {
   float c[kMaxTerms];
@@ -102,8 +108,8 @@ struct Smem {
   static constexpr int kM = G::NPAIR_PAD;                                   // per stage
   static constexpr int kX2 = 16;                                            // per stage: x2 row (<= 16 floats)
   static constexpr int kStage = (G::D1 + G::NPATH) * 32 * C;                // per stage: x1 block + weights
-  static constexpr int kPerStage = kM + kX2 + kStage;
-  static constexpr int kPerWarpFwd = 2 * kPerStage;
+  static constexpr int kPerStage = kX2 + kStage;
+  static constexpr int kPerWarpFwd = kM + 2 * kPerStage;
   static constexpr int kGrow = G::SUMD3 * 32 * C;                           // cotangent row of the receiver
   static constexpr int kPerWarpBwd = kPerWarpFwd + kGrow;
   static constexpr size_t bytes_fwd() { return sizeof(float) * (kWarps * kPerWarpFwd); }
@@ -199,7 +205,7 @@ struct MTerms {
 template <class G, int C, bool X1_MUL_IR>
 __device__ __forceinline__ int issue_edge(const CwParams& p, float* st, int pos, int ch, int lane, bool active) {
   const int eid = p.order ? __ldg(p.order + pos) : pos;
-  float* x2s = st + Smem<G, C>::kM;
+  float* x2s = st;
   Vec<C>* stage = reinterpret_cast<Vec<C>*>(x2s + Smem<G, C>::kX2);
   if (lane < (G::NX2 + 3) / 4) cp_async<16>(x2s + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane);
   if (active) {
@@ -234,7 +240,7 @@ struct StoreOut {
 };
 
 template <class G, int C, bool MUL_IR>
-__global__ void __launch_bounds__(kWarps * 32) cw_fwd_kernel(const __grid_constant__ CwParams p) {
+__global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const __grid_constant__ CwParams p) {
   extern __shared__ __align__(16) float smem[];
   using S = Smem<G, C>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -252,23 +258,25 @@ __global__ void __launch_bounds__(kWarps * 32) cw_fwd_kernel(const __grid_consta
     for (int a = 0; a < G::SUMD3; ++a)
 #pragma unroll
       for (int c = 0; c < C; ++c) acc[a][c] = 0.f;
-    if (beg < end) issue_edge<G, C, MUL_IR>(p, mine, beg, ch, lane, active);
+    float* Msm = mine;
+    float* stages = mine + S::kM;
+    if (beg < end) issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active);
     for (int pos = beg; pos < end; ++pos) {
-      float* st = mine + ((pos - beg) & 1) * S::kPerStage;
+      float* st = stages + ((pos - beg) & 1) * S::kPerStage;
       if (pos + 1 < end) {
-        issue_edge<G, C, MUL_IR>(p, mine + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
       }
       __syncwarp();
-      mt.compute(st, st + S::kM, lane);
+      mt.compute(Msm, st, lane);
       __syncwarp();
       if (active) {
-        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kM + S::kX2);
+        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kX2);
         float X[G::D1][C];
         unstage_block<G::D1, C, MUL_IR>(stage, lane, X);
-        FwdPaths<G, C, 0>::run(X, stage + G::D1 * 32, lane, st, acc);
+        FwdPaths<G, C, 0>::run(X, stage + G::D1 * 32, lane, Msm, acc);
       }
       __syncwarp();
     }
@@ -320,7 +328,7 @@ __device__ __forceinline__ float reduce16(float (&r)[16], int lane) {
 }
 
 template <class G, int C, bool MUL_IR>
-__global__ void __launch_bounds__(kWarps * 32) cw_bwd_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
+__global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
   extern __shared__ __align__(16) float smem[];
   using S = Smem<G, C>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -337,31 +345,33 @@ __global__ void __launch_bounds__(kWarps * 32) cw_bwd_kernel(const __grid_consta
     if (beg >= end) continue;
     if (active) StageG<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)n * p.out_stride, p, ch, lane);
     cp_async_commit();
-    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, mine, beg, ch, lane, active);
+    float* Msm = mine;
+    float* stages = mine + S::kM;
+    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active);
     for (int pos = beg; pos < end; ++pos) {
-      float* st = mine + ((pos - beg) & 1) * S::kPerStage;
+      float* st = stages + ((pos - beg) & 1) * S::kPerStage;
       eid = eid_next;
       if (pos + 1 < end) {
-        eid_next = issue_edge<G, C, MUL_IR>(p, mine + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
       }
       __syncwarp();
-      mt.compute(st, st + S::kM, lane);
+      mt.compute(Msm, st, lane);
       __syncwarp();
       float r[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) r[j] = 0.f;
       if (active) {
-        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kM + S::kX2);
+        const Vec<C>* stage = reinterpret_cast<const Vec<C>*>(st + S::kX2);
         float X[G::D1][C], gX[G::D1][C];
         unstage_block<G::D1, C, MUL_IR>(stage, lane, X);
 #pragma unroll
         for (int i = 0; i < G::D1; ++i)
 #pragma unroll
           for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
-        BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, st, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
+        BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
           const int snd = p.senders ? __ldg(p.senders + eid) : eid;
           emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0);

@@ -27,7 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 import numpy as np  # noqa: E402
 
-from cuequivariance_b200.channelwise import group_signature as _signature, pair_pattern  # noqa: E402
+from cuequivariance_b200.channelwise import group_signature as _signature, pair_pattern, split_group  # noqa: E402
 
 # Groups to build: (l1, [(l2, l3), ...]).  The list below is the family used by MACE-style
 # models: second operand 0e+1o+..+L2 (spherical harmonics), outputs filtered to natural
@@ -168,10 +168,11 @@ def all_groups():
             paths = group_paths(l1, L2, L3)
             if not paths:
                 continue
-            key = (l1, tuple(paths))
-            if key not in seen:
-                seen.add(key)
-                out.append((l1, paths))
+            for part in split_group(l1, paths):
+                key = (l1, tuple(part))
+                if key not in seen:
+                    seen.add(key)
+                    out.append((l1, part))
     return out
 
 
