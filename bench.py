@@ -36,7 +36,7 @@ E_TOTAL, N_TOTAL, MUL = 1_048_576, 32_768, 128
 IRREPS1 = "+".join(f"{MUL}x{ir}" for ir in ("0e", "1o", "2e", "3o"))
 IRREPS2 = "0e+1o+2e+3o"
 FILTER = ["0e", "1o", "2e", "3o"]
-CPU_SAMPLE_EDGES, CPU_SAMPLE_NODES = 4096, 128
+CPU_SAMPLE_EDGES, CPU_SAMPLE_NODES = 16384, 512
 
 
 # ----------------------------------------------------------------------------------------------
@@ -303,7 +303,8 @@ def main():
     total_bytes = sum(v["bytes"] for v in kernels.values())
     traffic = None
     try:
-        traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(dom)
+        per_edge = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))["per_edge_bytes"].get(dom)
+        traffic = per_edge * El if per_edge else None  # ncu capture of a smaller case, scaled by edges
     except (OSError, ValueError):
         pass
     roofline = None

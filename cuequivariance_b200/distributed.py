@@ -55,9 +55,17 @@ class _AllGatherRows(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         world = dist.get_world_size(ctx.group)
-        out = torch.empty((g.shape[0] // world,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
-        dist.reduce_scatter_tensor(out, g.contiguous(), op=dist.ReduceOp.SUM, group=ctx.group)
-        return out, None
+        rows = g.shape[0] // world
+        g = g.contiguous()
+        if g.is_cuda:
+            out = torch.empty((rows,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+            dist.reduce_scatter_tensor(out, g, op=dist.ReduceOp.SUM, group=ctx.group)
+            return out, None
+        # CPU backends (gloo) have no reduce-scatter: all-reduce, then keep the owned rows
+        g = g.clone()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        r = dist.get_rank(ctx.group)
+        return g[r * rows : (r + 1) * rows].clone(), None
 
 
 def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
