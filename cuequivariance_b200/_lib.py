@@ -58,6 +58,19 @@ class CwArgs(C.Structure):
     ]
 
 
+class CwNoAllocArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("x1", C.c_void_p), ("x2", C.c_void_p), ("out", C.c_void_p),
+        ("senders", C.c_void_p), ("receivers", C.c_void_p),
+        ("tab_start_host", C.POINTER(C.c_int32)), ("tab_j_host", C.POINTER(C.c_int32)), ("tab_c_host", C.POINTER(C.c_float)),
+        ("w_stride", C.c_int64), ("x1_stride", C.c_int64), ("x2_stride", C.c_int64), ("out_stride", C.c_int64),
+        ("num_edges", C.c_int64), ("num_receivers", C.c_int64),
+        ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
+        ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
+        ("mul_ir", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -95,6 +108,7 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
     L.cueq_b200_cw_forward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_backward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
+    L.cueq_b200_cw_forward_noalloc.argtypes = [C.c_int, C.POINTER(CwNoAllocArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     _lib = L

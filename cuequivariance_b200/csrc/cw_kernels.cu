@@ -517,3 +517,113 @@ extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream)
   for (int t = 0; t < kGroups[g].nterm; ++t) coef.c[t] = a->bwd_coef[t];
   return kGroups[g].bwd(p, coef, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
+
+// ---- forward without caller-provided scratch ----------------------------------------------------
+//
+// cueq_b200_cw_forward needs two pieces of device memory besides its inputs and outputs: the
+// CSR row pointers over receivers and the term tables.  Some hosts of this library cannot
+// provide them: code that runs where device allocation is forbidden or owned by someone else
+// (an inference-engine plugin whose enqueue call gets only its input and output bindings, a
+// callback running inside a memory pool it must not grow, a real-time loop that may not call
+// the allocator).  For those there is one entry point whose scratch lives in a fixed array
+// inside the library image.  The array exists once per GPU that loads the library, for the
+// life of the process, and every call reuses it.
+namespace {
+
+constexpr int kNoAllocMaxReceivers = 262144;   // row pointers: (N + 1) * 4 bytes = 1 MiB
+constexpr int kNoAllocMaxPairs = 256;
+constexpr int kNoAllocMaxTerms = 256;
+constexpr size_t kScratchRowptr = 0;
+constexpr size_t kScratchTabStart = ((size_t)(kNoAllocMaxReceivers + 1) * 4 + 255) & ~size_t(255);
+constexpr size_t kScratchTabJ = kScratchTabStart + ((kNoAllocMaxPairs + 1) * 4 + 255) / 256 * 256;
+constexpr size_t kScratchTabC = kScratchTabJ + (kNoAllocMaxTerms * 4 + 255) / 256 * 256;
+constexpr size_t kScratchBytes = kScratchTabC + (kNoAllocMaxTerms * 4 + 255) / 256 * 256;
+
+// Host code may only use this name with cudaGetSymbolAddress: as a plain expression it is the
+// host-side shadow of the symbol, not a device address.
+static __device__ __align__(256) unsigned char g_cw_scratch[kScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+struct NoAllocTables {
+  int start[kNoAllocMaxPairs + 1];
+  int j[kNoAllocMaxTerms];
+  float c[kNoAllocMaxTerms];
+};
+
+// rowptr[r] = first position whose receiver is >= r (receivers sorted ascending); also copies
+// the term tables from the kernel parameters into the scratch array
+__global__ void cw_noalloc_prepare(const int* __restrict__ receivers, int num_edges, int num_receivers, int* __restrict__ rowptr,
+                                   const __grid_constant__ NoAllocTables t, int npair, int nterm, int* tab_start, int* tab_j,
+                                   float* tab_c) {
+  const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+  for (int r = gid; r <= num_receivers; r += gridDim.x * blockDim.x) {
+    int lo = 0, hi = num_edges;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(receivers + mid) < r) lo = mid + 1; else hi = mid;
+    }
+    rowptr[r] = lo;
+  }
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i <= npair; i += blockDim.x) tab_start[i] = t.start[i];
+    for (int i = threadIdx.x; i < nterm; i += blockDim.x) { tab_j[i] = t.j[i]; tab_c[i] = t.c[i]; }
+  }
+}
+
+}  // namespace
+
+extern "C" int cueq_b200_cw_forward_noalloc(int g, const cueq_cw_noalloc_args* a, void* stream) {
+  if (g < 0 || g >= kNumGroups) return cueq::fail("channelwise (no-alloc): group %d out of range", g);
+  if (!a) return cueq::fail("channelwise (no-alloc): null arguments");
+  const GroupEntry& ge = kGroups[g];
+  if (a->num_receivers > kNoAllocMaxReceivers)
+    return cueq::fail("channelwise (no-alloc): %lld receivers exceed the built-in scratch (max %d); use cueq_b200_cw_forward",
+                      (long long)a->num_receivers, kNoAllocMaxReceivers);
+  if (ge.npair > kNoAllocMaxPairs || ge.nterm > kNoAllocMaxTerms)
+    return cueq::fail("channelwise (no-alloc): group tables exceed the built-in scratch");
+  if (a->num_edges < 0 || a->num_edges > 2147483647LL) return cueq::fail("channelwise (no-alloc): invalid edge count");
+  if (!a->receivers && a->num_edges > 0) return cueq::fail("channelwise (no-alloc): null receivers");
+  if (!a->tab_start_host || !a->tab_j_host || !a->tab_c_host) return cueq::fail("channelwise (no-alloc): null host table");
+
+  int dev = 0;
+  CUEQ_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return cueq::fail("channelwise (no-alloc): device ordinal %d not supported", dev);
+  if (!g_scratch_ptr[dev]) {  // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    CUEQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_cw_scratch));
+    g_scratch_ptr[dev] = ptr;
+  }
+  unsigned char* scratch = static_cast<unsigned char*>(g_scratch_ptr[dev]);
+  int* rowptr = reinterpret_cast<int*>(scratch + kScratchRowptr);
+  int* tab_start = reinterpret_cast<int*>(scratch + kScratchTabStart);
+  int* tab_j = reinterpret_cast<int*>(scratch + kScratchTabJ);
+  float* tab_c = reinterpret_cast<float*>(scratch + kScratchTabC);
+
+  cueq_cw_args full;
+  std::memset(&full, 0, sizeof(full));
+  full.w = a->w; full.x1 = a->x1; full.x2 = a->x2; full.out = a->out;
+  full.senders = a->senders; full.order = nullptr; full.rowptr = rowptr;
+  full.tab_start = tab_start; full.tab_j = tab_j; full.tab_c = tab_c;
+  full.w_stride = a->w_stride; full.x1_stride = a->x1_stride; full.x2_stride = a->x2_stride; full.out_stride = a->out_stride;
+  full.num_receivers = a->num_receivers; full.extent = a->extent; full.x1_offset = a->x1_offset;
+  full.num_paths = a->num_paths; full.num_terms = a->num_terms;
+  for (int q = 0; q < 8; ++q) { full.w_offset[q] = a->w_offset[q]; full.out_offset[q] = a->out_offset[q]; }
+  full.x1_mul_ir = a->mul_ir; full.out_mul_ir = a->mul_ir; full.channels_per_lane = 0;
+  CwParams p;
+  if (int rc = fill_params(&full, ge, p)) return rc;
+  if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise (no-alloc): null tensor");
+  if (p.num_receivers == 0) return 0;
+
+  NoAllocTables t;
+  std::memset(&t, 0, sizeof(t));
+  for (int i = 0; i <= ge.npair; ++i) t.start[i] = a->tab_start_host[i];
+  for (int i = 0; i < ge.nterm; ++i) { t.j[i] = a->tab_j_host[i]; t.c[i] = a->tab_c_host[i]; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int blocks = (int)((a->num_receivers + 1 + 255) / 256);
+  cw_noalloc_prepare<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(a->receivers, (int)a->num_edges, (int)a->num_receivers, rowptr, t, ge.npair,
+                                                              ge.nterm, tab_start, tab_j, tab_c);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return ge.fwd(p, a->mul_ir, pick_cpl(&full), st);
+}

@@ -153,6 +153,48 @@ int cueq_b200_cw_group_info(int group, int32_t* d1, int32_t* num_paths, int32_t*
 int cueq_b200_cw_forward(int group, const cueq_cw_args* args, void* stream);
 int cueq_b200_cw_backward(int group, const cueq_cw_args* args, void* stream);
 
+/* ---- channelwise forward for callers that cannot allocate ----------------------------------
+ *
+ * No counterpart in the reference.  cueq_b200_cw_forward expects the caller to keep the CSR row
+ * pointers and the term tables in device memory of its own.  A caller that is not allowed to
+ * obtain device memory - a plugin whose host hands it nothing but input and output buffers, code
+ * running under an allocator it must not touch, a latency-critical loop where cudaMalloc is
+ * banned - can use this variant instead: it takes the receiver index itself (int32, sorted
+ * ascending, one entry per edge) and the term tables as HOST arrays, and keeps the derived row
+ * pointers and the device copy of the tables in a fixed array inside the library (about 1 MiB,
+ * present on every GPU that loads the library until the process exits).
+ *
+ * Limits and rules
+ *   - at most 262,144 receivers (more is rejected with an error; use cueq_b200_cw_forward);
+ *   - edges must already be sorted by receiver (there is no `order` argument);
+ *   - the call performs no cudaMalloc/cudaFree and calls no allocating routine; it enqueues two
+ *     kernels on `stream` (row pointers + tables, then the product);
+ *   - the first call on a device looks up the address of the built-in array (with that device
+ *     current); make that first call outside any stream capture;
+ *   - all calls on one GPU share the array, which keeps what the last call wrote; every call
+ *     rewrites the parts it uses, nothing has to be cleared, but two calls that overlap on the
+ *     GPU (different streams) race on it: serialise them. */
+typedef struct {
+  const void* w;
+  const void* x1;
+  const void* x2;
+  void* out;
+  const int32_t* senders;        /* device, [num_edges]; NULL: x1 row = edge id                     */
+  const int32_t* receivers;      /* device, [num_edges], sorted ascending, values in [0, num_receivers) */
+  const int32_t* tab_start_host; /* host, [num_pairs + 1] (k-major pair order, as for cw_forward)    */
+  const int32_t* tab_j_host;     /* host, [num_terms]                                                */
+  const float* tab_c_host;       /* host, [num_terms]                                                */
+  int64_t w_stride, x1_stride, x2_stride, out_stride;
+  int64_t num_edges, num_receivers;
+  int32_t extent, x1_offset, num_paths, num_terms;
+  int32_t w_offset[8];
+  int32_t out_offset[8];
+  int32_t mul_ir;                /* layout of x1 and out, as in cueq_cw_args                         */
+  int32_t reserved;
+} cueq_cw_noalloc_args;
+
+int cueq_b200_cw_forward_noalloc(int group, const cueq_cw_noalloc_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
