@@ -109,6 +109,12 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_forward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_backward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_forward_noalloc.argtypes = [C.c_int, C.POINTER(CwNoAllocArgs), C.c_void_p]
+    L.cueq_b200_u1d_static_find.argtypes = [C.c_char_p]
+    L.cueq_b200_u1d_static_find.restype = C.c_int
+    L.cueq_b200_u1d_static_name.argtypes = [C.c_int]
+    L.cueq_b200_u1d_static_name.restype = C.c_char_p
+    L.cueq_b200_u1d_static_launch.argtypes = [C.c_int, C.c_int64, C.c_int32, C.POINTER(Buffer), C.POINTER(C.c_int32),
+                                              C.POINTER(C.c_int32), C.c_int32, C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     _lib = L

@@ -1,0 +1,135 @@
+"""Throughput of the other benchmark configurations (the headline one is ``bench.py``).
+
+    python -m cuequivariance_b200.bench_configs [--config 0|1|2|4|all] [--steps K]
+
+Prints one JSON line per configuration: device-timed (CUDA events) steps on seeded
+synthetic inputs of the configuration's shapes, with the per-kernel breakdown of the native
+launches.  Config 0: channelwise forward, 65,536 edges / 4,096 nodes / 128x(0e+1o+2e).
+Config 1: symmetric contraction 128x(0e+1o+2e+3o) -> 128x(0e+1o), degree 3, 16,384 atoms, 10
+species, forward + backward.  Config 2: fully connected 64x(0e+1o+2e)^3, batch 32,768, forward +
+backward (interim library-GEMM route).  Config 4: config-3 graph at 65,536 edges, energy =
+sum of the 0e outputs, first derivatives w.r.t. node features / harmonics / weights, then the
+second derivative of their squared norm w.r.t. the same inputs (force-training pattern).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+import cuequivariance_b200 as cb
+from cuequivariance_b200 import profiling
+
+FILTER = ["0e", "1o", "2e", "3o"]
+
+
+def _time(step, steps, warmup=3):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    profiling.reset()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = profiling.launch_count // steps
+    profiling.enable(True)
+    profiling.reset()
+    step()
+    kernels = {k: round(v[1], 4) for k, v in profiling.summary().items()}
+    profiling.enable(False)
+    return ms, launches, kernels
+
+
+def config0(steps, dev):
+    tp = cb.ChannelWiseTensorProduct("128x0e+128x1o+128x2e", "0e+1o+2e+3o", FILTER, layout=cb.mul_ir,
+                                     shared_weights=False, internal_weights=False)
+    sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)
+    g = torch.Generator(device=dev).manual_seed(0)
+    E, N = 65536, 4096
+    x1 = torch.randn(N, tp.irreps_in1.dim, generator=g, device=dev)
+    x2 = sh(torch.randn(E, 3, generator=g, device=dev))
+    w = torch.randn(E, tp.weight_numel, generator=g, device=dev)
+    snd = torch.randint(0, N, (E,), generator=g, device=dev, dtype=torch.int32)
+    rcv = torch.randint(0, N, (E,), generator=g, device=dev, dtype=torch.int32)
+    ms, n, k = _time(lambda: tp(x1, x2, w, indices_1=snd, indices_out=rcv, size_out=N), steps)
+    return {"config": 0, "what": "channelwise forward, unsorted receivers", "ms_per_step": ms, "value": E / ms * 1e3, "unit": "edges/s",
+            "gpu_launches": n, "kernels_ms": k}
+
+
+def config1(steps, dev):
+    B = 16384
+    m = cb.SymmetricContraction("128x0e+128x1o+128x2e+128x3o", "128x0e+128x1o", 3, 10, layout=cb.mul_ir, dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(10)
+    x = torch.randn(B, m.irreps_in.dim, generator=g, device=dev, requires_grad=True)
+    sp = torch.randint(0, 10, (B,), generator=g, device=dev)
+    with torch.no_grad():
+        m.weight.copy_(torch.randn(m.weight.shape, generator=g, device=dev) / 29 ** 0.5)
+
+    def step():
+        out = m(x, sp)
+        torch.autograd.grad(out.sum(), [x, m.weight])
+
+    ms, n, k = _time(step, steps)
+    return {"config": 1, "what": "symmetric contraction fwd+bwd", "ms_per_step": ms, "value": B / ms * 1e3, "unit": "atoms/s",
+            "gpu_launches": n, "kernels_ms": k}
+
+
+def config2(steps, dev):
+    s = "64x0e+64x1o+64x2e"
+    B = 32768
+    m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.mul_ir, internal_weights=False, shared_weights=True)
+    g = torch.Generator(device=dev).manual_seed(20)
+    x1 = torch.randn(B, m.irreps_in1.dim, generator=g, device=dev, requires_grad=True)
+    x2 = torch.randn(B, m.irreps_in2.dim, generator=g, device=dev, requires_grad=True)
+    w = (torch.randn(1, m.weight_numel, generator=g, device=dev) / 64.0).requires_grad_(True)
+
+    def step():
+        out = m(x1, x2, w)
+        torch.autograd.grad(out.sum(), [x1, x2, w])
+
+    ms, n, k = _time(step, steps)
+    return {"config": 2, "what": "fully connected fwd+bwd, float32, interim library-GEMM route", "ms_per_step": ms,
+            "value": B / ms * 1e3, "unit": "samples/s", "gpu_launches": n, "kernels_ms": k}
+
+
+def config4(steps, dev, E=65536, N=4096):
+    s1 = "+".join(f"128x{ir}" for ir in FILTER)
+    tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", FILTER, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
+    sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)
+    g = torch.Generator(device=dev).manual_seed(40)
+    x1 = torch.randn(N, tp.irreps_in1.dim, generator=g, device=dev, requires_grad=True)
+    vec = torch.randn(E, 3, generator=g, device=dev, requires_grad=True)
+    w = torch.randn(E, tp.weight_numel, generator=g, device=dev, requires_grad=True)
+    snd = torch.randint(0, N, (E,), generator=g, device=dev, dtype=torch.int32)
+    rcv = torch.sort(torch.randint(0, N, (E,), generator=g, device=dev, dtype=torch.int32)).values
+
+    def step():
+        out = tp(x1, sh(vec), w, indices_1=snd, indices_out=rcv, size_out=N)
+        energy = out[:, :512].sum()
+        gx, gv, gw = torch.autograd.grad(energy, (x1, vec, w), create_graph=True)
+        loss = gv.pow(2).sum()
+        torch.autograd.grad(loss, (x1, vec, w), allow_unused=True)
+
+    ms, n, k = _time(step, steps)
+    return {"config": 4, "what": f"energy -> forces -> force loss gradient (double backward), {E} edges", "ms_per_step": ms,
+            "value": E / ms * 1e3, "unit": "edges/s", "gpu_launches": n, "kernels_ms": k}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="all")
+    ap.add_argument("--steps", type=int, default=5)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    fns = {"0": config0, "1": config1, "2": config2, "4": config4}
+    for key in (fns if a.config == "all" else [a.config]):
+        print(json.dumps(fns[key](a.steps, dev)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

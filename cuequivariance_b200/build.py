@@ -37,7 +37,19 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
+def generate() -> None:
+    """Regenerates csrc/generated/*.cuh (no-op when the text is unchanged)."""
+    import importlib.util
+
+    for name in ("gen_cw_groups", "gen_u1d_static"):
+        spec = importlib.util.spec_from_file_location(name, CSRC / f"{name}.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.main()
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
+    generate()
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

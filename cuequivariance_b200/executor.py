@@ -185,6 +185,8 @@ class Uniform1dProgram:
             prog = Uniform1dProgram(bwd, self.math_dtype, dmap, name=self.name + "_bwd")
             if self._special is not None:
                 prog._special = self._special.derive(requires_gradient, has_cotangent)
+            if prog._special is None:
+                attach_static(prog)
             self._derivatives[key] = prog
         return prog
 
@@ -257,6 +259,59 @@ class Uniform1dProgram:
             _lib.check(
                 _lib.lib().cueq_b200_u1d_launch(self.plan(), tables.data_ptr(), cfg.batch, bufs, nb, C.c_void_p(stream))
             )
+
+
+class StaticKernel:
+    """Routes a program to the kernel generated for its polynomial at build time."""
+
+    def __init__(self, kernel_id: int, name: str):
+        self.kernel_id, self.name = kernel_id, name
+
+    def try_run(self, program: "Uniform1dProgram", cfg: CallConfig, xs):
+        from . import profiling
+
+        if program.math_dtype != torch.float32 or any(x.dtype != torch.float32 for x in xs):
+            return None
+        if any(cfg.layout(b) is not None for b in range(program.num_inputs + program.num_outputs)):
+            return None
+        device = xs[0].device
+        outs = [
+            torch.zeros((spec.rows, program.row_sizes[program.num_inputs + j]), dtype=torch.float32, device=device)
+            if spec.mode != _lib.BATCHED or program.buffer_dim[program.num_inputs + j] == 0
+            else torch.empty((spec.rows, program.row_sizes[program.num_inputs + j]), dtype=torch.float32, device=device)
+            for j, spec in enumerate(cfg.outputs)
+        ]
+        nb = program.num_inputs + program.num_outputs
+        bufs = (_lib.Buffer * nb)()
+        keep = []
+        for b, (t, spec) in enumerate(zip(list(xs) + outs, cfg.inputs + cfg.outputs)):
+            bufs[b].ptr = t.data_ptr() if t.numel() else None
+            bufs[b].rows, bufs[b].mode, bufs[b].dtype = spec.rows, spec.mode, _lib.F32
+            if spec.mode == _lib.INDEXED:
+                idx = spec.index.contiguous()
+                keep.append(idx)
+                bufs[b].index = idx.data_ptr() if idx.numel() else None
+                bufs[b].index_is_64 = 1 if idx.dtype == torch.int64 else 0
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        with torch.cuda.device(device), profiling.kernel(f"u1d_static[{self.name}]"):
+            _lib.check(_lib.lib().cueq_b200_u1d_static_launch(
+                self.kernel_id, cfg.batch, program.extent, bufs, _lib.int32_array(program.buffer_dim),
+                _lib.int32_array(program.buffer_num_segments), nb, stream))
+        return outs
+
+    def derive(self, requires_gradient, has_cotangent):
+        return None  # the derivative program is matched by its own digest
+
+
+def attach_static(program: "Uniform1dProgram") -> None:
+    """Gives ``program`` the build-time kernel of its polynomial if the library has one."""
+    from .static_poly import digest
+
+    if program.math_dtype != torch.float32 or program._special is not None:
+        return
+    kid = _lib.lib().cueq_b200_u1d_static_find(digest(program.flat).encode())
+    if kid >= 0:
+        program._special = StaticKernel(kid, _lib.lib().cueq_b200_u1d_static_name(kid).decode())
 
 
 def make_config(

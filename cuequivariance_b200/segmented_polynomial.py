@@ -117,12 +117,17 @@ class SegmentedPolynomial(nn.Module):
             if self.method == "uniform_1d":
                 prog = Uniform1dProgram(self.polynomial, math_dtype, self.output_dtype_map, self.name)
                 from .channelwise import attach_specialisation
+                from .executor import attach_static
 
                 attach_specialisation(prog)
+                attach_static(prog)
             else:
-                from .fused_tp import FusedTPProgram
+                from .fused_tp import FLATTEN_LIMIT, DenseUVW, FusedTPProgram, flattened_path_count, is_fully_connected
 
-                prog = FusedTPProgram(self.polynomial, math_dtype, self.output_dtype_map, self.name)
+                if is_fully_connected(self.polynomial) and flattened_path_count(self.polynomial) > FLATTEN_LIMIT:
+                    prog = DenseUVW(self.polynomial, self.math_dtype)
+                else:
+                    prog = FusedTPProgram(self.polynomial, math_dtype, self.output_dtype_map, self.name)
             self._programs[math_dtype] = prog
         return prog
 
@@ -167,4 +172,9 @@ class SegmentedPolynomial(nn.Module):
             md = inputs[0].dtype
         else:
             md = torch.float32
-        return evaluate(self._program(md), inputs, input_indices, output_shapes, output_indices, layouts)
+        prog = self._program(md)
+        if not hasattr(prog, "run"):  # composite route (dense uvw): no index support, batch semantics of the inputs
+            if input_indices or output_indices or output_shapes or layouts:
+                raise ValueError("the dense fully connected route takes plain batched (or shared-weight) inputs")
+            return prog(inputs)
+        return evaluate(prog, inputs, input_indices, output_shapes, output_indices, layouts)

@@ -153,6 +153,19 @@ int cueq_b200_cw_group_info(int group, int32_t* d1, int32_t* num_paths, int32_t*
 int cueq_b200_cw_forward(int group, const cueq_cw_args* args, void* stream);
 int cueq_b200_cw_backward(int group, const cueq_cw_args* args, void* stream);
 
+/* ---- kernels written out at build time for known polynomials ---------------------------------
+ *
+ * Same contract as cueq_b200_u1d_launch (float32 only, outputs zero-initialised by the caller,
+ * accumulated with atomics unless batched), for polynomials whose straight-line code was
+ * generated when the library was built - the counterpart of the per-polynomial NVRTC kernels of
+ * the reference's closed op (CHANGELOG.md:38,49).  `digest` identifies the polynomial
+ * (cuequivariance_b200/static_poly.py); _find returns a kernel id or -1. */
+int cueq_b200_u1d_static_find(const char* digest);
+const char* cueq_b200_u1d_static_name(int id);
+int cueq_b200_u1d_static_launch(int id, int64_t batch, int32_t extent, const cueq_buffer* buffers,
+                                const int32_t* buffer_dim, const int32_t* buffer_num_segments,
+                                int32_t num_buffers, void* stream);
+
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *
  * No counterpart in the reference.  cueq_b200_cw_forward expects the caller to keep the CSR row

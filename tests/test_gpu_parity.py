@@ -235,3 +235,26 @@ def test_gather_scatter_indexing_is_exact():
     (ref,) = naive.segmented_polynomial(p, [w, x1, x2], {1: snd}, {0: N}, {0: rcv})
     (got,) = f([w.to(DEV), x1.to(DEV), x2.to(DEV)], {1: snd.to(DEV).int()}, {0: torch.empty(N, 1, device=DEV)}, {0: rcv.to(DEV).int()})
     assert torch.equal(got.cpu(), ref)
+
+
+def test_fully_connected_dense_route_matches_oracle():
+    """Multiplicity 16 puts the fully connected product on the dense (composite) route; it
+    must agree with the CPU oracle like the flattened route does."""
+    from cuequivariance_b200.fused_tp import DenseUVW
+
+    s = "16x0e+16x1o+16x2e"
+    e = D.fully_connected_tensor_product(s, s, s)
+    m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.ir_mul, internal_weights=False, shared_weights=True)
+    assert isinstance(m.f._program(torch.float32), DenseUVW)
+    gen = torch.Generator().manual_seed(2)
+    B = 24
+    x1, x2 = torch.randn(B, m.irreps_in1.dim, generator=gen), torch.randn(B, m.irreps_in2.dim, generator=gen)
+    w = torch.randn(1, m.weight_numel, generator=gen) / 16.0
+    cot = torch.randn(B, m.irreps_out.dim, generator=gen)
+    ref = _derivatives(lambda w_, a, b: naive.segmented_polynomial(e.polynomial, [w_, a, b])[0], [w, x1, x2], cot)
+    got = _derivatives(lambda w_, a, b: m(a, b, w_), [w.to(DEV), x1.to(DEV), x2.to(DEV)], cot.to(DEV))
+    _close(got[0], ref[0], 1e-5, 2e-6, "out")
+    for a, b in zip(got[1], ref[1]):
+        _close(a, b, 1e-4, 2e-5, "grad")
+    for a, b in zip(got[2], ref[2]):
+        _close(a, b, 1e-3, 2e-4, "gradgrad")
