@@ -307,36 +307,64 @@ class _ChannelwiseBase:
         return a, keep
 
 
-class ChannelwiseForward(_ChannelwiseBase):
-    """``try_run`` returns the outputs, or None when the call is outside what the kernels
-    cover (the generic executor then takes it)."""
-
-    def try_run(self, program, cfg, xs):
+    # -- kernel launches shared by the first- and second-order handlers ------------------------
+    def _launch_forward(self, common, csr, mul_ir, w, x1, x2):
         import ctypes as C
 
         import torch
 
         from . import _lib, profiling
 
-        common = self._common(program, cfg, xs, 3)
-        if common is None:
-            return None
         plan = self.plan
-        out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
-        csr = self._csr(cfg.outputs[0], cfg.batch, xs[0].device)
-        if out_mul_ir is None or csr is None or out_mul_ir != common["x1_mul_ir"]:
-            return None
         order, rowptr, nrecv = csr
-        w, x1, x2 = xs
         out = torch.empty((nrecv, plan.row_sizes[3]), dtype=torch.float32, device=w.device)
         tabs = plan.tables_on(w.device)
         stream = C.c_void_p(torch.cuda.current_stream(w.device).cuda_stream)
         with torch.cuda.device(w.device):
             for g, t in zip(plan.groups, tabs):
-                a, _ = self._args(g, t, "fwd_tab", common, order, rowptr, nrecv, out_mul_ir, dict(w=w, x1=x1, x2=x2, out=out))
+                a, _ = self._args(g, t, "fwd_tab", common, order, rowptr, nrecv, mul_ir, dict(w=w, x1=x1, x2=x2, out=out))
                 with profiling.kernel(f"cw_fwd[{g['id']}]", stream):
                     _lib.check(_lib.lib().cueq_b200_cw_forward(g["id"], C.byref(a), stream))
-        return [out]
+        return out
+
+    def _launch_backward(self, common, csr, mul_ir, w, x1, x2, gout, needs):
+        import ctypes as C
+
+        import torch
+
+        from . import _lib, profiling
+
+        plan = self.plan
+        order, rowptr, nrecv = csr
+        dev = w.device
+        gw = torch.empty_like(w) if needs[0] else None
+        gx1 = torch.zeros_like(x1) if needs[1] else None
+        gx2 = torch.zeros_like(x2) if needs[2] else None
+        tabs = plan.tables_on(dev)
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            for g, t in zip(plan.groups, tabs):
+                a, keep = self._args(g, t, "bwd_tab", common, order, rowptr, nrecv, mul_ir,
+                                     dict(w=w, x1=x1, x2=x2, gout=gout, gw=gw, gx1=gx1, gx2=gx2))
+                with profiling.kernel(f"cw_bwd[{g['id']}]", stream):
+                    _lib.check(_lib.lib().cueq_b200_cw_backward(g["id"], C.byref(a), stream))
+                del keep
+        return gw, gx1, gx2
+
+
+class ChannelwiseForward(_ChannelwiseBase):
+    """``try_run`` returns the outputs, or None when the call is outside what the kernels
+    cover (the generic executor then takes it)."""
+
+    def try_run(self, program, cfg, xs):
+        common = self._common(program, cfg, xs, 3)
+        if common is None:
+            return None
+        out_mul_ir = _is_mul_ir(cfg.layout(3), self.plan.out_blocks)
+        csr = self._csr(cfg.outputs[0], cfg.batch, xs[0].device)
+        if out_mul_ir is None or csr is None or out_mul_ir != common["x1_mul_ir"]:
+            return None
+        return [self._launch_forward(common, csr, out_mul_ir, *xs)]
 
     def derive(self, requires_gradient, has_cotangent):
         if not has_cotangent[0]:
@@ -351,47 +379,107 @@ class ChannelwiseBackward(_ChannelwiseBase):
         super().__init__(plan)
         self.needs = needs
 
-    def try_run(self, program, cfg, xs):
-        import ctypes as C
-
-        import torch
-
-        from . import _lib, profiling
-
-        common = self._common(program, cfg, xs, 4)
+    def _check(self, program, cfg, xs, n_in, grad_specs):
+        """Common admission test; ``grad_specs`` = [(output position, input it mirrors)]."""
+        common = self._common(program, cfg, xs, n_in)
         if common is None:
             return None
-        plan = self.plan
-        out_mul_ir = _is_mul_ir(cfg.layout(3), plan.out_blocks)
+        out_mul_ir = _is_mul_ir(cfg.layout(3), self.plan.out_blocks)
         csr = self._csr(cfg.inputs[3], cfg.batch, xs[0].device)
         if out_mul_ir is None or csr is None or out_mul_ir != common["x1_mul_ir"]:
             return None
-        # gradient layouts must mirror the input layouts
-        k = 4
-        for i, need in enumerate(self.needs):
-            if need:
-                if cfg.layout(k) != cfg.layout(i) or cfg.outputs[k - 4].mode != cfg.inputs[i].mode:
-                    return None
-                k += 1
-        order, rowptr, nrecv = csr
-        w, x1, x2, gout = xs
-        dev = w.device
-        gw = torch.empty_like(w) if self.needs[0] else None
-        gx1 = torch.zeros_like(x1) if self.needs[1] else None
-        gx2 = torch.zeros_like(x2) if self.needs[2] else None
-        tabs = plan.tables_on(dev)
-        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-        with torch.cuda.device(dev):
-            for g, t in zip(plan.groups, tabs):
-                a, keep = self._args(g, t, "bwd_tab", common, order, rowptr, nrecv, out_mul_ir,
-                                     dict(w=w, x1=x1, x2=x2, gout=gout, gw=gw, gx1=gx1, gx2=gx2))
-                with profiling.kernel(f"cw_bwd[{g['id']}]", stream):
-                    _lib.check(_lib.lib().cueq_b200_cw_backward(g["id"], C.byref(a), stream))
-                del keep
-        return [t for t, need in zip((gw, gx1, gx2), self.needs) if need]
+        for k, i in grad_specs:  # gradient layouts and addressing must mirror their inputs
+            if cfg.layout(n_in + k) != cfg.layout(i) or cfg.outputs[k].mode != cfg.inputs[i].mode:
+                return None
+            if cfg.outputs[k].index is not cfg.inputs[i].index:
+                return None
+        return common, csr, out_mul_ir
+
+    def try_run(self, program, cfg, xs):
+        wanted = [i for i, n in enumerate(self.needs) if n]
+        ok = self._check(program, cfg, xs, 4, list(enumerate(wanted)))
+        if ok is None:
+            return None
+        common, csr, mul_ir = ok
+        res = self._launch_backward(common, csr, mul_ir, *xs, self.needs)
+        return [t for t, need in zip(res, self.needs) if need]
 
     def derive(self, requires_gradient, has_cotangent):
-        return None  # second derivatives run on the generic executor
+        return ChannelwiseSecondOrder(self.plan, self.needs, tuple(requires_gradient), tuple(has_cotangent))
+
+
+class ChannelwiseSecondOrder(ChannelwiseBackward):
+    """Derivative of the backward call, composed from the same first-order kernels.
+
+    With T(w, x1, x2, g) = <g, F(w, x1, x2)> linear in each argument, the backward call
+    returns the partial derivatives of T; pairing them with cotangents (tw, tx1, tx2) gives
+    L = T(tw, x1, x2, g) + T(w, tx1, x2, g) + T(w, x1, tx2, g), whose gradients are again
+    forward and backward evaluations with one argument replaced by a cotangent:
+        dL/dg  = F(tw, x1, x2) + F(w, tx1, x2) + F(w, x1, tx2)
+        dL/dw  = f_w(tx1, x2, g) + f_w(x1, tx2, g)       (f_w does not depend on w)
+        dL/dx1 = f_x1(tw, x2, g) + f_x1(w, tx2, g)
+        dL/dx2 = f_x2(tw, x1, g) + f_x2(w, tx1, g)
+    Inputs (w, x1, x2, g, cotangents of the first-order outputs that have one); outputs the
+    gradients of the flagged inputs among (w, x1, x2, g)."""
+
+    def __init__(self, plan, first_needs, requires_gradient, has_cotangent):
+        super().__init__(plan, first_needs)
+        self.req = requires_gradient
+        self.has = has_cotangent
+
+    def try_run(self, program, cfg, xs):
+        import torch
+
+        first_outputs = [i for i, n in enumerate(self.needs) if n]           # which of (gw, gx1, gx2) exist
+        cots = {}
+        k = 4
+        for pos, i in enumerate(first_outputs):
+            if self.has[pos]:
+                cots[i] = k
+                k += 1
+        n_in = k
+        if len(xs) != n_in or len(self.req) != 4:
+            return None
+        # cotangents must be addressed like the inputs they pair with
+        for i, b in cots.items():
+            if cfg.layout(b) != cfg.layout(i) or cfg.inputs[b].mode != cfg.inputs[i].mode or cfg.inputs[b].index is not cfg.inputs[i].index:
+                return None
+        wanted = [i for i, r in enumerate(self.req) if r]
+        ok = self._check(program, cfg, xs, n_in, list(enumerate(wanted)))
+        if ok is None:
+            return None
+        common, csr, mul_ir = ok
+        w, x1, x2, g = xs[:4]
+        tw, tx1, tx2 = (xs[cots[i]] if i in cots else None for i in range(3))
+        out = {0: None, 1: None, 2: None, 3: None}
+
+        def add(i, t):
+            if t is not None:
+                out[i] = t if out[i] is None else out[i] + t
+
+        if self.req[3]:
+            for a, b, c in ((tw, x1, x2), (w, tx1, x2), (w, x1, tx2)):
+                if a is not None and b is not None and c is not None:
+                    add(3, self._launch_forward(common, csr, mul_ir, a, b, c))
+        if tx1 is not None and (self.req[0] or self.req[2]):
+            gw_, _, gx2_ = self._launch_backward(common, csr, mul_ir, w, tx1, x2, g, (self.req[0], False, self.req[2]))
+            add(0, gw_), add(2, gx2_)
+        if tx2 is not None and (self.req[0] or self.req[1]):
+            gw_, gx1_, _ = self._launch_backward(common, csr, mul_ir, w, x1, tx2, g, (self.req[0], self.req[1], False))
+            add(0, gw_), add(1, gx1_)
+        if tw is not None and (self.req[1] or self.req[2]):
+            _, gx1_, gx2_ = self._launch_backward(common, csr, mul_ir, tw, x1, x2, g, (False, self.req[1], self.req[2]))
+            add(1, gx1_), add(2, gx2_)
+        res = []
+        for i in wanted:
+            if out[i] is None:
+                ref = (w, x1, x2, g)[i]
+                out[i] = torch.zeros_like(ref)
+            res.append(out[i])
+        return res
+
+    def derive(self, requires_gradient, has_cotangent):
+        return None  # third derivatives run on the generic executor
 
 
 def attach_specialisation(program) -> None:

@@ -146,3 +146,37 @@ def test_linearity_at_scale():
     assert torch.allclose(per_edge.double().sum(0), a.double().sum(0), rtol=1e-6, atol=1e-3)
     # run-to-run reproducibility of the forward (no atomics on that path)
     assert torch.equal(f(w1), a)
+
+
+def test_force_training_chain_float32_kernels_vs_float64_executor():
+    """Config-4 pattern at 65,536 edges: energy = sum of the 0e outputs, forces-like first
+    derivatives, then the gradient of their squared norm (double backward).  The float32
+    specialised kernels (first order + composed second order) are checked against the same
+    chain evaluated in float64 by the generic executor: an independent code path, itself
+    pinned on the reference fixtures and the CPU oracle at small sizes."""
+    s1 = "+".join(f"32x{ir}" for ir in FILTER)
+    E, N = 65536, 4096
+    tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", FILTER, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
+    gen = torch.Generator(device=DEV).manual_seed(44)
+    x1 = torch.randn(N, tp.irreps_in1.dim, generator=gen, device=DEV, dtype=torch.float64)
+    x2 = torch.randn(E, 16, generator=gen, device=DEV, dtype=torch.float64)
+    w = torch.randn(E, tp.weight_numel, generator=gen, device=DEV, dtype=torch.float64)
+    snd = torch.randint(0, N, (E,), generator=gen, device=DEV, dtype=torch.int32)
+    rcv = torch.sort(torch.randint(0, N, (E,), generator=gen, device=DEV, dtype=torch.int32)).values
+
+    def chain(dtype):
+        a, b, c = (t.to(dtype).clone().requires_grad_(True) for t in (x1, x2, w))
+        out = tp(a, b, c, indices_1=snd, indices_out=rcv, size_out=N)
+        energy = out[:, : 4 * 32].sum()
+        ga, gb, gc = torch.autograd.grad(energy, (a, b, c), create_graph=True)
+        loss = gb.pow(2).sum() + 1e-3 * ga.pow(2).sum() + 1e-3 * gc.pow(2).sum()
+        return [out.detach(), ga.detach(), gb.detach(), gc.detach()] + [t.detach() for t in torch.autograd.grad(loss, (a, b, c))]
+
+    profiling.reset()
+    got = chain(torch.float32)
+    assert profiling.launch_count > 0
+    ref = chain(torch.float64)
+    for name, a, b in zip(["out", "gx1", "gx2", "gw", "ggx1", "ggx2", "ggw"], got, ref):
+        scale = max(1.0, float(b.abs().max()))
+        err = float((a.double() - b).abs().max())
+        assert err <= 2e-5 * scale, f"{name}: max abs diff {err:.3e} at scale {scale:.3e}"
