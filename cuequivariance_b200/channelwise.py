@@ -206,7 +206,8 @@ def match_channelwise(polynomial) -> Optional[ChannelwisePlan]:
         if sig not in lib:
             return None
         g = {"id": lib[sig], "x1_off": x1_off[s1], "w_off": [w_off[p[3]] for p in plist],
-             "out_off": [out_off[p[4]] for p in plist], "npath": len(plist), "out_segs": [p[4] for p in plist]}
+             "out_off": [out_off[p[4]] for p in plist], "npath": len(plist), "out_segs": [p[4] for p in plist],
+             "x1_width": x1_op.segments[s1][0] * x1_op.segments[s1][1]}
         for name, major in (("fwd_tab", "k"), ("bwd_tab", "i")):
             start, tj, tc = [0], [], []
             for l1_, l2, l3, _, _, c in plist:
@@ -274,40 +275,88 @@ class _ChannelwiseBase:
             return None, rp, batch
         return None
 
-    def _args(self, g, tabs, which, common, order, rowptr, nrecv, out_mul_ir, tensors):
+    def _args(self, g, tabs, which, common, order, rowptr, nrecv, out_mul_ir, tensors, x1_is_block=False):
+        """``x1_is_block``: tensors['x1'] (and 'gx1') hold only this group's irrep block,
+        ``[rows, extent * d1]`` contiguous, instead of full rows.  The constant part of the
+        argument block is built once per (group, direction) and copied."""
         import ctypes as C
 
         from . import _lib
 
         plan = self.plan
-        a = _lib.CwArgs()
+        cache = g.setdefault("_arg_templates", {})
+        tmpl = cache.get(which)
+        if tmpl is None:
+            t = _lib.CwArgs()
+            t.w_stride, t.x1_stride, t.x2_stride, t.out_stride = plan.row_sizes
+            t.extent = plan.extent
+            t.x1_offset = g["x1_off"]
+            t.num_paths = g["npath"]
+            t.num_terms = g["nterm"]
+            for q in range(g["npath"]):
+                t.w_offset[q] = g["w_off"][q]
+                t.out_offset[q] = g["out_off"][q]
+            keep = None
+            if which == "bwd_tab":
+                keep = (C.c_float * g["nterm"])(*g["bwd_tab"][2])
+                t.bwd_coef = C.cast(keep, C.POINTER(C.c_float))
+            tmpl = (bytes(t), keep)
+            cache[which] = tmpl
+        a = _lib.CwArgs.from_buffer_copy(tmpl[0])
         for k, t in tensors.items():
-            setattr(a, k, t.data_ptr() if t is not None and t.numel() else None)
-        a.senders = common["senders"].data_ptr() if common["senders"] is not None else None
-        a.order = order.data_ptr() if order is not None else None
+            if t is not None and t.numel():
+                setattr(a, k, t.data_ptr())
+        if common["senders"] is not None:
+            a.senders = common["senders"].data_ptr()
+        if order is not None:
+            a.order = order.data_ptr()
         a.rowptr = rowptr.data_ptr()
         ts, tj, tc = tabs[which]
         a.tab_start, a.tab_j, a.tab_c = ts.data_ptr(), tj.data_ptr(), tc.data_ptr()
-        a.w_stride, a.x1_stride, a.x2_stride, a.out_stride = plan.row_sizes
         a.num_receivers = nrecv
-        a.extent = plan.extent
-        a.x1_offset = g["x1_off"]
-        a.num_paths = g["npath"]
-        a.num_terms = g["nterm"]
-        for q in range(g["npath"]):
-            a.w_offset[q] = g["w_off"][q]
-            a.out_offset[q] = g["out_off"][q]
+        if x1_is_block:
+            a.x1_stride = tensors["x1"].shape[1]
+            a.x1_offset = 0
         a.x1_mul_ir = 1 if common["x1_mul_ir"] else 0
         a.out_mul_ir = 1 if out_mul_ir else 0
         a.channels_per_lane = CHANNELS_PER_LANE
-        keep = None
-        if which == "bwd_tab":
-            keep = (C.c_float * g["nterm"])(*g["bwd_tab"][2])
-            a.bwd_coef = C.cast(keep, C.POINTER(C.c_float))
-        return a, keep
-
+        return a, tmpl[1]
 
     # -- kernel launches shared by the first- and second-order handlers ------------------------
+    def launch_forward_group(self, gi, common, csr, mul_ir, w, x1_block, x2, out):
+        """One group of the forward pass with that group's x1 block given separately (used by
+        the multi-GPU path, where blocks arrive one by one)."""
+        import ctypes as C
+
+        import torch
+
+        from . import _lib, profiling
+
+        order, rowptr, nrecv = csr
+        g, t = self.plan.groups[gi], self.plan.tables_on(w.device)[gi]
+        stream = C.c_void_p(torch.cuda.current_stream(w.device).cuda_stream)
+        with torch.cuda.device(w.device):
+            a, _ = self._args(g, t, "fwd_tab", common, order, rowptr, nrecv, mul_ir, dict(w=w, x1=x1_block, x2=x2, out=out), x1_is_block=True)
+            with profiling.kernel(f"cw_fwd[{g['id']}]", stream):
+                _lib.check(_lib.lib().cueq_b200_cw_forward(g["id"], C.byref(a), stream))
+
+    def launch_backward_group(self, gi, common, csr, mul_ir, w, x1_block, x2, gout, gw, gx1_block, gx2):
+        import ctypes as C
+
+        import torch
+
+        from . import _lib, profiling
+
+        order, rowptr, nrecv = csr
+        g, t = self.plan.groups[gi], self.plan.tables_on(w.device)[gi]
+        stream = C.c_void_p(torch.cuda.current_stream(w.device).cuda_stream)
+        with torch.cuda.device(w.device):
+            a, keep = self._args(g, t, "bwd_tab", common, order, rowptr, nrecv, mul_ir,
+                                 dict(w=w, x1=x1_block, x2=x2, gout=gout, gw=gw, gx1=gx1_block, gx2=gx2), x1_is_block=True)
+            with profiling.kernel(f"cw_bwd[{g['id']}]", stream):
+                _lib.check(_lib.lib().cueq_b200_cw_backward(g["id"], C.byref(a), stream))
+            del keep
+
     def _launch_forward(self, common, csr, mul_ir, w, x1, x2):
         import ctypes as C
 

@@ -72,6 +72,75 @@ def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
     return _AllGatherRows.apply(x, group)
 
 
+class _PipelinedShardedChannelwise(torch.autograd.Function):
+    """Sharded channelwise product with the node-feature exchange pipelined against the
+    per-irrep kernel launches.
+
+    Forward : the node features are all-gathered one irrep block at a time (asynchronous NCCL
+              calls, smallest block first); the launch for irrep l only waits for block l, so
+              every transfer but the first hides behind the previous launch.
+    Backward: launches run largest irrep first; as soon as a launch has produced its block of
+              the node-feature gradient, that block's reduce-scatter starts and overlaps the
+              next launch; the last (smallest) block is the only exposed transfer.
+    First-order only (differentiating the result again is not supported on this path)."""
+
+    @staticmethod
+    def forward(ctx, handler, group, x1_local, x2, weight, senders, receivers_local):
+        from . import _lib
+        from .channelwise import _CSR
+
+        plan = handler.plan
+        world = dist.get_world_size(group)
+        n_local = x1_local.shape[0]
+        dev = x1_local.device
+        mul_ir = True
+        common = dict(x1_mul_ir=mul_ir, senders=_CSR.int32(senders))
+        order, rowptr = _CSR.get(receivers_local, n_local)
+        csr = (order, rowptr, n_local)
+        blocks, works = [], []
+        for g in plan.groups:  # irrep blocks in ascending size
+            loc = x1_local[:, g["x1_off"] : g["x1_off"] + g["x1_width"]].contiguous()
+            full = torch.empty((n_local * world, g["x1_width"]), dtype=loc.dtype, device=dev)
+            works.append(dist.all_gather_into_tensor(full, loc, group=group, async_op=True))
+            blocks.append(full)
+        out = torch.empty((n_local, plan.row_sizes[3]), dtype=torch.float32, device=dev)
+        for gi in range(len(plan.groups)):
+            works[gi].wait()
+            handler.launch_forward_group(gi, common, csr, mul_ir, weight, blocks[gi], x2, out)
+        ctx.handler, ctx.group, ctx.common, ctx.csr = handler, group, common, csr
+        ctx.save_for_backward(weight, x2, *blocks)
+        ctx.n_local = n_local
+        del _lib
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gout):
+        handler, group, common, csr = ctx.handler, ctx.group, ctx.common, ctx.csr
+        plan = handler.plan
+        weight, x2, *blocks = ctx.saved_tensors
+        gout = gout.contiguous()
+        need_x1, need_x2, need_w = ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4]
+        gw = torch.empty_like(weight) if need_w else None
+        gx2 = torch.zeros_like(x2) if need_x2 else None
+        pieces, works = {}, []
+        for gi in reversed(range(len(plan.groups))):  # largest block first
+            gblock = torch.zeros_like(blocks[gi]) if need_x1 else None
+            handler.launch_backward_group(gi, common, csr, True, weight, blocks[gi], x2, gout, gw, gblock, gx2)
+            if need_x1:
+                mine = torch.empty((ctx.n_local, gblock.shape[1]), dtype=gblock.dtype, device=gblock.device)
+                works.append(dist.reduce_scatter_tensor(mine, gblock, op=dist.ReduceOp.SUM, group=group, async_op=True))
+                pieces[gi] = mine
+        gx1 = None
+        if need_x1:
+            for wk in works:
+                wk.wait()
+            gx1 = torch.empty((ctx.n_local, plan.row_sizes[1]), dtype=torch.float32, device=gout.device)
+            for gi, g in enumerate(plan.groups):
+                gx1[:, g["x1_off"] : g["x1_off"] + g["x1_width"]] = pieces[gi]
+        return None, None, gx1, gx2, gw, None, None
+
+
 class ReceiverShardedChannelWise(torch.nn.Module):
     """``forward(x1_local, x2, weight, senders, receivers_local)``.
 
@@ -81,12 +150,36 @@ class ReceiverShardedChannelWise(torch.nn.Module):
     rows of the output.  With ``group=None`` (one process) it is the plain fused call.
     """
 
-    def __init__(self, tp: torch.nn.Module, group=None):
+    def __init__(self, tp: torch.nn.Module, group=None, pipelined: bool = True):
         super().__init__()
         self.tp = tp
         self.group = group
+        self.pipelined = pipelined
+
+    def _handler(self, x1_local, x2, weight):
+        """The specialised-kernel handler if the pipelined path applies (float32, mul_ir
+        layouts, per-edge weights, one launch per irrep of x1), else None."""
+        if not self.pipelined or not x1_local.is_cuda or x1_local.dtype != torch.float32:
+            return None
+        if x2.dtype != torch.float32 or weight.dtype != torch.float32 or weight.shape[0] != x2.shape[0]:
+            return None
+        prog = self.tp.f._program(torch.float32)
+        special = getattr(prog, "_special", None)
+        lay = getattr(self.tp, "_layouts", {})
+        if special is None or not hasattr(special, "launch_forward_group") or 1 not in lay or 3 not in lay:
+            return None
+        offs = [g["x1_off"] for g in special.plan.groups]
+        if len(set(offs)) != len(offs):
+            return None
+        return special
 
     def forward(self, x1_local, x2, weight, senders, receivers_local):
         n_local = x1_local.shape[0]
-        x1 = x1_local if self.group is None else all_gather_rows(x1_local, self.group)
+        if self.group is None:
+            return self.tp(x1_local, x2, weight, indices_1=senders, indices_out=receivers_local, size_out=n_local)
+        handler = self._handler(x1_local, x2, weight)
+        if handler is not None:
+            return _PipelinedShardedChannelwise.apply(handler, self.group, x1_local, x2.contiguous(), weight.contiguous(),
+                                                      senders, receivers_local)
+        x1 = all_gather_rows(x1_local, self.group)
         return self.tp(x1, x2, weight, indices_1=senders, indices_out=receivers_local, size_out=n_local)

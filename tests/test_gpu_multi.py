@@ -1,0 +1,75 @@
+"""Two-GPU parity of the receiver-sharded channelwise product (pipelined all-gather /
+reduce-scatter path and the plain path) against the single-GPU call.  Skipped on boxes with
+fewer than two GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import cuequivariance_b200 as cb
+        from cuequivariance_b200.distributed import ReceiverShardedChannelWise, shard_bounds, shard_edges
+
+        s1 = "32x0e+32x1o+32x2e+32x3o"
+        filt = ["0e", "1o", "2e", "3o"]
+        tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", filt, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
+        gen = torch.Generator(device=dev).manual_seed(9)  # same seed on every rank: identical global data
+        E, N = 4000, 64
+        x1 = torch.randn(N, tp.irreps_in1.dim, generator=gen, device=dev)
+        x2 = torch.randn(E, 16, generator=gen, device=dev)
+        w = torch.randn(E, tp.weight_numel, generator=gen, device=dev)
+        snd = torch.randint(0, N, (E,), generator=gen, device=dev, dtype=torch.int32)
+        rcv = torch.sort(torch.randint(0, N, (E,), generator=gen, device=dev, dtype=torch.int32)).values
+        cot = torch.randn(N, tp.irreps_out.dim, generator=gen, device=dev)
+
+        def grads(fn, a, b, c, ct):
+            a, b, c = (t.clone().requires_grad_(True) for t in (a, b, c))
+            out = fn(a, b, c)
+            return [out.detach()] + list(torch.autograd.grad((out * ct).sum(), (a, b, c)))
+
+        ref = grads(lambda a, b, c: tp(a, b, c, indices_1=snd, indices_out=rcv, size_out=N), x1, x2, w, cot)
+        lo, hi = shard_bounds(N, world, rank)
+        e0, e1 = shard_edges(rcv, N, world, rank)
+        ok = True
+        for pipelined in (True, False):
+            op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD, pipelined=pipelined)
+            got = grads(lambda a, b, c: op(a, b, c, snd[e0:e1].contiguous(), (rcv[e0:e1] - lo).contiguous()),
+                        x1[lo:hi], x2[e0:e1], w[e0:e1], cot[lo:hi])
+            want = [ref[0][lo:hi], ref[1][lo:hi], ref[2][e0:e1], ref[3][e0:e1]]
+            for g_, w_ in zip(got, want):
+                scale = max(1.0, float(w_.abs().max()))
+                ok = ok and bool(((g_ - w_).abs() <= 1e-4 * w_.abs() + 2e-5 * scale).all())
+        results[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_receiver_sharded_channelwise_two_gpus():
+    import torch.multiprocessing as mp
+
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world and all(results.values())
