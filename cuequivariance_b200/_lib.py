@@ -54,7 +54,8 @@ class CwArgs(C.Structure):
         ("num_receivers", C.c_int64),
         ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
         ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
-        ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32), ("channels_per_lane", C.c_int32), ("reserved", C.c_int32),
+        ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32), ("channels_per_lane", C.c_int32), ("staging", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -115,6 +116,8 @@ def lib() -> C.CDLL:
     L.cueq_b200_u1d_static_name.restype = C.c_char_p
     L.cueq_b200_u1d_static_launch.argtypes = [C.c_int, C.c_int64, C.c_int32, C.POINTER(Buffer), C.POINTER(C.c_int32),
                                               C.POINTER(C.c_int32), C.c_int32, C.c_void_p]
+    L.cueq_b200_gemm_bf16_tn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                         C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     _lib = L

@@ -102,6 +102,7 @@ class _CsrCache:
 
 
 _CSR = _CsrCache()
+STAGING = 0  # forward kernels: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) signalled on an mbarrier
 CHANNELS_PER_LANE = 0  # 0: the library chooses; 2 or 4 force a variant (used by the tests)
 _IDENTITY_ROWPTR: dict = {}
 
@@ -320,6 +321,7 @@ class _ChannelwiseBase:
         a.x1_mul_ir = 1 if common["x1_mul_ir"] else 0
         a.out_mul_ir = 1 if out_mul_ir else 0
         a.channels_per_lane = CHANNELS_PER_LANE
+        a.staging = STAGING if which == "fwd_tab" else 0
         return a, tmpl[1]
 
     # -- kernel launches shared by the first- and second-order handlers ------------------------

@@ -67,6 +67,7 @@ struct CwParams {
   int w_off[kMaxPaths];     // element offset of each path's weight segment inside a w row
   int out_off[kMaxPaths];   // element offset of each path's output block inside an out row
   int need_gw, need_gx1, need_gx2;
+  int* status;              // nullable: set to 1 if a bounded wait on a bulk copy ran out
 };
 
 template <int C> struct VecT;
@@ -88,6 +89,33 @@ __device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// ---- bulk-copy (TMA) staging ----------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2^20 polls (each poll itself blocks for a hardware time slice),
+// records the failure and lets the kernel run to its end instead of hanging the GPU.
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, int* status) {
+  for (int spin = 0; spin < (1 << 20); ++spin)
+    if (mbar_try_wait(bar, parity)) return;
+  if (status) atomicExch(status, 1);
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 __device__ __forceinline__ void red_add(float* addr, const float (&v)[4]) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
@@ -284,6 +312,128 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const
   }
 }
 
+// ---- forward, staging by bulk copies ----------------------------------------------------------
+//
+// Same arithmetic as cw_fwd_kernel; the rows of the next edge are fetched by the copy engine
+// (cp.async.bulk, one instruction per contiguous piece, issued by one lane) and their arrival
+// is signalled on an mbarrier, instead of one cp.async per lane and piece.  The staged data
+// keep their global layout: for mul_ir the whole [channel][component] block of the gathered
+// row is one contiguous copy.
+template <class G, int C>
+struct SmemBulk {
+  static constexpr int NCH = 32 * C;                                        // channels per warp
+  static constexpr int kBar = 4;                                            // two 64-bit barriers
+  static constexpr int kM = G::NPAIR_PAD;
+  static constexpr int kX2 = 16;
+  static constexpr int kPerStage = kX2 + (G::D1 + G::NPATH) * NCH;
+  static constexpr int kPerWarp = kBar + kM + 2 * kPerStage;
+  static constexpr size_t bytes() { return sizeof(float) * (kWarps * kPerWarp); }
+};
+
+template <class G, int C, bool MUL_IR>
+__device__ __forceinline__ void bulk_issue_edge(const CwParams& p, float* st, unsigned long long* bar, int pos, int c0, int nch) {
+  using S = SmemBulk<G, C>;
+  const int eid = p.order ? __ldg(p.order + pos) : pos;
+  const int snd = p.senders ? __ldg(p.senders + eid) : eid;
+  constexpr unsigned x2_bytes = ((G::NX2 + 3) / 4) * 16;
+  const unsigned row_bytes = (unsigned)nch * 4u;
+  fence_proxy_async();
+  mbar_expect_tx(bar, x2_bytes + row_bytes * (G::D1 + G::NPATH));
+  bulk_g2s(st, p.x2 + (int64_t)eid * p.x2_stride, x2_bytes, bar);
+  float* xs = st + S::kX2;
+  const float* xrow = p.x1 + (int64_t)snd * p.x1_stride + p.x1_off;
+  if (MUL_IR) {
+    bulk_g2s(xs, xrow + (int64_t)c0 * G::D1, row_bytes * G::D1, bar);
+  } else {
+#pragma unroll
+    for (int i = 0; i < G::D1; ++i) bulk_g2s(xs + i * S::NCH, xrow + (int64_t)i * p.extent + c0, row_bytes, bar);
+  }
+  float* ws = xs + G::D1 * S::NCH;
+  const float* wrow = p.w + (int64_t)eid * p.w_stride + c0;
+#pragma unroll
+  for (int q = 0; q < G::NPATH; ++q) bulk_g2s(ws + q * S::NCH, wrow + p.w_off[q], row_bytes, bar);
+}
+
+template <class G, int C, int P>
+struct FwdPathsBulk {
+  __device__ __forceinline__ static void run(const float (&X)[G::D1][C], const float* ws, int lane, const float* M,
+                                             float (&acc)[G::SUMD3][C]) {
+    float W[C];
+    to_array(*reinterpret_cast<const Vec<C>*>(ws + P * (32 * C) + C * lane), W);
+    G::template fwd_path<P, C>(X, W, M, acc);
+    if constexpr (P + 1 < G::NPATH) FwdPathsBulk<G, C, P + 1>::run(X, ws, lane, M, acc);
+  }
+};
+
+template <class G, int C, bool MUL_IR>
+__global__ void __launch_bounds__(kWarps * 32, C == 2 ? CW_MINBLOCKS : 2) cw_fwd_bulk_kernel(const __grid_constant__ CwParams p) {
+  extern __shared__ __align__(16) float smem[];
+  using S = SmemBulk<G, C>;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* mine = smem + warp * S::kPerWarp;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(mine);
+  float* Msm = mine + S::kBar;
+  float* stages = Msm + S::kM;
+  const int c0 = blockIdx.y * S::NCH;
+  const int ch = c0 + C * lane;
+  const bool active = ch < p.extent;
+  const int nch = min(S::NCH, p.extent - c0);
+  MTerms<G> mt;
+  mt.load(p, lane);
+  if (lane == 0) {
+    mbar_init(bars + 0, 1);
+    mbar_init(bars + 1, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+  unsigned it = 0;  // edges consumed by this warp so far: stage = it & 1, parity = (it >> 1) & 1
+
+  const int total_warps = gridDim.x * kWarps;
+  for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
+    const int beg = __ldg(p.rowptr + n), end = __ldg(p.rowptr + n + 1);
+    float acc[G::SUMD3][C];
+#pragma unroll
+    for (int a = 0; a < G::SUMD3; ++a)
+#pragma unroll
+      for (int c = 0; c < C; ++c) acc[a][c] = 0.f;
+    if (beg < end && lane == 0) bulk_issue_edge<G, C, MUL_IR>(p, stages + (it & 1) * S::kPerStage, bars + (it & 1), beg, c0, nch);
+    for (int pos = beg; pos < end; ++pos, ++it) {
+      const unsigned s = it & 1;
+      float* st = stages + s * S::kPerStage;
+      if (pos + 1 < end && lane == 0)
+        bulk_issue_edge<G, C, MUL_IR>(p, stages + (s ^ 1) * S::kPerStage, bars + (s ^ 1), pos + 1, c0, nch);
+      mbar_wait(bars + s, (it >> 1) & 1, p.status);
+      mt.compute(Msm, st, lane);
+      __syncwarp();
+      if (active) {
+        const float* xs = st + S::kX2;
+        float X[G::D1][C];
+        if (MUL_IR) {
+          float f[G::D1 * C];
+          const Vec<C>* src = reinterpret_cast<const Vec<C>*>(xs + (int64_t)C * lane * G::D1);
+#pragma unroll
+          for (int t = 0; t < G::D1; ++t) {
+            float a[C];
+            to_array(src[t], a);
+#pragma unroll
+            for (int c = 0; c < C; ++c) f[C * t + c] = a[c];
+          }
+#pragma unroll
+          for (int i = 0; i < G::D1; ++i)
+#pragma unroll
+            for (int c = 0; c < C; ++c) X[i][c] = f[c * G::D1 + i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < G::D1; ++i) to_array(*reinterpret_cast<const Vec<C>*>(xs + i * S::NCH + C * lane), X[i]);
+        }
+        FwdPathsBulk<G, C, 0>::run(X, xs + G::D1 * S::NCH, lane, Msm, acc);
+      }
+      __syncwarp();
+    }
+    if (active) StoreOut<G, C, 0, MUL_IR>::run(p.out + (int64_t)n * p.out_stride, p, ch, acc);
+  }
+}
+
 // ---- backward ---------------------------------------------------------------------------------
 template <class G, int C, int P, bool MUL_IR>
 struct BwdPaths {
@@ -392,6 +542,7 @@ struct GroupEntry {
   int d1, npath, npair, nterm, sumd3, nx2;
   int (*fwd)(const CwParams&, int, int, cudaStream_t);
   int (*bwd)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
+  int (*fwd_bulk)(const CwParams&, int, int, cudaStream_t);
 };
 
 int grid_x(int num_receivers) {
@@ -414,10 +565,30 @@ int launch_fwd_t(const CwParams& p, cudaStream_t st) {
   return 0;
 }
 
+template <class G, int C, bool A>
+int launch_fwd_bulk_t(const CwParams& p, cudaStream_t st) {
+  const size_t smem = SmemBulk<G, C>::bytes();
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_fwd_bulk_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
+  cw_fwd_bulk_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 template <class G>
 int launch_fwd(const CwParams& p, int mul_ir, int cpl, cudaStream_t st) {
   if (cpl == 2) return mul_ir ? launch_fwd_t<G, 2, true>(p, st) : launch_fwd_t<G, 2, false>(p, st);
   return mul_ir ? launch_fwd_t<G, 4, true>(p, st) : launch_fwd_t<G, 4, false>(p, st);
+}
+
+template <class G>
+int launch_fwd_bulk(const CwParams& p, int mul_ir, int cpl, cudaStream_t st) {
+  if (cpl == 2) return mul_ir ? launch_fwd_bulk_t<G, 2, true>(p, st) : launch_fwd_bulk_t<G, 2, false>(p, st);
+  return mul_ir ? launch_fwd_bulk_t<G, 4, true>(p, st) : launch_fwd_bulk_t<G, 4, false>(p, st);
 }
 
 template <class G, int C, bool A>
@@ -440,7 +611,7 @@ int launch_bwd(const CwParams& p, const CwCoef& coef, int mul_ir, int cpl, cudaS
   return mul_ir ? launch_bwd_t<G, 4, true>(p, coef, st) : launch_bwd_t<G, 4, false>(p, coef, st);
 }
 
-#define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, &launch_fwd<G>, &launch_bwd<G>},
+#define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, &launch_fwd<G>, &launch_bwd<G>, &launch_fwd_bulk<G>},
 const GroupEntry kGroups[] = {CW_FOR_EACH_GROUP(CW_ENTRY)};
 constexpr int kNumGroups = sizeof(kGroups) / sizeof(kGroups[0]);
 
@@ -453,6 +624,7 @@ int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p) {
   if (!a) return cueq::fail("channelwise: null arguments");
   if (a->extent < 4 || a->extent % 4) return cueq::fail("channelwise: extent %d must be a positive multiple of 4", a->extent);
   if (a->x1_mul_ir != a->out_mul_ir) return cueq::fail("channelwise: x1 and out must use the same layout");
+  if (a->staging != 0 && a->staging != 1) return cueq::fail("channelwise: staging must be 0 (cp.async) or 1 (bulk copy)");
   if (a->channels_per_lane != 0 && a->channels_per_lane != 2 && a->channels_per_lane != 4)
     return cueq::fail("channelwise: channels_per_lane must be 0 (auto), 2 or 4");
   if (a->num_paths != g.npath) return cueq::fail("channelwise: group has %d paths, got %d", g.npath, a->num_paths);
@@ -501,6 +673,8 @@ extern "C" int cueq_b200_cw_forward(int g, const cueq_cw_args* a, void* stream) 
   if (int rc = fill_params(a, kGroups[g], p)) return rc;
   if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise forward: null tensor");
   if (p.num_receivers == 0) return 0;
+  p.status = reinterpret_cast<int*>(a->status);
+  if (a->staging == 1) return kGroups[g].fwd_bulk(p, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
   return kGroups[g].fwd(p, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -1,0 +1,234 @@
+// Tensor-core GEMM for the dense ("uvw") contractions: C[M,N] (+)= A[M,K] * B[N,K]^T with
+// bf16 operands (both K-major) and float32 accumulation, written directly against the
+// Blackwell tensor-core interface:
+//   * operand tiles are brought into 128-byte-swizzled shared memory by TMA
+//     (cp.async.bulk.tensor.2d) and their arrival is signalled on mbarriers;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x 64 x 16 per
+//     instruction) with the accumulator in tensor memory (TMEM); tcgen05.commit releases a
+//     pipeline stage when the MMAs that read it have finished;
+//   * four epilogue warps read the accumulator back with tcgen05.ld and store the rows.
+// Takes the place of the closed FusedTensorProductOp4 kernel's dense contraction
+// (cuequivariance_torch/primitives/segmented_polynomial_fused_tp.py:51-72) once the coupled
+// operand has been formed.  Every wait is bounded: on timeout the kernel records a status
+// word, still frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 64;       // tile; BK bf16 = 128 bytes = one swizzle row
+constexpr int kStagesTc = 4;
+constexpr int kTileA = BM * BK * 2, kTileB = BN * BK * 2;
+constexpr int kStageBytes = kTileA + kTileB;
+constexpr int kThreads = 192;                   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kSpin = 1 << 22;
+
+__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(unsigned long long* b, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(unsigned long long* b, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(unsigned long long* b, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// returns false (and records it) if the barrier did not flip within the spin budget
+// (non-blocking polls with a short sleep: at most a few tenths of a second in total)
+__device__ __forceinline__ bool bar_wait(unsigned long long* b, unsigned parity, int* status) {
+  for (int i = 0; i < kSpin; ++i) {
+    if (bar_try(b, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  if (status) atomicExch(status, 2);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
+  // K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart; version 1 (Blackwell)
+  const unsigned long long addr = (s32(p) & 0x3FFFFu) >> 4;
+  return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+               ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+
+struct GemmParams {
+  float* C;
+  int64_t ldc;
+  int M, N, K;
+  int accumulate;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b,
+                                                               const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + kStagesTc * kStageBytes);
+  unsigned long long* empty = full + kStagesTc;
+  unsigned long long* acc_ready = empty + kStagesTc;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int num_kb = p.K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesTc; ++s) { bar_init(full + s, 1); bar_init(empty + s, 1); }
+    bar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM: 64 columns x 128 lanes of float32 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(64u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStagesTc;
+        if (!bar_wait(empty + s, ((kb / kStagesTc) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(full + s, kStageBytes);
+        unsigned char* a = smem + s * kStageBytes;
+        tma_load_2d(a, &map_a, kb * BK, m0, full + s);
+        tma_load_2d(a + kTileA, &map_b, kb * BK, n0, full + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kStagesTc;
+        ok = bar_wait(full + s, (kb / kStagesTc) & 1, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned long long da = smem_desc(smem + s * kStageBytes);
+        const unsigned long long db = smem_desc(smem + s * kStageBytes + kTileA);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk)  // 16 bf16 = 32 bytes = 2 descriptor units along K
+          umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+        umma_commit(empty + s);  // frees the stage once these MMAs have read it
+      }
+      umma_commit(acc_ready);
+    }
+  } else {
+    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. 32*(w%4)+31
+    const int q = warp & 3;
+    const bool ok = bar_wait(acc_ready, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int row = m0 + q * 32 + lane;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      unsigned v[32];
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + half * 32;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                   "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                   "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                     "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                     "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                     "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      if (ok && row < p.M) {
+        float* dst = p.C + (int64_t)row * p.ldc + n0 + half * 32;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+          if (p.accumulate) {
+            const float4 old = *reinterpret_cast<const float4*>(dst + c);
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *reinterpret_cast<float4*>(dst + c) = o;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(64u) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cueq::fail("gemm: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cueq::fail("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                      int64_t ldb, int64_t ldc, int32_t accumulate, void* status, void* stream) {
+  if (!A || !B || !C) return cueq::fail("gemm: null operand");
+  if (M <= 0 || N <= 0 || K <= 0) return cueq::fail("gemm: empty problem");
+  if (N % BN || K % BK) return cueq::fail("gemm: N must be a multiple of %d and K of %d (got N=%lld K=%lld)", BN, BK, (long long)N, (long long)K);
+  if ((lda % 8) || (ldb % 8) || (ldc % 4)) return cueq::fail("gemm: leading dimensions must keep rows 16-byte aligned");
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return cueq::fail("gemm: operands must be 16-byte aligned");
+  if (M > 2147483647LL || K > 2147483647LL) return cueq::fail("gemm: dimension too large");
+  CUtensorMap ma, mb;
+  if (int rc = make_map(&ma, A, M, K, lda, BM)) return rc;
+  if (int rc = make_map(&mb, B, N, K, ldb, BN)) return rc;
+  GemmParams p;
+  p.C = C; p.ldc = ldc; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.accumulate = accumulate; p.status = reinterpret_cast<int*>(status);
+  const size_t smem = kStagesTc * kStageBytes + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)(N / BN));
+  gemm_bf16_tn_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -93,21 +93,23 @@ def emit_group(l1: int, paths) -> str:
         q0 = pair_off[p]
         A(f"      float m[{len(pat)}];")
         A(f"      cw_load_m<{q0}, {len(pat)}>(M, m);")
-        by_k: dict[int, list] = {}
+        # i-major emission: consecutive multiply-adds go to different accumulators t[k], so that
+        # the chains over i of the d3 outputs interleave instead of running one after the other
+        A(f"      float t[{d3}][C];")
+        seen_k = set()
+        by_i2: dict[int, list] = {}
         for q, (i, k, _) in enumerate(pat):
-            by_k.setdefault(k, []).append((q, i))
+            by_i2.setdefault(i, []).append((q, k))
+        for i in sorted(by_i2):
+            for q, k in by_i2[i]:
+                if k in seen_k:
+                    A(f"      CW_FMA4(t[{k}], m[{q}], X[{i}]);")
+                else:
+                    seen_k.add(k)
+                    A(f"      CW_MUL4(t[{k}], m[{q}], X[{i}]);")
         for k in range(d3):
-            terms = by_k.get(k, [])
-            if not terms:
-                continue
-            A("      {")
-            A("        float t[C];")
-            q, i = terms[0]
-            A(f"        CW_MUL4(t, m[{q}], X[{i}]);")
-            for q, i in terms[1:]:
-                A(f"        CW_FMA4(t, m[{q}], X[{i}]);")
-            A(f"        CW_FMAV4(acc[{out_off[p] + k}], W, t);")
-            A("      }")
+            if k in seen_k:
+                A(f"      CW_FMAV4(acc[{out_off[p] + k}], W, t[{k}]);")
         A("    }")
     A("  }")
 

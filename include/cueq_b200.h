@@ -144,7 +144,8 @@ typedef struct {
   int32_t x1_mul_ir;    /* 1: x1/gx1 blocks are [channel][component], 0: [component][channel]   */
   int32_t out_mul_ir;   /* same for out/gout (must equal x1_mul_ir)                             */
   int32_t channels_per_lane; /* 0: automatic; 2 or 4: channels owned by one thread              */
-  int32_t reserved;
+  int32_t staging;      /* forward only: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) + mbarrier */
+  void* status;         /* nullable device int32: set to 1 if a bounded wait on a bulk copy ran out */
 } cueq_cw_args;
 
 int cueq_b200_cw_num_groups(void);
@@ -165,6 +166,18 @@ const char* cueq_b200_u1d_static_name(int id);
 int cueq_b200_u1d_static_launch(int id, int64_t batch, int32_t extent, const cueq_buffer* buffers,
                                 const int32_t* buffer_dim, const int32_t* buffer_num_segments,
                                 int32_t num_buffers, void* stream);
+
+/* ---- tensor-core GEMM for the dense (uvw) contractions --------------------------------------
+ *
+ * C[M,N] (+)= A[M,K] * B[N,K]^T, bf16 operands (both K-major, leading dimensions lda/ldb in
+ * elements), float32 result, written with TMA + tcgen05.mma + TMEM.  Stands where the closed
+ * FusedTensorProductOp4 kernel does its dense contraction
+ * (cuequivariance_torch/primitives/segmented_polynomial_fused_tp.py:51-72).  N must be a
+ * multiple of 64 and K of 64.  `status` (nullable device int32) is set to 2 if an internal
+ * bounded wait ran out (the result is then invalid). */
+int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldb, int64_t ldc, int32_t accumulate, void* status,
+                           void* stream);
 
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *
