@@ -72,6 +72,28 @@ class CwNoAllocArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("group_stride", C.c_int64),
+        ("rows_per_group", C.c_int32), ("accumulate", C.c_int32), ("out_bf16", C.c_int32),
+        ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32), ("reserved", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
+class FctpArgs(C.Structure):
+    _fields_ = [
+        ("x1", C.c_void_p), ("x2", C.c_void_p), ("z", C.c_void_p), ("gx1", C.c_void_p), ("gx2", C.c_void_p),
+        ("cg", C.POINTER(C.c_float)),
+        ("ld1", C.c_int64), ("ld2", C.c_int64), ("batch", C.c_int64),
+        ("off1", C.c_int32), ("off2", C.c_int32),
+        ("d1", C.c_int32), ("d2", C.c_int32), ("d3", C.c_int32), ("U", C.c_int32), ("V", C.c_int32),
+        ("x_dtype", C.c_int32), ("z_dtype", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -118,6 +140,9 @@ def lib() -> C.CDLL:
                                               C.POINTER(C.c_int32), C.c_int32, C.c_void_p]
     L.cueq_b200_gemm_bf16_tn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
+    L.cueq_b200_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+    L.cueq_b200_fctp_build_z.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
+    L.cueq_b200_fctp_consume_gz.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     _lib = L

@@ -1,0 +1,208 @@
+// Fully connected ("uvw") tensor product: the CUDA-core kernels around the tensor-core GEMM.
+//
+// For one path (l1, l2, l3) of ``uvw,iu,jv,kw+ijk`` (descriptor:
+// cuequivariance/group_theory/descriptors/irreps_tp.py:22-91) with coupling tensor C[i,j,k]:
+//   build   : Z[(z,k), (u,v)] = sum_ij C[i,j,k] x1[z,i,u] x2[z,j,v]         (bf16, GEMM operand)
+//   GEMMs   : out[(z,k), w] += Z W;   gW = Z^T gout;   gZ = gout W^T          (gemm_tc.cu)
+//   consume : gx1[z,i,u] += sum_jkv C[i,j,k] gZ[(z,k),(u,v)] x2[z,j,v]
+//             gx2[z,j,v] += sum_iku C[i,j,k] gZ[(z,k),(u,v)] x1[z,i,u]
+// Both kernels first contract the coupling tensor with one operand per sample
+// (T[k,i,v] = sum_j C x2[j,v], S[k,j,u] = sum_i C x1[i,u]; a few hundred values kept in shared
+// memory), so the per-element work on the big (u,v) axis is d1 (or d1+d2) multiply-adds instead
+// of the number of non-zero couplings.  One CTA per sample; lanes run along v, so every access
+// to Z / gZ is a contiguous 128-byte row segment.
+#include <cuda_bf16.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxD = 7;            // irrep dimension up to l = 3
+constexpr int kThreadsF = 256;
+
+struct FctpParams {
+  const void* x1;
+  const void* x2;
+  void* z;            // build: bf16 output; consume: gZ input
+  float* gx1;
+  float* gx2;
+  int64_t ld1, ld2;   // row pitches of x1 / x2 (and gx1 / gx2) in elements
+  int64_t batch;
+  int off1, off2;     // element offsets of the path's segments inside a row
+  int d1, d2, d3, U, V;
+  int z_is_bf16;      // consume: element type of gZ
+  float cg[kMaxD * kMaxD * kMaxD];  // C[i][j][k], row-major, already scaled by the path normalisation
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, int64_t i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, int64_t i) { return __ldg(p + i); }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+
+// shared: xs1[d1*U], xs2[d2*V], T[d3*d1*V], S[d3*d2*U]
+template <typename TX>
+__device__ __forceinline__ void load_sample(const FctpParams& p, int64_t z, float* xs1, float* xs2) {
+  const TX* r1 = reinterpret_cast<const TX*>(p.x1) + z * p.ld1 + p.off1;
+  const TX* r2 = reinterpret_cast<const TX*>(p.x2) + z * p.ld2 + p.off2;
+  for (int t = threadIdx.x; t < p.d1 * p.U; t += blockDim.x) xs1[t] = ldf<TX>(r1, t);
+  for (int t = threadIdx.x; t < p.d2 * p.V; t += blockDim.x) xs2[t] = ldf<TX>(r2, t);
+}
+
+__device__ __forceinline__ void contract_T(const FctpParams& p, const float* xs2, float* T) {
+  // T[(k*d1 + i)*V + v] = sum_j C[i,j,k] x2[j,v]
+  for (int t = threadIdx.x; t < p.d3 * p.d1 * p.V; t += blockDim.x) {
+    const int v = t % p.V, ki = t / p.V, i = ki % p.d1, k = ki / p.d1;
+    float acc = 0.f;
+    for (int j = 0; j < p.d2; ++j) acc = fmaf(p.cg[(i * p.d2 + j) * p.d3 + k], xs2[j * p.V + v], acc);
+    T[t] = acc;
+  }
+}
+
+__device__ __forceinline__ void contract_S(const FctpParams& p, const float* xs1, float* S) {
+  // S[(k*d2 + j)*U + u] = sum_i C[i,j,k] x1[i,u]
+  for (int t = threadIdx.x; t < p.d3 * p.d2 * p.U; t += blockDim.x) {
+    const int u = t % p.U, kj = t / p.U, j = kj % p.d2, k = kj / p.d2;
+    float acc = 0.f;
+    for (int i = 0; i < p.d1; ++i) acc = fmaf(p.cg[(i * p.d2 + j) * p.d3 + k], xs1[i * p.U + u], acc);
+    S[t] = acc;
+  }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_constant__ FctpParams p) {
+  extern __shared__ float sm[];
+  float* xs1 = sm;
+  float* xs2 = xs1 + p.d1 * p.U;
+  float* T = xs2 + p.d2 * p.V;
+  __nv_bfloat16* Z = reinterpret_cast<__nv_bfloat16*>(p.z);
+  const int UV = p.U * p.V;
+  for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
+    __syncthreads();
+    load_sample<TX>(p, z, xs1, xs2);
+    __syncthreads();
+    contract_T(p, xs2, T);
+    __syncthreads();
+    // threads: v fastest; each thread owns one v (pairs of v for the packed store) and strides over u
+    const int vpairs = p.V / 2;
+    for (int k = 0; k < p.d3; ++k) {
+      __nv_bfloat16* zrow = Z + (z * p.d3 + k) * (int64_t)UV;
+      for (int t = threadIdx.x; t < p.U * vpairs; t += blockDim.x) {
+        const int vp = t % vpairs, u = t / vpairs;
+        float a0 = 0.f, a1 = 0.f;
+        for (int i = 0; i < p.d1; ++i) {
+          const float xi = xs1[i * p.U + u];
+          const float2 tt = *reinterpret_cast<const float2*>(T + (k * p.d1 + i) * p.V + 2 * vp);
+          a0 = fmaf(tt.x, xi, a0);
+          a1 = fmaf(tt.y, xi, a1);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(zrow + u * p.V + 2 * vp) = __floats2bfloat162_rn(a0, a1);
+      }
+    }
+  }
+}
+
+template <typename TX, typename TZ>
+__global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid_constant__ FctpParams p) {
+  extern __shared__ float sm[];
+  float* xs1 = sm;
+  float* xs2 = xs1 + p.d1 * p.U;
+  float* T = xs2 + p.d2 * p.V;
+  float* S = T + p.d3 * p.d1 * p.V;
+  float* g2 = S + p.d3 * p.d2 * p.U;   // [d2*V] block-level accumulator of gx2
+  const TZ* GZ = reinterpret_cast<const TZ*>(p.z);
+  const int UV = p.U * p.V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
+    __syncthreads();
+    load_sample<TX>(p, z, xs1, xs2);
+    for (int t = threadIdx.x; t < p.d2 * p.V; t += blockDim.x) g2[t] = 0.f;
+    __syncthreads();
+    contract_T(p, xs2, T);
+    contract_S(p, xs1, S);
+    __syncthreads();
+    // a warp owns rows u = warp, warp + nwarps, ...; lanes run along v
+    for (int u = warp; u < p.U; u += nwarps) {
+      float a1[kMaxD];
+#pragma unroll
+      for (int i = 0; i < kMaxD; ++i) a1[i] = 0.f;
+      for (int v = lane; v < p.V; v += 32) {
+        float a2[kMaxD];
+#pragma unroll
+        for (int j = 0; j < kMaxD; ++j) a2[j] = 0.f;
+        for (int k = 0; k < p.d3; ++k) {
+          const float g = ldf<TZ>(GZ, (z * p.d3 + k) * (int64_t)UV + u * p.V + v);
+#pragma unroll
+          for (int i = 0; i < kMaxD; ++i)
+            if (i < p.d1) a1[i] = fmaf(g, T[(k * p.d1 + i) * p.V + v], a1[i]);
+#pragma unroll
+          for (int j = 0; j < kMaxD; ++j)
+            if (j < p.d2) a2[j] = fmaf(g, S[(k * p.d2 + j) * p.U + u], a2[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxD; ++j)
+          if (j < p.d2) atomicAdd(g2 + j * p.V + v, a2[j]);
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxD; ++i) {
+        if (i < p.d1) {
+          const float tot = cueq::warp_sum(a1[i]);
+          if (lane == 0 && p.gx1) p.gx1[z * p.ld1 + p.off1 + i * p.U + u] += tot;
+        }
+      }
+    }
+    __syncthreads();
+    if (p.gx2)
+      for (int t = threadIdx.x; t < p.d2 * p.V; t += blockDim.x) p.gx2[z * p.ld2 + p.off2 + t] += g2[t];
+  }
+}
+
+int fill(const cueq_fctp_args* a, FctpParams& p) {
+  if (!a) return cueq::fail("fctp: null arguments");
+  if (a->d1 < 1 || a->d1 > kMaxD || a->d2 < 1 || a->d2 > kMaxD || a->d3 < 1 || a->d3 > kMaxD)
+    return cueq::fail("fctp: irrep dimensions must be in 1..%d", kMaxD);
+  if (a->U < 1 || a->V < 2 || (a->V & 1)) return cueq::fail("fctp: V must be even and U positive");
+  if (!a->x1 || !a->x2 || !a->z || !a->cg) return cueq::fail("fctp: null tensor");
+  if (a->batch < 0) return cueq::fail("fctp: negative batch");
+  std::memset(&p, 0, sizeof(p));
+  p.x1 = a->x1; p.x2 = a->x2; p.z = a->z; p.gx1 = (float*)a->gx1; p.gx2 = (float*)a->gx2;
+  p.ld1 = a->ld1; p.ld2 = a->ld2; p.batch = a->batch; p.off1 = a->off1; p.off2 = a->off2;
+  p.d1 = a->d1; p.d2 = a->d2; p.d3 = a->d3; p.U = a->U; p.V = a->V; p.z_is_bf16 = a->z_dtype == CUEQ_BF16;
+  for (int t = 0; t < a->d1 * a->d2 * a->d3; ++t) p.cg[t] = a->cg[t];
+  return 0;
+}
+
+unsigned grid_for(int64_t batch) { return (unsigned)(batch < 148 * 16 ? (batch < 1 ? 1 : batch) : 148 * 16); }
+
+}  // namespace
+
+extern "C" int cueq_b200_fctp_build_z(const cueq_fctp_args* a, void* stream) {
+  FctpParams p;
+  if (int rc = fill(a, p)) return rc;
+  if (p.batch == 0) return 0;
+  if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
+  const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a->x_dtype == CUEQ_F32) fctp_build_z_kernel<float><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  else fctp_build_z_kernel<__nv_bfloat16><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int cueq_b200_fctp_consume_gz(const cueq_fctp_args* a, void* stream) {
+  FctpParams p;
+  if (int rc = fill(a, p)) return rc;
+  if (p.batch == 0) return 0;
+  if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
+  if (a->z_dtype != CUEQ_F32 && a->z_dtype != CUEQ_BF16) return cueq::fail("fctp: gZ must be float32 or bfloat16");
+  const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V + p.d3 * p.d2 * p.U + p.d2 * p.V);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(p.batch);
+  const bool xb = a->x_dtype == CUEQ_BF16, zb = a->z_dtype == CUEQ_BF16;
+  if (!xb && !zb) fctp_consume_gz_kernel<float, float><<<grid, kThreadsF, smem, st>>>(p);
+  else if (!xb && zb) fctp_consume_gz_kernel<float, __nv_bfloat16><<<grid, kThreadsF, smem, st>>>(p);
+  else if (xb && !zb) fctp_consume_gz_kernel<__nv_bfloat16, float><<<grid, kThreadsF, smem, st>>>(p);
+  else fctp_consume_gz_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreadsF, smem, st>>>(p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -60,6 +60,13 @@ __device__ __forceinline__ unsigned long long smem_desc(const void* p) {
   const unsigned long long addr = (s32(p) & 0x3FFFFu) >> 4;
   return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
+__device__ __forceinline__ unsigned long long smem_desc_mn(const void* p) {
+  // MN-major, 128-byte swizzle: the tile is stored as blocks of [64 K-rows][64 elements along M/N]
+  // (8 KiB each, rows of 128 bytes); groups of 8 K-rows are 1024 bytes apart (stride offset),
+  // consecutive 64-element blocks along M/N are 8192 bytes apart (leading offset)
+  const unsigned long long addr = (s32(p) & 0x3FFFFu) >> 4;
+  return addr | ((8192ull >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
 __device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
@@ -70,10 +77,14 @@ __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
 }
 
 struct GemmParams {
-  float* C;
-  int64_t ldc;
+  void* C;
+  int64_t ldc;          // elements between consecutive rows of one group
+  int64_t group_stride; // elements between consecutive groups of rows
+  int rows_per_group;   // row r lives at (r / rows_per_group) * group_stride + (r % rows_per_group) * ldc
   int M, N, K;
   int accumulate;
+  int out_bf16;         // 1: C is bf16 (no accumulation), 0: float32
+  int a_mn_major, b_mn_major;  // 1: the operand is stored [K][M or N] (M/N contiguous) instead of [M or N][K]
   int* status;
 };
 
@@ -113,25 +124,35 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
         if (!bar_wait(empty + s, ((kb / kStagesTc) & 1) ^ 1, p.status)) break;
         bar_expect_tx(full + s, kStageBytes);
         unsigned char* a = smem + s * kStageBytes;
-        tma_load_2d(a, &map_a, kb * BK, m0, full + s);
-        tma_load_2d(a + kTileA, &map_b, kb * BK, n0, full + s);
+        if (p.a_mn_major) {
+          tma_load_2d(a, &map_a, m0, kb * BK, full + s);
+          tma_load_2d(a + 8192, &map_a, m0 + 64, kb * BK, full + s);
+        } else {
+          tma_load_2d(a, &map_a, kb * BK, m0, full + s);
+        }
+        if (p.b_mn_major) tma_load_2d(a + kTileA, &map_b, n0, kb * BK, full + s);
+        else tma_load_2d(a + kTileA, &map_b, kb * BK, n0, full + s);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24) |
+                             (p.a_mn_major ? (1u << 15) : 0u) | (p.b_mn_major ? (1u << 16) : 0u);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % kStagesTc;
         ok = bar_wait(full + s, (kb / kStagesTc) & 1, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned long long da = smem_desc(smem + s * kStageBytes);
-        const unsigned long long db = smem_desc(smem + s * kStageBytes + kTileA);
+        const unsigned long long da = p.a_mn_major ? smem_desc_mn(smem + s * kStageBytes) : smem_desc(smem + s * kStageBytes);
+        const unsigned long long db = p.b_mn_major ? smem_desc_mn(smem + s * kStageBytes + kTileA) : smem_desc(smem + s * kStageBytes + kTileA);
+        // one instruction covers 16 elements of K: 32 bytes along a K-major row (2 descriptor
+        // units), or 16 rows of 128 bytes of an MN-major block (128 units)
+        const unsigned long long sa = p.a_mn_major ? 128 : 2, sb = p.b_mn_major ? 128 : 2;
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk)  // 16 bf16 = 32 bytes = 2 descriptor units along K
-          umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < BK / 16; ++kk)
+          umma_bf16(tmem_base, da + sa * kk, db + sb * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
         umma_commit(empty + s);  // frees the stage once these MMAs have read it
       }
       umma_commit(acc_ready);
@@ -156,15 +177,27 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
                    : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
       if (ok && row < p.M) {
-        float* dst = p.C + (int64_t)row * p.ldc + n0 + half * 32;
+        const int64_t roff = (int64_t)(row / p.rows_per_group) * p.group_stride + (int64_t)(row % p.rows_per_group) * p.ldc + n0 + half * 32;
+        if (p.out_bf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + roff;
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-          if (p.accumulate) {
-            const float4 old = *reinterpret_cast<const float4*>(dst + c);
-            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          for (int c = 0; c < 32; c += 8) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * t]), __uint_as_float(v[c + 2 * t + 1]));
+            *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<uint4*>(h);
           }
-          *reinterpret_cast<float4*>(dst + c) = o;
+        } else {
+          float* dst = reinterpret_cast<float*>(p.C) + roff;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+            if (p.accumulate) {
+              const float4 old = *reinterpret_cast<const float4*>(dst + c);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dst + c) = o;
+          }
         }
       }
     }
@@ -192,6 +225,8 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// K-major operand: global [rows][cols = K] with `ld` elements between rows; box = 64 K x box_rows.
+// MN-major operand: global [K][cols = M or N]; box = 64 (M/N) x 64 (K).
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return cueq::fail("gemm: cuTensorMapEncodeTiled is not available from the driver");
@@ -208,19 +243,27 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
 
 }  // namespace
 
-extern "C" int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                                      int64_t ldb, int64_t ldc, int32_t accumulate, void* status, void* stream) {
-  if (!A || !B || !C) return cueq::fail("gemm: null operand");
+extern "C" int cueq_b200_gemm_bf16(const cueq_gemm_args* g, void* stream) {
+  if (!g || !g->A || !g->B || !g->C) return cueq::fail("gemm: null operand");
+  const int64_t M = g->M, N = g->N, K = g->K;
   if (M <= 0 || N <= 0 || K <= 0) return cueq::fail("gemm: empty problem");
   if (N % BN || K % BK) return cueq::fail("gemm: N must be a multiple of %d and K of %d (got N=%lld K=%lld)", BN, BK, (long long)N, (long long)K);
-  if ((lda % 8) || (ldb % 8) || (ldc % 4)) return cueq::fail("gemm: leading dimensions must keep rows 16-byte aligned");
-  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return cueq::fail("gemm: operands must be 16-byte aligned");
+  if (g->a_mn_major && (M % BM)) return cueq::fail("gemm: an MN-major A needs M to be a multiple of %d", BM);
+  if ((g->lda % 8) || (g->ldb % 8) || (g->ldc % 4)) return cueq::fail("gemm: leading dimensions must keep rows 16-byte aligned");
+  if (((uintptr_t)g->A | (uintptr_t)g->B | (uintptr_t)g->C) & 15) return cueq::fail("gemm: operands must be 16-byte aligned");
   if (M > 2147483647LL || K > 2147483647LL) return cueq::fail("gemm: dimension too large");
+  if (g->out_bf16 && g->accumulate) return cueq::fail("gemm: accumulation needs a float32 output");
+  const int rpg = g->rows_per_group > 0 ? g->rows_per_group : 1;
+  if ((g->group_stride % 4) != 0) return cueq::fail("gemm: group stride must be a multiple of 4 elements");
   CUtensorMap ma, mb;
-  if (int rc = make_map(&ma, A, M, K, lda, BM)) return rc;
-  if (int rc = make_map(&mb, B, N, K, ldb, BN)) return rc;
+  // K-major: rows = M (or N), cols = K.  MN-major: rows = K, cols = M (or N).
+  if (int rc = g->a_mn_major ? make_map(&ma, g->A, K, M, g->lda, 64) : make_map(&ma, g->A, M, K, g->lda, BM)) return rc;
+  if (int rc = g->b_mn_major ? make_map(&mb, g->B, K, N, g->ldb, 64) : make_map(&mb, g->B, N, K, g->ldb, BN)) return rc;
   GemmParams p;
-  p.C = C; p.ldc = ldc; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.accumulate = accumulate; p.status = reinterpret_cast<int*>(status);
+  std::memset(&p, 0, sizeof(p));
+  p.C = g->C; p.ldc = g->ldc; p.rows_per_group = rpg; p.group_stride = g->group_stride > 0 ? g->group_stride : (int64_t)rpg * g->ldc;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.accumulate = g->accumulate; p.out_bf16 = g->out_bf16;
+  p.a_mn_major = g->a_mn_major; p.b_mn_major = g->b_mn_major; p.status = reinterpret_cast<int*>(g->status);
   const size_t smem = kStagesTc * kStageBytes + 1024 + 256;
   static bool configured = false;
   if (!configured) {
@@ -231,4 +274,13 @@ extern "C" int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, in
   gemm_bf16_tn_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                      int64_t ldb, int64_t ldc, int32_t accumulate, void* status, void* stream) {
+  cueq_gemm_args g;
+  std::memset(&g, 0, sizeof(g));
+  g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+  g.accumulate = accumulate; g.status = status; g.rows_per_group = 1;
+  return cueq_b200_gemm_bf16(&g, stream);
 }

@@ -10,12 +10,18 @@ Two routes:
   segments, which turns the product into a uniform-1d polynomial for the generic CUDA kernel
   (`FusedTPProgram`);
 * the fully connected pattern ``uvw,iu,jv,kw+ijk`` with shared weights at sizes where that
-  flattening explodes (u*v*nnz paths): INTERIM composite of device-side torch ops
-  (`dense_uvw`): per path the coupled operand ``Z[z,k,(u,v)] = sum_ij C[ijk] x1[z,i,u] x2[z,j,v]``
-  is formed and contracted with the weight block by a library GEMM in float32 (TF32 off), and
-  autograd differentiates the composite.  It exists so that the configuration runs and is
-  checked at full size; the tensor-core kernel that should replace it (weights through TMA,
-  ``Z`` tiles built in shared memory, tcgen05 accumulation in TMEM) is not written yet.
+  flattening explodes (u*v*nnz paths), `DenseUVW`:
+  - bf16/fp16 inputs (or ``options={"tensor_cores": True}``): the tensor-core route.  Per path
+    the coupled operand ``Z[(z,k),(u,v)] = sum_ij C[ijk] x1[z,i,u] x2[z,j,v]`` is written in
+    bf16 by a CUDA-core kernel and contracted with the weight block by this library's
+    TMA + tcgen05 GEMM (float32 accumulation in TMEM); the backward runs two more GEMMs per
+    path (weight gradient with both operands MN-major, so nothing is transposed in memory;
+    gradient of Z) and a kernel that folds the gradient of Z back onto x1 and x2.  First
+    derivatives only.  ``Z`` makes a round trip through HBM; building its tiles directly in
+    shared memory inside the GEMM is the remaining step.
+  - float32/float64 inputs: INTERIM composite of device-side torch ops with a library GEMM in
+    full precision (TF32 off), differentiable to any order; kept because bf16 operands cannot
+    meet the float32 tolerance (a split-precision tensor-core variant is not written yet).
 """
 from __future__ import annotations
 
@@ -63,13 +69,121 @@ def is_fully_connected(poly: Polynomial) -> bool:
     return d.subscripts == "uvw,iu,jv,kw+ijk" and tuple(ope.buffers) == (0, 1, 2, 3)
 
 
-class DenseUVW:
-    """INTERIM composite for ``uvw,iu,jv,kw+ijk`` (see the module docstring)."""
+class _TensorCoreUVW(torch.autograd.Function):
+    """``out = sum_paths Z_p W_p`` on the tcgen05 GEMM; see the module docstring."""
 
-    def __init__(self, polynomial: Polynomial, math_dtype: Optional[torch.dtype]):
+    @staticmethod
+    def _launch_build(owner, k, x1, x2, Z, B):
+        import ctypes as C
+
+        from . import _lib, profiling
+        from .executor import dtype_code
+
+        a = owner._fctp_args(k, x1, x2, B)
+        a.z = Z.data_ptr()
+        a.z_dtype = _lib.BF16
+        with profiling.kernel("fctp_build_z"):
+            _lib.check(_lib.lib().cueq_b200_fctp_build_z(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        del dtype_code
+
+    @staticmethod
+    def _gemm(A, Bm, Cptr, M, N, K, lda, ldb, ldc, status, accumulate=0, out_bf16=0, a_mn=0, b_mn=0, rows_per_group=1, group_stride=0):
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), Bm.data_ptr(), Cptr
+        g.M, g.N, g.K, g.lda, g.ldb, g.ldc = M, N, K, lda, ldb, ldc
+        g.rows_per_group, g.group_stride = rows_per_group, group_stride
+        g.accumulate, g.out_bf16, g.a_mn_major, g.b_mn_major = accumulate, out_bf16, a_mn, b_mn
+        g.status = status.data_ptr()
+        with profiling.kernel("gemm_bf16_tcgen05"):
+            _lib.check(_lib.lib().cueq_b200_gemm_bf16(C.byref(g), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    @staticmethod
+    def forward(ctx, owner, w, x1, x2):
+        d, off = owner.d, owner.offsets
+        B = x1.shape[0]
+        dev = x1.device
+        x1c, x2c = owner._as_kernel_input(x1), owner._as_kernel_input(x2)
+        out = torch.zeros((B, owner.out_size), dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        seen = set()
+        for k, p in enumerate(d.paths):
+            sw, s1, s2, so = p.indices
+            U, V, Wd = d.operands[0].segments[sw]
+            d3 = p.coefficients.shape[2]
+            rows = B * d3
+            Z = torch.empty((rows, U * V), dtype=torch.bfloat16, device=dev)
+            _TensorCoreUVW._launch_build(owner, k, x1c, x2c, Z, B)
+            WT = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd).t().contiguous().to(torch.bfloat16)
+            cptr = out.data_ptr() + 4 * off[3][so]
+            _TensorCoreUVW._gemm(Z, WT, cptr, rows, Wd, U * V, U * V, U * V, Wd, status, accumulate=1 if so in seen else 0,
+                                 rows_per_group=d3, group_stride=owner.out_size)
+            seen.add(so)
+        ctx.owner, ctx.status = owner, status
+        ctx.save_for_backward(w, x1, x2)
+        return out.to(x1.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gout):
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        owner = ctx.owner
+        w, x1, x2 = ctx.saved_tensors
+        d, off = owner.d, owner.offsets
+        B, dev = x1.shape[0], x1.device
+        need_w, need_x1, need_x2 = ctx.needs_input_grad[1], ctx.needs_input_grad[2], ctx.needs_input_grad[3]
+        x1c, x2c = owner._as_kernel_input(x1), owner._as_kernel_input(x2)
+        gw = torch.zeros((1, w.shape[1]), dtype=torch.float32, device=dev) if need_w else None
+        gx1 = torch.zeros(x1.shape, dtype=torch.float32, device=dev) if need_x1 else None
+        gx2 = torch.zeros(x2.shape, dtype=torch.float32, device=dev) if need_x2 else None
+        status = ctx.status
+        for k, p in enumerate(d.paths):
+            sw, s1, s2, so = p.indices
+            U, V, Wd = d.operands[0].segments[sw]
+            d3 = p.coefficients.shape[2]
+            rows = B * d3
+            rows_pad = (rows + 63) // 64 * 64
+            G = torch.zeros((rows_pad, Wd), dtype=torch.bfloat16, device=dev)
+            G[:rows] = gout[:, off[3][so] : off[3][so] + d3 * Wd].reshape(rows, Wd)
+            if need_w:
+                Z = torch.empty((rows_pad, U * V), dtype=torch.bfloat16, device=dev)
+                if rows_pad > rows:
+                    Z[rows:].zero_()
+                _TensorCoreUVW._launch_build(owner, k, x1c, x2c, Z, B)
+                gwp = gw[0, off[0][sw] : off[0][sw] + U * V * Wd]
+                # gW[(uv), w] = sum_(z,k) Z[(z,k),(uv)] G[(z,k),w]: both operands are stored [K][M or N]
+                _TensorCoreUVW._gemm(Z, G, gwp.data_ptr(), U * V, Wd, rows_pad, U * V, Wd, Wd, status, a_mn=1, b_mn=1)
+                del Z
+            if need_x1 or need_x2:
+                W16 = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd).contiguous().to(torch.bfloat16)
+                gZ = torch.empty((rows, U * V), dtype=torch.bfloat16, device=dev)
+                _TensorCoreUVW._gemm(G, W16, gZ.data_ptr(), rows, U * V, Wd, Wd, Wd, U * V, status, out_bf16=1)
+                a = owner._fctp_args(k, x1c, x2c, B)
+                a.z, a.z_dtype = gZ.data_ptr(), _lib.BF16
+                a.gx1 = gx1.data_ptr() if need_x1 else None
+                a.gx2 = gx2.data_ptr() if need_x2 else None
+                with profiling.kernel("fctp_consume_gz"):
+                    _lib.check(_lib.lib().cueq_b200_fctp_consume_gz(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                del gZ
+        return (None, gw.to(w.dtype) if need_w else None, gx1.to(x1.dtype) if need_x1 else None,
+                gx2.to(x2.dtype) if need_x2 else None)
+
+
+class DenseUVW:
+    """Dense route for ``uvw,iu,jv,kw+ijk`` (see the module docstring)."""
+
+    def __init__(self, polynomial: Polynomial, math_dtype: Optional[torch.dtype], options: Optional[dict] = None):
         _, d = polynomial.operations[0]
         self.d = d
         self.math_dtype = math_dtype
+        self.force_tc = bool((options or {}).get("tensor_cores", False))
+        self._cg = {}
         self.offsets = [op.offsets() for op in d.operands]
         self.out_size = d.operands[3].size
         self._coef = {}
@@ -82,10 +196,56 @@ class DenseUVW:
             self._coef[key] = t
         return t
 
+    # -- tensor-core route ---------------------------------------------------------------------
+    def _tc_applicable(self, w, x1, x2) -> bool:
+        if w.shape[0] != 1 or x1.shape[0] != x2.shape[0] or x1.shape[0] == 0:
+            return False
+        if not (self.force_tc or x1.dtype in (torch.bfloat16, torch.float16)):
+            return False
+        for p in self.d.paths:
+            U, V, Wd = self.d.operands[0].segments[p.indices[0]]
+            if (U * V) % 128 or Wd % 64 or V % 2 or max(p.coefficients.shape) > 7:
+                return False
+        return True
+
+    @staticmethod
+    def _as_kernel_input(x):
+        if x.dtype in (torch.float32, torch.bfloat16):
+            return x.contiguous()
+        return x.float().contiguous()
+
+    def _fctp_args(self, k, x1, x2, B):
+        import ctypes as C
+
+        from . import _lib
+        from .executor import dtype_code
+
+        d, off, p = self.d, self.offsets, self.d.paths[k]
+        sw, s1, s2, so = p.indices
+        U, V, _ = d.operands[0].segments[sw]
+        d1, d2, d3 = p.coefficients.shape
+        cg = self._cg.get(k)
+        if cg is None:
+            flat = [float(v) for v in p.coefficients.reshape(-1)]
+            cg = (C.c_float * len(flat))(*flat)
+            self._cg[k] = cg
+        a = _lib.FctpArgs()
+        a.x1, a.x2 = x1.data_ptr(), x2.data_ptr()
+        a.cg = C.cast(cg, C.POINTER(C.c_float))
+        a.ld1, a.ld2, a.batch = x1.shape[1], x2.shape[1], B
+        a.off1, a.off2 = off[1][s1], off[2][s2]
+        a.d1, a.d2, a.d3, a.U, a.V = d1, d2, d3, U, V
+        a.x_dtype = dtype_code(x1.dtype)
+        return a
+
     def __call__(self, inputs: List[torch.Tensor]) -> List[torch.Tensor]:
         w, x1, x2 = inputs
         if w.device.type != "cuda":
             raise RuntimeError("cuequivariance_b200 executes on CUDA devices only (there is no CPU fallback)")
+        if self._tc_applicable(w, x1, x2):
+            if x1.dtype != x2.dtype:
+                x2 = x2.to(x1.dtype)
+            return [_TensorCoreUVW.apply(self, w, x1, x2)]
         io = x1.dtype
         md = self.math_dtype or (io if io in (torch.float32, torch.float64) else torch.float32)
         d, off = self.d, self.offsets

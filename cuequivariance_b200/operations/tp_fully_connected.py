@@ -33,7 +33,10 @@ class FullyConnectedTensorProduct(torch.nn.Module):
         math_dtype=None,
         use_fallback: Optional[bool] = None,
         method: Optional[str] = None,
+        options: Optional[dict] = None,
     ):
+        """``options={"tensor_cores": True}`` sends float32 inputs through the bf16 tensor-core
+        route as well (bf16/fp16 inputs always take it when the shapes allow)."""
         super().__init__()
         if use_fallback:
             raise ValueError("cuequivariance_b200 has no fallback implementation (use_fallback must be None or False)")
@@ -59,7 +62,8 @@ class FullyConnectedTensorProduct(torch.nn.Module):
         self.transpose_out = TransposeIrrepsLayout(irreps_out, source=e.outputs[0].layout, target=IrrepsLayout.parse(layout_out or layout), device=device)
         if math_dtype is None and dtype in (torch.float32, torch.float64):
             math_dtype = dtype
-        self.f = SegmentedPolynomial(e.polynomial, method=self.method, math_dtype=math_dtype, name="fully_connected_tensor_product")
+        self.f = SegmentedPolynomial(e.polynomial, method=self.method, math_dtype=math_dtype, name="fully_connected_tensor_product",
+                                     options=options)
 
     def extra_repr(self) -> str:
         return f"shared_weights={self.shared_weights}, internal_weights={self.internal_weights}, weight_numel={self.weight_numel}"

@@ -125,7 +125,7 @@ class SegmentedPolynomial(nn.Module):
                 from .fused_tp import FLATTEN_LIMIT, DenseUVW, FusedTPProgram, flattened_path_count, is_fully_connected
 
                 if is_fully_connected(self.polynomial) and flattened_path_count(self.polynomial) > FLATTEN_LIMIT:
-                    prog = DenseUVW(self.polynomial, self.math_dtype)
+                    prog = DenseUVW(self.polynomial, self.math_dtype, self.options)
                 else:
                     prog = FusedTPProgram(self.polynomial, math_dtype, self.output_dtype_map, self.name)
             self._programs[math_dtype] = prog

@@ -175,9 +175,57 @@ int cueq_b200_u1d_static_launch(int id, int64_t batch, int32_t extent, const cue
  * (cuequivariance_torch/primitives/segmented_polynomial_fused_tp.py:51-72).  N must be a
  * multiple of 64 and K of 64.  `status` (nullable device int32) is set to 2 if an internal
  * bounded wait ran out (the result is then invalid). */
+/* General form.  An operand is K-major when stored [M or N][K] (K contiguous, the default) or
+ * MN-major when stored [K][M or N]; ld* are the row pitches in elements.  Output row r is written at
+ * C + (r / rows_per_group) * group_stride + (r % rows_per_group) * ldc (rows_per_group < 1 counts as
+ * 1; group_stride 0 means rows_per_group * ldc, i.e. plain C + r * ldc), as float32 (optionally
+ * accumulated into) or bf16. */
+typedef struct {
+  const void* A;
+  const void* B;
+  void* C;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc;
+  int64_t group_stride;
+  int32_t rows_per_group;
+  int32_t accumulate;
+  int32_t out_bf16;
+  int32_t a_mn_major, b_mn_major;
+  int32_t reserved;
+  void* status;
+} cueq_gemm_args;
+int cueq_b200_gemm_bf16(const cueq_gemm_args* args, void* stream);
 int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
                            int64_t lda, int64_t ldb, int64_t ldc, int32_t accumulate, void* status,
                            void* stream);
+
+/* ---- fully connected ("uvw") tensor product: kernels around the tensor-core GEMM -----------------
+ *
+ * For one path of uvw,iu,jv,kw+ijk (cue.descriptors.fully_connected_tensor_product,
+ * cuequivariance/group_theory/descriptors/irreps_tp.py:22-91; module forward at
+ * cuequivariance_torch/operations/tp_fully_connected.py:166-207) with coupling tensor cg[i][j][k]
+ * (host array, d1*d2*d3 floats, normalisation included):
+ *   build_z   : Z[(z,k), (u,v)] = sum_ij cg[i,j,k] x1[z, off1 + i*U + u] x2[z, off2 + j*V + v]   (bf16, [batch*d3, U*V])
+ *   consume_gz: gx1[z, off1 + i*U + u] += sum_jkv cg[i,j,k] gZ[(z,k),(u,v)] x2[...]
+ *               gx2[z, off2 + j*V + v] += sum_iku cg[i,j,k] gZ[(z,k),(u,v)] x1[...]
+ * x1/x2 are float32 or bf16 (x_dtype), component-major (ir_mul) rows of pitch ld1/ld2; gx1/gx2
+ * are float32 with the same pitches (either may be NULL); z is the bf16 output of build_z or the
+ * gZ input (float32 or bf16, z_dtype) of consume_gz. */
+typedef struct {
+  const void* x1;
+  const void* x2;
+  void* z;
+  void* gx1;
+  void* gx2;
+  const float* cg;
+  int64_t ld1, ld2, batch;
+  int32_t off1, off2;
+  int32_t d1, d2, d3, U, V;
+  int32_t x_dtype, z_dtype;
+  int32_t reserved;
+} cueq_fctp_args;
+int cueq_b200_fctp_build_z(const cueq_fctp_args* args, void* stream);
+int cueq_b200_fctp_consume_gz(const cueq_fctp_args* args, void* stream);
 
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *

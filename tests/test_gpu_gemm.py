@@ -37,3 +37,47 @@ def test_gemm_bf16_matches_torch(M, N, K):
     # accumulate into an existing C
     got2 = _gemm(a, b, got.clone())
     assert torch.allclose(got2, 2 * ref, rtol=1e-4, atol=2e-3 * (K / 64) ** 0.5)
+
+
+def _gemm_general(a, b, M, N, K, a_mn=False, b_mn=False, out_bf16=False, rows_per_group=1, group_stride=0, c=None, ldc=None):
+    g = _lib.GemmArgs()
+    ldc = ldc or N
+    if c is None:
+        c = torch.zeros((M, N), dtype=torch.bfloat16 if out_bf16 else torch.float32, device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    g.A, g.B, g.C = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb, g.ldc = a.stride(0), b.stride(0), ldc
+    g.rows_per_group, g.group_stride = rows_per_group, group_stride
+    g.out_bf16, g.a_mn_major, g.b_mn_major = int(out_bf16), int(a_mn), int(b_mn)
+    g.status = status.data_ptr()
+    _lib.check(_lib.lib().cueq_b200_gemm_bf16(C.byref(g), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return c
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(True, False), (False, True), (True, True)])
+def test_gemm_mn_major_operands(a_mn, b_mn):
+    M, N, K = 256, 128, 320
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    got = _gemm_general(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, M, N, K, a_mn, b_mn)
+    assert torch.allclose(got, ref, rtol=1e-4, atol=3e-3), float((got - ref).abs().max())
+
+
+def test_gemm_grouped_rows_and_bf16_output():
+    M, N, K = 3 * 100, 64, 128
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    # rows (z, k) with k < 3 land at z * 400 + 70 + k * 64 inside a wider row-major buffer
+    buf = torch.zeros(100, 400, device="cuda")
+    _gemm_general(a, b, M, N, K, rows_per_group=3, group_stride=400, c=buf[:, 8:], ldc=64)
+    assert torch.allclose(buf[:, 8 : 8 + 192].reshape(300, 64), ref, rtol=1e-4, atol=2e-3)
+    assert torch.count_nonzero(buf[:, :8]) == 0 and torch.count_nonzero(buf[:, 200:]) == 0
+    got = _gemm_general(a, b, M, N, K, out_bf16=True)
+    assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-1)

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import cuequivariance_b200 as cb
-from cuequivariance_b200 import descriptors as D
+from cuequivariance_b200 import descriptors as D, profiling
 from oracle import naive
 
 pytestmark = pytest.mark.gpu
@@ -258,3 +258,35 @@ def test_fully_connected_dense_route_matches_oracle():
         _close(a, b, 1e-4, 2e-5, "grad")
     for a, b in zip(got[2], ref[2]):
         _close(a, b, 1e-3, 2e-4, "gradgrad")
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float32])
+def test_fully_connected_tensor_core_route(in_dtype):
+    """64 channels: the tensor-core route (bf16 operands, float32 accumulation).  Compared with
+    the CPU oracle evaluated in float32 on the same (bf16-rounded) inputs; tolerance is that of
+    bf16 operands (rtol 2e-2 of the tensor's scale; the reference's own bf16 tolerance is
+    rtol 1e-2 / atol 4.0, cuequivariance_torch/_tests/utils.py:282)."""
+    s = "64x0e+64x1o+64x2e"
+    e = D.fully_connected_tensor_product(s, s, s)
+    m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.ir_mul, internal_weights=False, shared_weights=True,
+                                       options={"tensor_cores": True})
+    gen = torch.Generator().manual_seed(22)
+    B = 96
+    x1 = torch.randn(B, m.irreps_in1.dim, generator=gen).to(in_dtype)
+    x2 = torch.randn(B, m.irreps_in2.dim, generator=gen).to(in_dtype)
+    w = (torch.randn(1, m.weight_numel, generator=gen) / 64.0).to(in_dtype)
+    cot = torch.randn(B, m.irreps_out.dim, generator=gen)
+
+    def grads(fn, xs, c):
+        xs = [x.clone().requires_grad_(True) for x in xs]
+        out = fn(*xs)
+        return [out.detach()] + list(torch.autograd.grad((out.float() * c).sum(), xs))
+
+    ref = grads(lambda w_, a, b: naive.segmented_polynomial(e.polynomial, [w_, a, b])[0], [w.float(), x1.float(), x2.float()], cot)
+    profiling.reset()
+    got = grads(lambda w_, a, b: m(a, b, w_), [w.to(DEV), x1.to(DEV), x2.to(DEV)], cot.to(DEV))
+    assert profiling.launch_count >= 3 * 11, "the tensor-core route did not run"
+    for name, a, b in zip(["out", "gw", "gx1", "gx2"], got, ref):
+        scale = float(b.abs().max())
+        err = float((a.float().cpu() - b).abs().max())
+        assert err <= 2e-2 * scale, f"{name}: max abs diff {err:.3e} at scale {scale:.3e}"
