@@ -78,7 +78,7 @@ class GemmArgs(C.Structure):
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("group_stride", C.c_int64),
         ("rows_per_group", C.c_int32), ("accumulate", C.c_int32), ("out_bf16", C.c_int32),
-        ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32), ("reserved", C.c_int32),
+        ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32), ("c_is_zero", C.c_int32),
         ("status", C.c_void_p),
     ]
 

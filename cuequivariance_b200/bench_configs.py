@@ -79,22 +79,29 @@ def config1(steps, dev):
             "gpu_launches": n, "kernels_ms": k}
 
 
-def config2(steps, dev):
+def config2(steps, dev, dtype=torch.float32):
     s = "64x0e+64x1o+64x2e"
     B = 32768
     m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.mul_ir, internal_weights=False, shared_weights=True)
     g = torch.Generator(device=dev).manual_seed(20)
-    x1 = torch.randn(B, m.irreps_in1.dim, generator=g, device=dev, requires_grad=True)
-    x2 = torch.randn(B, m.irreps_in2.dim, generator=g, device=dev, requires_grad=True)
-    w = (torch.randn(1, m.weight_numel, generator=g, device=dev) / 64.0).requires_grad_(True)
+    x1 = torch.randn(B, m.irreps_in1.dim, generator=g, device=dev).to(dtype).requires_grad_(True)
+    x2 = torch.randn(B, m.irreps_in2.dim, generator=g, device=dev).to(dtype).requires_grad_(True)
+    w = (torch.randn(1, m.weight_numel, generator=g, device=dev) / 64.0).to(dtype).requires_grad_(True)
 
     def step():
         out = m(x1, x2, w)
-        torch.autograd.grad(out.sum(), [x1, x2, w])
+        torch.autograd.grad(out.float().sum(), [x1, x2, w])
 
     ms, n, k = _time(step, steps)
-    return {"config": 2, "what": "fully connected fwd+bwd, float32, interim library-GEMM route", "ms_per_step": ms,
-            "value": B / ms * 1e3, "unit": "samples/s", "gpu_launches": n, "kernels_ms": k}
+    route = "tensor-core route (TMA + tcgen05 GEMM, bf16 operands, float32 accumulation)" if dtype == torch.bfloat16 \
+        else "interim full-precision library-GEMM route"
+    flops = 4 * 2 * 35 * 64 ** 3 * B
+    return {"config": 2, "what": f"fully connected fwd+bwd, {str(dtype).split('.')[-1]}, {route}", "ms_per_step": ms,
+            "value": B / ms * 1e3, "unit": "samples/s", "tflops": flops / ms / 1e9, "gpu_launches": n, "kernels_ms": k}
+
+
+def config2_bf16(steps, dev):
+    return config2(steps, dev, torch.bfloat16)
 
 
 def config4(steps, dev, E=65536, N=4096):
@@ -126,7 +133,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
-    fns = {"0": config0, "1": config1, "2": config2, "4": config4}
+    fns = {"0": config0, "1": config1, "2": config2, "2bf16": config2_bf16, "4": config4}
     for key in (fns if a.config == "all" else [a.config]):
         print(json.dumps(fns[key](a.steps, dev)), flush=True)
 

@@ -83,20 +83,30 @@ __global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_co
     __syncthreads();
     contract_T(p, xs2, T);
     __syncthreads();
-    // threads: v fastest; each thread owns one v (pairs of v for the packed store) and strides over u
+    // a thread owns one pair of v (its T values stay in registers) and strides over u; the
+    // threads of a warp share u, so x1 is read as a broadcast and Z rows are written contiguously
     const int vpairs = p.V / 2;
-    for (int k = 0; k < p.d3; ++k) {
-      __nv_bfloat16* zrow = Z + (z * p.d3 + k) * (int64_t)UV;
-      for (int t = threadIdx.x; t < p.U * vpairs; t += blockDim.x) {
-        const int vp = t % vpairs, u = t / vpairs;
-        float a0 = 0.f, a1 = 0.f;
-        for (int i = 0; i < p.d1; ++i) {
-          const float xi = xs1[i * p.U + u];
-          const float2 tt = *reinterpret_cast<const float2*>(T + (k * p.d1 + i) * p.V + 2 * vp);
-          a0 = fmaf(tt.x, xi, a0);
-          a1 = fmaf(tt.y, xi, a1);
+    const int ugroups = blockDim.x / vpairs;
+    const int vp = threadIdx.x % vpairs, ug = threadIdx.x / vpairs;
+    if (ug < ugroups) {
+      for (int k = 0; k < p.d3; ++k) {
+        float2 tt[kMaxD];
+#pragma unroll
+        for (int i = 0; i < kMaxD; ++i)
+          tt[i] = i < p.d1 ? *reinterpret_cast<const float2*>(T + (k * p.d1 + i) * p.V + 2 * vp) : make_float2(0.f, 0.f);
+        __nv_bfloat16* zrow = Z + (z * p.d3 + k) * (int64_t)UV + 2 * vp;
+        for (int u = ug; u < p.U; u += ugroups) {
+          float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < kMaxD; ++i) {
+            if (i < p.d1) {
+              const float xi = xs1[i * p.U + u];
+              a0 = fmaf(tt[i].x, xi, a0);
+              a1 = fmaf(tt[i].y, xi, a1);
+            }
+          }
+          *reinterpret_cast<__nv_bfloat162*>(zrow + u * p.V) = __floats2bfloat162_rn(a0, a1);
         }
-        *reinterpret_cast<__nv_bfloat162*>(zrow + u * p.V + 2 * vp) = __floats2bfloat162_rn(a0, a1);
       }
     }
   }

@@ -85,6 +85,7 @@ struct GemmParams {
   int accumulate;
   int out_bf16;         // 1: C is bf16 (no accumulation), 0: float32
   int a_mn_major, b_mn_major;  // 1: the operand is stored [K][M or N] (M/N contiguous) instead of [M or N][K]
+  int kb_per_split;     // K blocks handled by one CTA (split-K over blockIdx.z; partial sums are added atomically)
   int* status;
 };
 
@@ -101,7 +102,9 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int num_kb = p.K / BK;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int num_kb = min(p.kb_per_split, p.K / BK - kb_begin);
+  const bool split = gridDim.z > 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesTc; ++s) { bar_init(full + s, 1); bar_init(empty + s, 1); }
@@ -125,13 +128,13 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
         bar_expect_tx(full + s, kStageBytes);
         unsigned char* a = smem + s * kStageBytes;
         if (p.a_mn_major) {
-          tma_load_2d(a, &map_a, m0, kb * BK, full + s);
-          tma_load_2d(a + 8192, &map_a, m0 + 64, kb * BK, full + s);
+          tma_load_2d(a, &map_a, m0, (kb_begin + kb) * BK, full + s);
+          tma_load_2d(a + 8192, &map_a, m0 + 64, (kb_begin + kb) * BK, full + s);
         } else {
-          tma_load_2d(a, &map_a, kb * BK, m0, full + s);
+          tma_load_2d(a, &map_a, (kb_begin + kb) * BK, m0, full + s);
         }
-        if (p.b_mn_major) tma_load_2d(a + kTileA, &map_b, n0, kb * BK, full + s);
-        else tma_load_2d(a + kTileA, &map_b, kb * BK, n0, full + s);
+        if (p.b_mn_major) tma_load_2d(a + kTileA, &map_b, n0, (kb_begin + kb) * BK, full + s);
+        else tma_load_2d(a + kTileA, &map_b, (kb_begin + kb) * BK, n0, full + s);
       }
     }
   } else if (warp == 1) {
@@ -192,6 +195,10 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+            if (split) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst + c), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+              continue;
+            }
             if (p.accumulate) {
               const float4 old = *reinterpret_cast<const float4*>(dst + c);
               o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -270,7 +277,19 @@ extern "C" int cueq_b200_gemm_bf16(const cueq_gemm_args* g, void* stream) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)(N / BN));
+  // split K when the tile grid alone cannot fill the GPU (partial sums then need a float32 C that
+  // the caller zeroed or wants accumulated into)
+  const int64_t tiles = ((M + BM - 1) / BM) * (N / BN);
+  const int total_kb = (int)(K / BK);
+  int splits = 1;
+  if (!g->out_bf16 && (g->accumulate || g->c_is_zero) && tiles < 296 && total_kb >= 16) {
+    splits = (int)((592 + tiles - 1) / tiles);
+    if (splits > total_kb / 4) splits = total_kb / 4;
+    if (splits < 1) splits = 1;
+  }
+  p.kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)(N / BN), (unsigned)splits);
   gemm_bf16_tn_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
@@ -281,6 +300,6 @@ extern "C" int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, in
   cueq_gemm_args g;
   std::memset(&g, 0, sizeof(g));
   g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
-  g.accumulate = accumulate; g.status = status; g.rows_per_group = 1;
+  g.accumulate = accumulate; g.status = status; g.rows_per_group = 1; g.c_is_zero = 0;
   return cueq_b200_gemm_bf16(&g, stream);
 }

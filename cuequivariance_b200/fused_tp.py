@@ -87,7 +87,8 @@ class _TensorCoreUVW(torch.autograd.Function):
         del dtype_code
 
     @staticmethod
-    def _gemm(A, Bm, Cptr, M, N, K, lda, ldb, ldc, status, accumulate=0, out_bf16=0, a_mn=0, b_mn=0, rows_per_group=1, group_stride=0):
+    def _gemm(A, Bm, Cptr, M, N, K, lda, ldb, ldc, status, accumulate=0, out_bf16=0, a_mn=0, b_mn=0, rows_per_group=1, group_stride=0,
+              c_is_zero=0):
         import ctypes as C
 
         from . import _lib, profiling
@@ -97,6 +98,7 @@ class _TensorCoreUVW(torch.autograd.Function):
         g.M, g.N, g.K, g.lda, g.ldb, g.ldc = M, N, K, lda, ldb, ldc
         g.rows_per_group, g.group_stride = rows_per_group, group_stride
         g.accumulate, g.out_bf16, g.a_mn_major, g.b_mn_major = accumulate, out_bf16, a_mn, b_mn
+        g.c_is_zero = c_is_zero
         g.status = status.data_ptr()
         with profiling.kernel("gemm_bf16_tcgen05"):
             _lib.check(_lib.lib().cueq_b200_gemm_bf16(C.byref(g), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
@@ -158,7 +160,7 @@ class _TensorCoreUVW(torch.autograd.Function):
                 _TensorCoreUVW._launch_build(owner, k, x1c, x2c, Z, B)
                 gwp = gw[0, off[0][sw] : off[0][sw] + U * V * Wd]
                 # gW[(uv), w] = sum_(z,k) Z[(z,k),(uv)] G[(z,k),w]: both operands are stored [K][M or N]
-                _TensorCoreUVW._gemm(Z, G, gwp.data_ptr(), U * V, Wd, rows_pad, U * V, Wd, Wd, status, a_mn=1, b_mn=1)
+                _TensorCoreUVW._gemm(Z, G, gwp.data_ptr(), U * V, Wd, rows_pad, U * V, Wd, Wd, status, a_mn=1, b_mn=1, c_is_zero=1)
                 del Z
             if need_x1 or need_x2:
                 W16 = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd).contiguous().to(torch.bfloat16)

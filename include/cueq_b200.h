@@ -191,7 +191,8 @@ typedef struct {
   int32_t accumulate;
   int32_t out_bf16;
   int32_t a_mn_major, b_mn_major;
-  int32_t reserved;
+  int32_t c_is_zero;    /* 1: C holds zeros, so the library may split K over several CTAs and add
+                           their partial sums atomically (it also may when accumulate is set)    */
   void* status;
 } cueq_gemm_args;
 int cueq_b200_gemm_bf16(const cueq_gemm_args* args, void* stream);
