@@ -86,6 +86,32 @@ __device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
   else
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
+// L2 cache policies: per-edge operands are read once (evict first), the gathered node rows
+// and the scattered node gradients are revisited by other edges (evict last)
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ unsigned long long policy_evict_last() {
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(p));
+  return p;
+}
+template <int BYTES>
+__device__ __forceinline__ void cp_async_hint(void* smem_dst, const void* gmem_src, unsigned long long policy) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  if constexpr (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem_src), "l"(policy) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 8, %2;\n" ::"r"(d), "l"(gmem_src), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void red_add_hint(float* addr, const float (&v)[4], unsigned long long policy) {
+  asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void red_add_hint(float* addr, const float (&v)[2], unsigned long long policy) {
+  asm volatile("red.global.add.L2::cache_hint.v2.f32 [%0], {%1, %2}, %3;\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -155,6 +181,14 @@ __device__ __forceinline__ void stage_block(Vec<C>* dst, const float* base, int 
     cp_async<4 * C>(dst + t * 32 + lane, src);
   }
 }
+template <int D, int C, bool MUL_IR>
+__device__ __forceinline__ void stage_block_hint(Vec<C>* dst, const float* base, int extent, int ch, int lane, unsigned long long pol) {
+#pragma unroll
+  for (int t = 0; t < D; ++t) {
+    const float* src = MUL_IR ? base + (int64_t)ch * D + C * t : base + (int64_t)t * extent + ch;
+    cp_async_hint<4 * C>(dst + t * 32 + lane, src, pol);
+  }
+}
 
 template <int D, int C, bool MUL_IR, int ROWS>
 __device__ __forceinline__ void unstage_block(const Vec<C>* src, int lane, float (&X)[ROWS][C]) {
@@ -174,7 +208,7 @@ __device__ __forceinline__ void unstage_block(const Vec<C>* src, int lane, float
 
 // registers -> global, same two layouts; RED: vector reduction, else streaming store
 template <int D, int C, bool MUL_IR, bool RED, int ROWS>
-__device__ __forceinline__ void emit_block(float* base, int extent, int ch, const float (&V)[ROWS][C], int row0) {
+__device__ __forceinline__ void emit_block(float* base, int extent, int ch, const float (&V)[ROWS][C], int row0, unsigned long long pol = 0) {
   if (MUL_IR) {
     float f[D * C];
 #pragma unroll
@@ -186,12 +220,12 @@ __device__ __forceinline__ void emit_block(float* base, int extent, int ch, cons
       float v[C];
 #pragma unroll
       for (int c = 0; c < C; ++c) v[c] = f[C * t + c];
-      if (RED) red_add(base + (int64_t)ch * D + C * t, v); else st_stream(base + (int64_t)ch * D + C * t, v);
+      if (RED) red_add_hint(base + (int64_t)ch * D + C * t, v, pol); else st_stream(base + (int64_t)ch * D + C * t, v);
     }
   } else {
 #pragma unroll
     for (int i = 0; i < D; ++i) {
-      if (RED) red_add(base + (int64_t)i * extent + ch, V[row0 + i]); else st_stream(base + (int64_t)i * extent + ch, V[row0 + i]);
+      if (RED) red_add_hint(base + (int64_t)i * extent + ch, V[row0 + i], pol); else st_stream(base + (int64_t)i * extent + ch, V[row0 + i]);
     }
   }
 }
@@ -231,18 +265,19 @@ struct MTerms {
 
 // asynchronous loads of everything edge `pos` needs into the stage at `st`; returns the edge id
 template <class G, int C, bool X1_MUL_IR>
-__device__ __forceinline__ int issue_edge(const CwParams& p, float* st, int pos, int ch, int lane, bool active) {
+__device__ __forceinline__ int issue_edge(const CwParams& p, float* st, int pos, int ch, int lane, bool active,
+                                          unsigned long long pol_stream, unsigned long long pol_keep) {
   const int eid = p.order ? __ldg(p.order + pos) : pos;
   float* x2s = st;
   Vec<C>* stage = reinterpret_cast<Vec<C>*>(x2s + Smem<G, C>::kX2);
-  if (lane < (G::NX2 + 3) / 4) cp_async<16>(x2s + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane);
+  if (lane < (G::NX2 + 3) / 4) cp_async_hint<16>(x2s + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane, pol_stream);
   if (active) {
     const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-    stage_block<G::D1, C, X1_MUL_IR>(stage, p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, lane);
+    stage_block_hint<G::D1, C, X1_MUL_IR>(stage, p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, lane, pol_keep);
     const float* wrow = p.w + (int64_t)eid * p.w_stride + ch;
     Vec<C>* wst = stage + G::D1 * 32;
 #pragma unroll
-    for (int q = 0; q < G::NPATH; ++q) cp_async<4 * C>(wst + q * 32 + lane, wrow + p.w_off[q]);
+    for (int q = 0; q < G::NPATH; ++q) cp_async_hint<4 * C>(wst + q * 32 + lane, wrow + p.w_off[q], pol_stream);
   }
   cp_async_commit();
   return eid;
@@ -277,6 +312,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const
   const bool active = ch < p.extent;
   MTerms<G> mt;
   mt.load(p, lane);
+  const unsigned long long pol_stream = policy_evict_first(), pol_keep = policy_evict_last();
 
   const int total_warps = gridDim.x * kWarps;
   for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
@@ -288,11 +324,11 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const
       for (int c = 0; c < C; ++c) acc[a][c] = 0.f;
     float* Msm = mine;
     float* stages = mine + S::kM;
-    if (beg < end) issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active);
+    if (beg < end) issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active, pol_stream, pol_keep);
     for (int pos = beg; pos < end; ++pos) {
       float* st = stages + ((pos - beg) & 1) * S::kPerStage;
       if (pos + 1 < end) {
-        issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active, pol_stream, pol_keep);
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
@@ -488,6 +524,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
   const bool active = ch < p.extent;
   MTerms<G> mt;
   mt.load(p, lane);
+  const unsigned long long pol_stream = policy_evict_first(), pol_keep = policy_evict_last();
 
   const int total_warps = gridDim.x * kWarps;
   for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
@@ -497,12 +534,12 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
     cp_async_commit();
     float* Msm = mine;
     float* stages = mine + S::kM;
-    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active);
+    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active, pol_stream, pol_keep);
     for (int pos = beg; pos < end; ++pos) {
       float* st = stages + ((pos - beg) & 1) * S::kPerStage;
       eid = eid_next;
       if (pos + 1 < end) {
-        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active);
+        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active, pol_stream, pol_keep);
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
@@ -524,7 +561,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
         BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
           const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0);
+          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
         }
       }
       if (p.need_gx2) {
