@@ -187,6 +187,7 @@ def main():
     ap.add_argument("--edges", type=int, default=E_TOTAL, help="total edges (default: the named configuration)")
     ap.add_argument("--nodes", type=int, default=N_TOTAL)
     ap.add_argument("--cpl", type=int, default=0, help="force channels per lane (2 or 4) in the channelwise kernels; 0 = library default")
+    ap.add_argument("--sender-passes", type=int, default=None, help="backward: sender-range passes (1 = off)")
     ap.add_argument("--staging", type=int, default=None, help="forward staging: 0 = cp.async per lane, 1 = bulk copies")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -221,6 +222,10 @@ def main():
         from cuequivariance_b200 import channelwise
 
         channelwise.STAGING = args.staging
+    if args.sender_passes is not None:
+        from cuequivariance_b200 import channelwise
+
+        channelwise.SENDER_PASSES = args.sender_passes
     E, N = args.edges, args.nodes
     tp = cb.ChannelWiseTensorProduct(IRREPS1, IRREPS2, FILTER, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
     sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)

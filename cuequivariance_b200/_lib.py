@@ -55,7 +55,7 @@ class CwArgs(C.Structure):
         ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
         ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
         ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32), ("channels_per_lane", C.c_int32), ("staging", C.c_int32),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("recv_mod", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -145,6 +145,11 @@ def lib() -> C.CDLL:
     L.cueq_b200_fctp_consume_gz.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
+    L.cueq_b200_sizeof.restype = C.c_int64
+    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs)):
+        if L.cueq_b200_sizeof(which) != C.sizeof(struct):
+            raise CueqError(f"{struct.__name__}: this binding declares {C.sizeof(struct)} bytes, the library "
+                            f"{L.cueq_b200_sizeof(which)}; rebuild the library or update the binding")
     _lib = L
     return L
 

@@ -85,6 +85,27 @@ class _CsrCache:
             self.entries.pop(0)
         return val
 
+    def get_passes(self, receivers, senders, num_rows: int, num_senders: int, passes: int):
+        """CSR over (pass, receiver) rows, pass = which of ``passes`` equal ranges the sender
+        falls in: edges are visited pass by pass, so that only 1/passes of the node rows is
+        gathered from / reduced into at a time (keeps that working set inside L2)."""
+        import torch
+
+        key = ("passes", receivers.data_ptr(), receivers._version, senders.data_ptr(), senders._version, num_rows, num_senders, passes)
+        for k, ref, val in self.entries:
+            if k == key and ref is receivers:
+                return val
+        span = (num_senders + passes - 1) // passes
+        rows = (senders.to(torch.int64) // span) * num_rows + receivers.to(torch.int64)
+        sorted_rows, order = torch.sort(rows, stable=True)
+        bounds = torch.arange(passes * num_rows + 1, device=receivers.device, dtype=torch.int64)
+        rowptr = torch.searchsorted(sorted_rows.contiguous(), bounds, right=False).to(torch.int32)
+        val = (order.to(torch.int32), rowptr)
+        self.entries.append((key, receivers, val))
+        if len(self.entries) > self.capacity:
+            self.entries.pop(0)
+        return val
+
     def int32(self, index):
         import torch
 
@@ -102,6 +123,7 @@ class _CsrCache:
 
 
 _CSR = _CsrCache()
+SENDER_PASSES = 1  # backward: visit the edges in this many sender-range passes when the node table exceeds 64 MB
 STAGING = 0  # forward kernels: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) signalled on an mbarrier
 CHANNELS_PER_LANE = 0  # 0: the library chooses; 2 or 4 force a variant (used by the tests)
 _IDENTITY_ROWPTR: dict = {}
@@ -256,7 +278,9 @@ class _ChannelwiseBase:
         if x1_mul_ir is None or any(x.data_ptr() % 16 for x in xs):
             return None
         senders = _CSR.int32(x1_s.index) if x1_s.mode == _lib.INDEXED else None
-        return dict(x1_mul_ir=x1_mul_ir, senders=senders)
+        recv_spec = cfg.inputs[3] if n_in >= 4 else cfg.outputs[0]
+        receivers = recv_spec.index if recv_spec.mode == _lib.INDEXED else None
+        return dict(x1_mul_ir=x1_mul_ir, senders=senders, receivers=receivers)
 
     def _csr(self, spec, batch, device):
         import torch
@@ -387,6 +411,11 @@ class _ChannelwiseBase:
 
         plan = self.plan
         order, rowptr, nrecv = csr
+        recv_mod = 0
+        if (needs[1] and SENDER_PASSES > 1 and common["senders"] is not None and common.get("receivers") is not None
+                and x1.shape[0] * plan.row_sizes[1] * 4 > (64 << 20)):
+            order, rowptr = _CSR.get_passes(common["receivers"], common["senders"], nrecv, x1.shape[0], SENDER_PASSES)
+            recv_mod, nrecv = nrecv, nrecv * SENDER_PASSES
         dev = w.device
         gw = torch.empty_like(w) if needs[0] else None
         gx1 = torch.zeros_like(x1) if needs[1] else None
@@ -397,6 +426,7 @@ class _ChannelwiseBase:
             for g, t in zip(plan.groups, tabs):
                 a, keep = self._args(g, t, "bwd_tab", common, order, rowptr, nrecv, mul_ir,
                                      dict(w=w, x1=x1, x2=x2, gout=gout, gw=gw, gx1=gx1, gx2=gx2))
+                a.recv_mod = recv_mod
                 with profiling.kernel(f"cw_bwd[{g['id']}]", stream):
                     _lib.check(_lib.lib().cueq_b200_cw_backward(g["id"], C.byref(a), stream))
                 del keep

@@ -20,3 +20,14 @@ int fail(const char* fmt, ...) {
 
 extern "C" int cueq_b200_abi_version(void) { return CUEQ_B200_ABI_VERSION; }
 extern "C" const char* cueq_b200_last_error(void) { return cueq::error_buffer(); }
+extern "C" int64_t cueq_b200_sizeof(int which) {
+  switch (which) {
+    case 0: return sizeof(cueq_u1d_desc);
+    case 1: return sizeof(cueq_buffer);
+    case 2: return sizeof(cueq_cw_args);
+    case 3: return sizeof(cueq_cw_noalloc_args);
+    case 4: return sizeof(cueq_gemm_args);
+    case 5: return sizeof(cueq_fctp_args);
+    default: return -1;
+  }
+}

@@ -68,6 +68,7 @@ struct CwParams {
   int out_off[kMaxPaths];   // element offset of each path's output block inside an out row
   int need_gw, need_gx1, need_gx2;
   int* status;              // nullable: set to 1 if a bounded wait on a bulk copy ran out
+  int recv_mod;             // backward: CSR rows are (pass, receiver) pairs; the cotangent row is row % recv_mod (0: off)
 };
 
 template <int C> struct VecT;
@@ -530,7 +531,8 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
   for (int n = blockIdx.x * kWarps + warp; n < p.num_receivers; n += total_warps) {
     const int beg = __ldg(p.rowptr + n), end = __ldg(p.rowptr + n + 1);
     if (beg >= end) continue;
-    if (active) StageG<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)n * p.out_stride, p, ch, lane);
+    const int nrow = p.recv_mod ? n % p.recv_mod : n;
+    if (active) StageG<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)nrow * p.out_stride, p, ch, lane);
     cp_async_commit();
     float* Msm = mine;
     float* stages = mine + S::kM;
@@ -723,6 +725,7 @@ extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream)
   if (!a->bwd_coef) return cueq::fail("channelwise backward: null coefficient table");
   if (kGroups[g].nterm > kMaxTerms) return cueq::fail("channelwise backward: too many terms");
   if (p.num_receivers == 0) return 0;
+  p.recv_mod = a->recv_mod;
   CwCoef coef;
   std::memset(&coef, 0, sizeof(coef));
   for (int t = 0; t < kGroups[g].nterm; ++t) coef.c[t] = a->bwd_coef[t];

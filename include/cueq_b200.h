@@ -72,6 +72,10 @@ typedef struct {
 
 int cueq_b200_abi_version(void);
 const char* cueq_b200_last_error(void);
+/* sizeof() of an argument block as this library was compiled, so that a binding can check its own
+   declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
+   3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args; -1 for any other number. */
+int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
 
@@ -146,6 +150,9 @@ typedef struct {
   int32_t channels_per_lane; /* 0: automatic; 2 or 4: channels owned by one thread              */
   int32_t staging;      /* forward only: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) + mbarrier */
   void* status;         /* nullable device int32: set to 1 if a bounded wait on a bulk copy ran out */
+  int32_t recv_mod;     /* backward only: if > 0 the CSR has several rows per receiver (row r belongs to
+                           receiver r % recv_mod), used to visit the edges in sender-range passes        */
+  int32_t reserved2;
 } cueq_cw_args;
 
 int cueq_b200_cw_num_groups(void);
