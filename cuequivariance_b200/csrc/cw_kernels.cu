@@ -11,7 +11,7 @@
 //   * edges are addressed through a CSR over receivers (rowptr, optional edge order), so the
 //     reduction over the edges of a receiver happens in registers: every output row is
 //     written exactly once, without atomics and without a prior memset;
-//   * one warp owns one receiver at a time; a lane owns four consecutive channels (one
+//   * one warp owns one receiver at a time; a lane owns two (or four) consecutive channels (one
 //     128-bit access per segment), so a warp covers 128 channels; wider operands use
 //     blockIdx.y;
 //   * per edge, the channel-independent matrices M[i,k] = sum_j C[i,j,k] x2[j] of all paths of
