@@ -187,6 +187,7 @@ def main():
     ap.add_argument("--edges", type=int, default=E_TOTAL, help="total edges (default: the named configuration)")
     ap.add_argument("--nodes", type=int, default=N_TOTAL)
     ap.add_argument("--cpl", type=int, default=0, help="force channels per lane (2 or 4) in the channelwise kernels; 0 = library default")
+    ap.add_argument("--nccl-ctas", type=int, default=0, help="N>1: upper bound on the thread blocks of a collective (0: NCCL's choice)")
     ap.add_argument("--sender-passes", type=int, default=None, help="backward: sender-range passes (1 = off)")
     ap.add_argument("--staging", type=int, default=None, help="forward staging: 0 = cp.async per lane, 1 = bulk copies")
     ap.add_argument("--no-e2e", action="store_true")
@@ -212,7 +213,9 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        from cuequivariance_b200.distributed import exchange_group_options
+
+        dist.init_process_group("nccl", device_id=dev, pg_options=exchange_group_options(args.nccl_ctas))
 
     if args.cpl:
         from cuequivariance_b200 import channelwise

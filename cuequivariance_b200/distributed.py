@@ -41,6 +41,28 @@ def shard_edges(receivers: torch.Tensor, num_nodes: int, world: int, rank: int) 
     return int(e[0]), int(e[1])
 
 
+def exchange_group_options(max_ctas: Optional[int] = None):
+    """NCCL options for the group that carries the node-feature exchange.
+
+    The channelwise launches fill every SM, and thread blocks of a collective issued on a
+    normal-priority stream only become resident when the running launch drains, which
+    serialises each block's transfer behind the previous launch instead of overlapping it.
+    A high-priority stream lets the collective's few blocks in as soon as any block of the
+    compute kernel retires; ``max_ctas`` optionally bounds how many SMs it takes away
+    (measured on 8 B200s, ms per config-3 step: default stream 3.02; high priority 2.77;
+    high priority capped at 32 / 16 / 8 blocks 2.77 / 3.03 / 3.78)."""
+    opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    if max_ctas:
+        opts.config.max_ctas = int(max_ctas)
+    return opts
+
+
+def new_exchange_group(ranks=None, max_ctas: Optional[int] = None):
+    """A process group for :class:`ReceiverShardedChannelWise` with the options above
+    (collective on every rank, like ``torch.distributed.new_group``)."""
+    return dist.new_group(ranks=ranks, backend="nccl", pg_options=exchange_group_options(max_ctas))
+
+
 class _AllGatherRows(torch.autograd.Function):
     """``[n_local, d] -> [n_local * world, d]``; the adjoint is a sum reduce-scatter."""
 
