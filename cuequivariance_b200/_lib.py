@@ -94,6 +94,26 @@ class FctpArgs(C.Structure):
     ]
 
 
+class FctpFusedPath(C.Structure):
+    _fields_ = [
+        ("off1", C.c_int32), ("off2", C.c_int32), ("d1", C.c_int32), ("d2", C.c_int32),
+        ("w_row0", C.c_int32), ("reserved", C.c_int32), ("c", C.c_float * 25), ("reserved2", C.c_float),
+    ]
+
+
+class FctpFusedTask(C.Structure):
+    _fields_ = [("out_off", C.c_int32), ("num_paths", C.c_int32), ("paths", FctpFusedPath * 4)]
+
+
+class FctpFusedArgs(C.Structure):
+    _fields_ = [
+        ("x1", C.c_void_p), ("x2", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p),
+        ("ld1", C.c_int64), ("ld2", C.c_int64), ("ldo", C.c_int64), ("batch", C.c_int64), ("w_rows", C.c_int64),
+        ("out_dtype", C.c_int32), ("num_tasks", C.c_int32),
+        ("tasks", C.POINTER(FctpFusedTask)), ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -143,10 +163,11 @@ def lib() -> C.CDLL:
     L.cueq_b200_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
     L.cueq_b200_fctp_build_z.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     L.cueq_b200_fctp_consume_gz.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
+    L.cueq_b200_fctp_fused_forward.argtypes = [C.POINTER(FctpFusedArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     L.cueq_b200_sizeof.restype = C.c_int64
-    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs)):
+    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask)):
         if L.cueq_b200_sizeof(which) != C.sizeof(struct):
             raise CueqError(f"{struct.__name__}: this binding declares {C.sizeof(struct)} bytes, the library "
                             f"{L.cueq_b200_sizeof(which)}; rebuild the library or update the binding")

@@ -28,6 +28,8 @@ extern "C" int64_t cueq_b200_sizeof(int which) {
     case 3: return sizeof(cueq_cw_noalloc_args);
     case 4: return sizeof(cueq_gemm_args);
     case 5: return sizeof(cueq_fctp_args);
+    case 6: return sizeof(cueq_fctp_fused_args);
+    case 7: return sizeof(cueq_fctp_fused_task);
     default: return -1;
   }
 }

@@ -1,0 +1,370 @@
+// Fully connected ("uvw") tensor product with the coupled operand built on chip.
+//
+// For a path (l1, l2, l3) of ``uvw,iu,jv,kw+ijk`` (descriptor:
+// cuequivariance/group_theory/descriptors/irreps_tp.py:22-91; executor call site:
+// cuequivariance_torch/primitives/segmented_polynomial_fused_tp.py:51-72) with coupling C[i,j,k]:
+//
+//   out[z,k,w] = sum_paths sum_(u,v) Z[z,k,(u,v)] * W[(u,v),w],   Z[z,k,(u,v)] = sum_ij C[i,j,k] x1[z,i,u] x2[z,j,v]
+//
+// Z has 64 x 64 columns per (sample, component); writing it to memory costs 2.4 GB per pass at
+// 32,768 samples.  Here it never leaves the SM: producer warps compute one [128 samples x 64 (u
+// fixed, all v)] slice at a time directly into 128-byte-swizzled shared memory in the layout
+// tcgen05.mma expects for a K-major A operand, the matching [64 x 64] slice of W arrives by TMA,
+// one thread issues the MMAs into a TMEM accumulator, and four epilogue warps write the finished
+// [128 x 64] block of the output.  One CTA owns (output irrep, component k, 128 samples) and runs
+// over all paths that end in that irrep, so every output element is written exactly once.
+//
+// Warp roles: 0 = TMA (W slices), 1 = MMA issue + TMEM owner, 2-5 = epilogue, 6-13 = producers.
+// Every wait is bounded; a wait that runs out records status 2, the thread stops waiting and
+// working but keeps arriving on barriers, so the CTA always reaches its end and frees its TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace cueq_tc;
+
+constexpr int FM = 128;                 // samples per CTA (MMA M)
+constexpr int FN = 64;                  // w extent (MMA N)
+constexpr int FK = 64;                  // K per stage: one u, all 64 v
+constexpr int kStagesF = 6;             // A ring: tiles written by the producer warps (short latency)
+constexpr int kStagesB = 8;             // B ring: W slices fetched by TMA (L2 latency: needs the deeper lookahead)
+constexpr int kTileAF = FM * FK * 2;    // 16 KiB
+constexpr int kTileBF = FK * FN * 2;    // 8 KiB
+constexpr int kStageF = kTileAF;
+constexpr int kProducers = 256;
+constexpr int kThreadsF = 64 + 128 + kProducers;
+
+struct FwdParams {
+  const __nv_bfloat16* x1;
+  const __nv_bfloat16* x2;
+  void* out;
+  int64_t ld1, ld2, ldo, batch;
+  int out_bf16;
+  int* status;
+  cueq_fctp_fused_task tasks[CUEQ_FCTP_FUSED_MAX_TASKS];
+};
+
+__device__ __forceinline__ void producers_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kProducers) : "memory"); }
+__device__ __forceinline__ void bar_arrive(unsigned long long* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ float bf16_lo(unsigned w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(unsigned w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ unsigned hfma2_bits(unsigned a, unsigned b, unsigned c) {
+  unsigned d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned hmul2_bits(unsigned a, unsigned b) {
+  unsigned d;
+  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ unsigned pack_same(float t) {
+  unsigned d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %1;\n" : "=r"(d) : "f"(t));
+  return d;
+}
+
+// The 64 stage items (u = 0..63) of one path for this CTA's component k.  `ptid` in [0, 256): a
+// warp covers 16 sample rows; the 2 lanes of a row each own 32 of the 64 v (four 16-byte chunks)
+// and keep that part of x2[z, j, v] in registers for the whole path (only the NJ columns j for
+// which C[:, j, k] is not all zero), so the only shared-memory traffic of an item is the A tile
+// itself.  The 2 lanes take turns computing T[j] = sum_i C[i,j,k] x1[z,i,u] for 2 consecutive u
+// and exchange the values with shuffles.  `coef[i * 5 + jj]` holds C[i, active[jj], k].
+template <int D1, int NJ>
+__device__ __forceinline__ void produce_items(const FwdParams& p, const cueq_fctp_fused_path& path, unsigned char* stages,
+                                              const float* coef, const int* active, unsigned long long* full,
+                                              unsigned long long* empty, int item0, bool& dead, int64_t z0, int ptid) {
+  const int lane = ptid & 31;
+  const int row = (ptid >> 5) * 16 + (lane >> 1), half = lane & 1;
+  const int64_t z = z0 + row;
+  const bool valid = z < p.batch;
+  const unsigned short* x1row = reinterpret_cast<const unsigned short*>(p.x1 + (valid ? z : 0) * p.ld1 + path.off1);
+  uint4 x2r[4][NJ];
+#pragma unroll
+  for (int jj = 0; jj < NJ; ++jj) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.x2 + (valid ? z : 0) * p.ld2 + path.off2 + active[jj] * 64) + half * 4;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) x2r[cc][jj] = valid ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
+  }
+  float cf[D1][NJ];
+#pragma unroll
+  for (int i = 0; i < D1; ++i)
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) cf[i][jj] = coef[i * 5 + jj];
+  const int swz = row & 7;
+  unsigned short xn[D1];
+#pragma unroll
+  for (int i = 0; i < D1; ++i) xn[i] = valid ? __ldg(x1row + i * 64 + half) : (unsigned short)0;
+  for (int u0 = 0; u0 < FK; u0 += 2) {
+    unsigned tmine[NJ];
+    {
+      float xf[D1];
+#pragma unroll
+      for (int i = 0; i < D1; ++i) xf[i] = bf16_lo(xn[i]);
+      if (u0 + 2 < FK) {
+#pragma unroll
+        for (int i = 0; i < D1; ++i) xn[i] = valid ? __ldg(x1row + i * 64 + u0 + 2 + half) : (unsigned short)0;
+      }
+#pragma unroll
+      for (int jj = 0; jj < NJ; ++jj) {
+        float t = cf[0][jj] * xf[0];
+#pragma unroll
+        for (int i = 1; i < D1; ++i) t = fmaf(cf[i][jj], xf[i], t);
+        tmine[jj] = pack_same(t);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      unsigned t2[NJ];
+#pragma unroll
+      for (int jj = 0; jj < NJ; ++jj) t2[jj] = __shfl_sync(0xffffffffu, tmine[jj], (lane & ~1) + q);
+      const int item = item0 + u0 + q;
+      const int s = item % kStagesF;
+      if (!dead) dead = !bar_wait(empty + s, ((item / kStagesF) & 1) ^ 1, p.status);
+      if (!dead) {
+        unsigned char* arow = stages + s * kStageF + row * 128;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint4 acc;
+          acc.x = hmul2_bits(t2[0], x2r[cc][0].x);
+          acc.y = hmul2_bits(t2[0], x2r[cc][0].y);
+          acc.z = hmul2_bits(t2[0], x2r[cc][0].z);
+          acc.w = hmul2_bits(t2[0], x2r[cc][0].w);
+#pragma unroll
+          for (int jj = 1; jj < NJ; ++jj) {
+            acc.x = hfma2_bits(t2[jj], x2r[cc][jj].x, acc.x);
+            acc.y = hfma2_bits(t2[jj], x2r[cc][jj].y, acc.y);
+            acc.z = hfma2_bits(t2[jj], x2r[cc][jj].z, acc.z);
+            acc.w = hfma2_bits(t2[jj], x2r[cc][jj].w, acc.w);
+          }
+          *reinterpret_cast<uint4*>(arow + (((half * 4 + cc) ^ swz) << 4)) = acc;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+      __syncwarp();
+      if (lane == 0) bar_arrive(full + s);
+    }
+  }
+}
+
+// Compacts the path's coupling columns (thread 0), then runs the item loop specialised on the
+// number of active columns.
+template <int D1>
+__device__ __forceinline__ void produce_path(const FwdParams& p, const cueq_fctp_fused_path& path, unsigned char* stages,
+                                             float* coef, int* active, unsigned long long* full, unsigned long long* empty,
+                                             int item0, bool& dead, int64_t z0, int ptid) {
+  producers_sync();  // every producer has finished with the previous path's tables
+  if (ptid == 0) {
+    int nj = 0;
+    for (int j = 0; j < path.d2; ++j) {
+      bool any = false;
+      for (int i = 0; i < D1; ++i) any |= path.c[i * 5 + j] != 0.f;
+      if (any || (j == path.d2 - 1 && nj == 0)) {
+        for (int i = 0; i < D1; ++i) coef[i * 5 + nj] = path.c[i * 5 + j];
+        active[nj++] = j;
+      }
+    }
+    active[7] = nj;
+  }
+  producers_sync();
+  switch (active[7]) {
+    case 1: produce_items<D1, 1>(p, path, stages, coef, active, full, empty, item0, dead, z0, ptid); break;
+    case 2: produce_items<D1, 2>(p, path, stages, coef, active, full, empty, item0, dead, z0, ptid); break;
+    case 3: produce_items<D1, 3>(p, path, stages, coef, active, full, empty, item0, dead, z0, ptid); break;
+    case 4: produce_items<D1, 4>(p, path, stages, coef, active, full, empty, item0, dead, z0, ptid); break;
+    default: produce_items<D1, 5>(p, path, stages, coef, active, full, empty, item0, dead, z0, ptid); break;
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                         const __grid_constant__ FwdParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* ringB = smem + kStagesF * kStageF;
+  float* coef = reinterpret_cast<float*>(ringB + kStagesB * kTileBF);
+  int* active = reinterpret_cast<int*>(coef + 32);   // active[0..4]: column ids, active[7]: their count
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(active + 8);
+  unsigned long long* empty = full + kStagesF;
+  unsigned long long* fullB = empty + kStagesF;
+  unsigned long long* emptyB = fullB + kStagesB;
+  unsigned long long* acc_ready = emptyB + kStagesB;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const cueq_fctp_fused_task& task = p.tasks[blockIdx.y];
+  const int64_t z0 = (int64_t)blockIdx.x * FM;
+  const int total_items = task.num_paths * (FK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesF; ++s) { bar_init(full + s, kProducers / 32); bar_init(empty + s, 1); }
+    for (int s = 0; s < kStagesB; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
+    bar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(64u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int item = 0; item < total_items; ++item) {
+        const int s = item % kStagesB;
+        if (!bar_wait(emptyB + s, ((item / kStagesB) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(fullB + s, kTileBF);
+        const int row0 = task.paths[item / FK].w_row0 + (item % FK) * FK;
+        tma_load_2d(ringB + s * kTileBF, &map_w, 0, row0, fullB + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // D = f32, A = B = bf16, A K-major, B MN-major ([K = (u,v)][N = w], w contiguous), N = 64, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(FN >> 3) << 17) | ((unsigned)(FM >> 4) << 24);
+      for (int item = 0; item < total_items; ++item) {
+        const int s = item % kStagesF, sb = item % kStagesB;
+        if (!bar_wait(fullB + sb, (item / kStagesB) & 1, p.status)) break;
+        if (!bar_wait(full + s, (item / kStagesF) & 1, p.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned long long da = smem_desc(smem + s * kStageF);
+        const unsigned long long db = smem_desc_mn(ringB + sb * kTileBF);
+#pragma unroll
+        for (int kk = 0; kk < FK / 16; ++kk) umma_bf16(tmem_base, da + 2ull * kk, db + 128ull * kk, idesc, (item | kk) != 0 ? 1u : 0u);
+        umma_commit(empty + s);
+        umma_commit(emptyB + sb);
+      }
+      umma_commit(acc_ready);
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    const bool ok = bar_wait(acc_ready, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int64_t z = z0 + q * 32 + lane;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      unsigned v[32];
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + half * 32;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                   "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                   "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                     "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                     "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                     "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      if (ok && z < p.batch) {
+        const int64_t off = z * p.ldo + task.out_off + half * 32;
+        if (p.out_bf16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * t]), __uint_as_float(v[c + 2 * t + 1]));
+            *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<uint4*>(h);
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.out) + off;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(dst + c) = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+        }
+      }
+    }
+  } else {
+    const int ptid = threadIdx.x - 192;
+    bool dead = false;
+    for (int pi = 0; pi < task.num_paths; ++pi) {
+      const int item = pi * FK;
+      const cueq_fctp_fused_path& path = task.paths[pi];
+      switch (path.d1) {
+        case 1: produce_path<1>(p, path, smem, coef, active, full, empty, item, dead, z0, ptid); break;
+        case 3: produce_path<3>(p, path, smem, coef, active, full, empty, item, dead, z0, ptid); break;
+        case 5: produce_path<5>(p, path, smem, coef, active, full, empty, item, dead, z0, ptid); break;
+        default: break;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(64u) : "memory");
+  }
+}
+
+// W as a 2-D bf16 array [rows = (path, u, v)][64 w]; one box = 64 rows x 64 columns.
+int make_w_map(CUtensorMap* map, const void* base, int64_t rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cueq::fail("fctp fused: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)FN, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)FN * 2};
+  cuuint32_t box[2] = {(cuuint32_t)FN, (cuuint32_t)FK};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cueq::fail("fctp fused: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+int check_tasks(const cueq_fctp_fused_args* a) {
+  if (a->num_tasks < 1 || a->num_tasks > CUEQ_FCTP_FUSED_MAX_TASKS) return cueq::fail("fctp fused: between 1 and %d tasks", CUEQ_FCTP_FUSED_MAX_TASKS);
+  for (int t = 0; t < a->num_tasks; ++t) {
+    const cueq_fctp_fused_task& task = a->tasks[t];
+    if (task.num_paths < 1 || task.num_paths > CUEQ_FCTP_FUSED_MAX_PATHS) return cueq::fail("fctp fused: task %d has %d paths (1..%d)", t, task.num_paths, CUEQ_FCTP_FUSED_MAX_PATHS);
+    if (task.out_off < 0 || (task.out_off % 8)) return cueq::fail("fctp fused: output offsets must be multiples of 8 elements");
+    for (int q = 0; q < task.num_paths; ++q) {
+      const cueq_fctp_fused_path& path = task.paths[q];
+      const bool okd = (path.d1 == 1 || path.d1 == 3 || path.d1 == 5) && (path.d2 == 1 || path.d2 == 3 || path.d2 == 5);
+      if (!okd) return cueq::fail("fctp fused: irrep dimensions must be 1, 3 or 5 (task %d path %d: %d, %d)", t, q, path.d1, path.d2);
+      if ((path.off1 % 8) || (path.off2 % 8) || path.off1 < 0 || path.off2 < 0) return cueq::fail("fctp fused: segment offsets must be multiples of 8 elements");
+      if (path.w_row0 < 0 || (int64_t)path.w_row0 + FK * FK > a->w_rows) return cueq::fail("fctp fused: weight block of task %d path %d is outside the weight array", t, q);
+    }
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* a, void* stream) {
+  if (!a || !a->x1 || !a->x2 || !a->w || !a->out || !a->tasks) return cueq::fail("fctp fused: null argument");
+  if (a->batch <= 0) return 0;
+  if (int rc = check_tasks(a)) return rc;
+  if ((a->ld1 % 8) || (a->ld2 % 8) || (a->ldo % 8)) return cueq::fail("fctp fused: row pitches must be multiples of 8 elements");
+  if (((uintptr_t)a->x1 | (uintptr_t)a->x2 | (uintptr_t)a->w | (uintptr_t)a->out) & 15) return cueq::fail("fctp fused: operands must be 16-byte aligned");
+  if (a->out_dtype != CUEQ_F32 && a->out_dtype != CUEQ_BF16) return cueq::fail("fctp fused: output must be float32 or bfloat16");
+  CUtensorMap mw;
+  if (int rc = make_w_map(&mw, a->w, a->w_rows)) return rc;
+  FwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x1 = reinterpret_cast<const __nv_bfloat16*>(a->x1);
+  p.x2 = reinterpret_cast<const __nv_bfloat16*>(a->x2);
+  p.out = a->out;
+  p.ld1 = a->ld1; p.ld2 = a->ld2; p.ldo = a->ldo; p.batch = a->batch;
+  p.out_bf16 = a->out_dtype == CUEQ_BF16;
+  p.status = reinterpret_cast<int*>(a->status);
+  std::memcpy(p.tasks, a->tasks, sizeof(cueq_fctp_fused_task) * a->num_tasks);
+  const size_t smem = kStagesF * kStageF + kStagesB * kTileBF + 160 + 40 * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_tasks);
+  fctp_fused_forward_kernel<<<grid, kThreadsF, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mw, p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}

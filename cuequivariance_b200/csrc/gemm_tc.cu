@@ -17,64 +17,17 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace {
+
+using namespace cueq_tc;
 
 constexpr int BM = 128, BN = 64, BK = 64;       // tile; BK bf16 = 128 bytes = one swizzle row
 constexpr int kStagesTc = 4;
 constexpr int kTileA = BM * BK * 2, kTileB = BN * BK * 2;
 constexpr int kStageBytes = kTileA + kTileB;
 constexpr int kThreads = 192;                   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int kSpin = 1 << 22;
-
-__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void bar_init(unsigned long long* b, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(b)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_expect_tx(unsigned long long* b, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool bar_try(unsigned long long* b, unsigned parity) {
-  unsigned ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// returns false (and records it) if the barrier did not flip within the spin budget
-// (non-blocking polls with a short sleep: at most a few tenths of a second in total)
-__device__ __forceinline__ bool bar_wait(unsigned long long* b, unsigned parity, int* status) {
-  for (int i = 0; i < kSpin; ++i) {
-    if (bar_try(b, parity)) return true;
-    if (i > 64) __nanosleep(64);
-  }
-  if (status) atomicExch(status, 2);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-               ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
-  // K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart; version 1 (Blackwell)
-  const unsigned long long addr = (s32(p) & 0x3FFFFu) >> 4;
-  return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ unsigned long long smem_desc_mn(const void* p) {
-  // MN-major, 128-byte swizzle: the tile is stored as blocks of [64 K-rows][64 elements along M/N]
-  // (8 KiB each, rows of 128 bytes); groups of 8 K-rows are 1024 bytes apart (stride offset),
-  // consecutive 64-element blocks along M/N are 8192 bytes apart (leading offset)
-  const unsigned long long addr = (s32(p) & 0x3FFFFu) >> 4;
-  return addr | ((8192ull >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-               ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(s32(bar)) : "memory");
-}
 
 struct GemmParams {
   void* C;
@@ -215,21 +168,6 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(64u) : "memory");
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 // K-major operand: global [rows][cols = K] with `ld` elements between rows; box = 64 K x box_rows.

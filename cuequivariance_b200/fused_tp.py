@@ -34,6 +34,7 @@ from .executor import Uniform1dProgram
 from .polynomial import Polynomial
 
 FLATTEN_LIMIT = 20000  # flattened paths above which the composite route is taken
+FUSED = True  # fully connected tensor-core route: build the coupled operand on chip when the shape allows
 
 
 def _flatten_all_but_inner(poly: Polynomial) -> Polynomial:
@@ -108,9 +109,14 @@ class _TensorCoreUVW(torch.autograd.Function):
         d, off = owner.d, owner.offsets
         B = x1.shape[0]
         dev = x1.device
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if FUSED and owner._fused_tasks() is not None:
+            out = owner._fused_forward(w, x1, x2, status)
+            ctx.owner, ctx.status = owner, status
+            ctx.save_for_backward(w, x1, x2)
+            return out.to(x1.dtype)
         x1c, x2c = owner._as_kernel_input(x1), owner._as_kernel_input(x2)
         out = torch.zeros((B, owner.out_size), dtype=torch.float32, device=dev)
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
         seen = set()
         for k, p in enumerate(d.paths):
             sw, s1, s2, so = p.indices
@@ -209,6 +215,67 @@ class DenseUVW:
             if (U * V) % 128 or Wd % 64 or V % 2 or max(p.coefficients.shape) > 7:
                 return False
         return True
+
+    # -- fused route: coupled operand built in shared memory ------------------------------------
+    def _fused_tasks(self):
+        """Task table for the fused kernels, or None if the shape is outside what they cover
+        (all multiplicities 64, irrep dimensions 1/3/5, at most 4 paths per output irrep)."""
+        if hasattr(self, "_tasks"):
+            return self._tasks
+        from . import _lib
+
+        d, off = self.d, self.offsets
+        self._tasks = None
+        by_out = {}
+        for p in d.paths:
+            sw, s1, s2, so = p.indices
+            if tuple(d.operands[0].segments[sw]) != (64, 64, 64):
+                return None
+            d1, d2, d3 = p.coefficients.shape
+            if d1 not in (1, 3, 5) or d2 not in (1, 3, 5) or off[0][sw] % 64:
+                return None
+            by_out.setdefault(so, []).append(p)
+        tasks = []
+        for so, paths in sorted(by_out.items()):
+            if len(paths) > 4:
+                return None
+            d3 = paths[0].coefficients.shape[2]
+            for k in range(d3):
+                t = _lib.FctpFusedTask()
+                t.out_off, t.num_paths = off[3][so] + k * 64, len(paths)
+                for q, p in enumerate(paths):
+                    sw, s1, s2, _ = p.indices
+                    fp = t.paths[q]
+                    fp.off1, fp.off2 = off[1][s1], off[2][s2]
+                    fp.d1, fp.d2, fp.w_row0 = p.coefficients.shape[0], p.coefficients.shape[1], off[0][sw] // 64
+                    for i in range(fp.d1):
+                        for j in range(fp.d2):
+                            fp.c[i * 5 + j] = float(p.coefficients[i, j, k])
+                tasks.append(t)
+        if len(tasks) > 12 or len(by_out) != d.operands[3].num_segments:
+            return None
+        self._tasks = (_lib.FctpFusedTask * len(tasks))(*tasks)
+        return self._tasks
+
+    def _fused_forward(self, w, x1, x2, status):
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        tasks = self._fused_tasks()
+        B = x1.shape[0]
+        x1c, x2c = x1.to(torch.bfloat16).contiguous(), x2.to(torch.bfloat16).contiguous()
+        w16 = w.reshape(-1, 64).to(torch.bfloat16).contiguous()
+        out = torch.empty((B, self.out_size), dtype=torch.float32, device=x1.device)
+        a = _lib.FctpFusedArgs()
+        a.x1, a.x2, a.w, a.out = x1c.data_ptr(), x2c.data_ptr(), w16.data_ptr(), out.data_ptr()
+        a.ld1, a.ld2, a.ldo, a.batch, a.w_rows = x1c.shape[1], x2c.shape[1], out.shape[1], B, w16.shape[0]
+        a.out_dtype, a.num_tasks = _lib.F32, len(tasks)
+        a.tasks = C.cast(tasks, C.POINTER(_lib.FctpFusedTask))
+        a.status = status.data_ptr()
+        with profiling.kernel("fctp_fused_forward"):
+            _lib.check(_lib.lib().cueq_b200_fctp_fused_forward(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
 
     @staticmethod
     def _as_kernel_input(x):

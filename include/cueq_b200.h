@@ -74,7 +74,8 @@ int cueq_b200_abi_version(void);
 const char* cueq_b200_last_error(void);
 /* sizeof() of an argument block as this library was compiled, so that a binding can check its own
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
-   3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args; -1 for any other number. */
+   3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
+   7 cueq_fctp_fused_task; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -234,6 +235,48 @@ typedef struct {
 } cueq_fctp_args;
 int cueq_b200_fctp_build_z(const cueq_fctp_args* args, void* stream);
 int cueq_b200_fctp_consume_gz(const cueq_fctp_args* args, void* stream);
+
+/* ---- fully connected product with the coupled operand built on chip ---------------------------
+ *
+ * Same operation as build_z + GEMM (+ consume_gz) above - the dense contraction behind
+ * FusedTensorProductOp4 (cuequivariance_torch/primitives/segmented_polynomial_fused_tp.py:51-72)
+ * for the descriptor uvw,iu,jv,kw+ijk (cuequivariance/group_theory/descriptors/irreps_tp.py:22-91) -
+ * but Z = C . x1 . x2 is produced tile by tile in shared memory as the tensor-core operand and is
+ * never written to device memory.  Restrictions: all three multiplicities are 64, irrep dimensions
+ * 1, 3 or 5, x1 / x2 / W in bfloat16, rows in ir_mul layout (component-major blocks of 64).
+ *
+ * A task is one (output irrep, component k): `out_off` = offset of that component's 64 outputs in
+ * an output row; its paths are all the paths that end in that irrep, each with the offsets of its
+ * x1 / x2 segments, the first row of its [4096, 64] weight block inside W (W is one bf16 array
+ * [w_rows, 64], row = (u * 64 + v) within a block) and c[i * 5 + j] = C[i, j, k] (normalisation
+ * included).  Forward writes every task's [batch, 64] block once (no accumulation). */
+#define CUEQ_FCTP_FUSED_MAX_TASKS 12
+#define CUEQ_FCTP_FUSED_MAX_PATHS 4
+typedef struct {
+  int32_t off1, off2;   /* element offsets of the path's x1 / x2 segments inside a row            */
+  int32_t d1, d2;       /* irrep dimensions of x1 / x2 for this path                               */
+  int32_t w_row0;       /* first row of the path's weight block in W                               */
+  int32_t reserved;
+  float c[25];          /* C[i, j, k] for the task's k at c[i * 5 + j]                             */
+  float reserved2;
+} cueq_fctp_fused_path;
+typedef struct {
+  int32_t out_off;      /* element offset inside an output row                                     */
+  int32_t num_paths;    /* 1 .. CUEQ_FCTP_FUSED_MAX_PATHS                                          */
+  cueq_fctp_fused_path paths[CUEQ_FCTP_FUSED_MAX_PATHS];
+} cueq_fctp_fused_task;
+typedef struct {
+  const void* x1;       /* device bf16 [batch, ld1]                                                */
+  const void* x2;       /* device bf16 [batch, ld2]                                                */
+  const void* w;        /* device bf16 [w_rows, 64]                                                */
+  void* out;            /* device float32 or bf16 [batch, ldo]                                     */
+  int64_t ld1, ld2, ldo, batch, w_rows;
+  int32_t out_dtype;    /* CUEQ_F32 or CUEQ_BF16                                                   */
+  int32_t num_tasks;    /* 1 .. CUEQ_FCTP_FUSED_MAX_TASKS                                          */
+  const cueq_fctp_fused_task* tasks;  /* HOST array, copied into the launch parameters            */
+  void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
+} cueq_fctp_fused_args;
+int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* args, void* stream);
 
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *
