@@ -114,6 +114,22 @@ class FctpFusedArgs(C.Structure):
     ]
 
 
+class FctpFusedUnit(C.Structure):
+    _fields_ = [
+        ("offa", C.c_int32), ("offb", C.c_int32), ("da", C.c_int32), ("db", C.c_int32),
+        ("w_row0", C.c_int32), ("nk", C.c_int32), ("goff", C.c_int32 * 2), ("c", (C.c_float * 25) * 2),
+    ]
+
+
+class FctpFusedGxArgs(C.Structure):
+    _fields_ = [
+        ("xb", C.c_void_p), ("gout", C.c_void_p), ("w", C.c_void_p), ("gxa", C.c_void_p),
+        ("ldb", C.c_int64), ("ldg", C.c_int64), ("lda", C.c_int64), ("batch", C.c_int64), ("w_rows", C.c_int64),
+        ("num_units", C.c_int32), ("reserved", C.c_int32),
+        ("units", C.POINTER(FctpFusedUnit)), ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -164,10 +180,11 @@ def lib() -> C.CDLL:
     L.cueq_b200_fctp_build_z.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     L.cueq_b200_fctp_consume_gz.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     L.cueq_b200_fctp_fused_forward.argtypes = [C.POINTER(FctpFusedArgs), C.c_void_p]
+    L.cueq_b200_fctp_fused_gx.argtypes = [C.POINTER(FctpFusedGxArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     L.cueq_b200_sizeof.restype = C.c_int64
-    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask)):
+    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask, FctpFusedGxArgs, FctpFusedUnit)):
         if L.cueq_b200_sizeof(which) != C.sizeof(struct):
             raise CueqError(f"{struct.__name__}: this binding declares {C.sizeof(struct)} bytes, the library "
                             f"{L.cueq_b200_sizeof(which)}; rebuild the library or update the binding")

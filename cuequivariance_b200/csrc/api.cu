@@ -30,6 +30,8 @@ extern "C" int64_t cueq_b200_sizeof(int which) {
     case 5: return sizeof(cueq_fctp_args);
     case 6: return sizeof(cueq_fctp_fused_args);
     case 7: return sizeof(cueq_fctp_fused_task);
+    case 8: return sizeof(cueq_fctp_fused_gx_args);
+    case 9: return sizeof(cueq_fctp_fused_unit);
     default: return -1;
   }
 }

@@ -337,6 +337,249 @@ int check_tasks(const cueq_fctp_fused_args* a) {
   return 0;
 }
 
+
+// ---- gradient with respect to one of the two data operands -------------------------------------
+//
+//   gXa[z, ia, a] += sum_k sum_jb C[ia, jb, k] * sum_b gZ[z, k, (a, b)] * xb[z, jb, b],
+//   gZ[z, k, (a, b)] = sum_w gout[z, k, w] * W[(a, b), w]
+//
+// ("a" = the operand being differentiated, "b" = the other one; for x2 the caller passes a copy
+// of W with rows ordered (v, u) and the transposed coupling table).  gZ is a [128 samples x 256
+// (4 a, 64 b)] tile of a GEMM with K = 64: gout tile (K-major A, TMA) x W rows (K-major B, TMA),
+// accumulated in TMEM (two 256-column buffers, so that the next tile's MMAs overlap the reduction
+// of the current one).  Consumer warps read the tile back with tcgen05.ld and fold it against xb
+// (held in shared memory) on the CUDA cores; gZ never exists in memory.
+// One CTA owns (path, up to two components k, 128 samples).
+// Warp roles: 0 = TMA, 1 = MMA issue + TMEM owner, 2-9 = consumers (lane quadrant = warp % 4,
+// a-pair = (warp - 2) / 4).
+constexpr int GN = 256;                       // columns per tile: 4 a x 64 b
+constexpr int kStagesG = 3;                   // W-row ring (32 KiB each)
+constexpr int kTileBG = GN * 64 * 2;          // 32 KiB
+constexpr int kMaxKG = 2;                     // components per CTA
+constexpr int kConsumers = 256;
+constexpr int kThreadsG = 64 + kConsumers;
+constexpr int kXPitch = 5 * 128 + 16;
+constexpr int kXTile = FM * kXPitch;
+
+struct GxParams {
+  const __nv_bfloat16* xb;
+  float* gxa;
+  int64_t ldb, lda, batch;
+  int* status;
+  cueq_fctp_fused_unit units[CUEQ_FCTP_FUSED_MAX_UNITS];
+};
+
+__device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 2, %0;\n" ::"n"(kConsumers) : "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr));
+}
+
+// Folds one [row, 2 a, 64 b] strip of a gZ tile against the NJ active rows of xb:
+// r[a2][jj] = sum_b gZ[a2, b] * xb[act[jj], b].
+template <int NJ>
+__device__ __forceinline__ void fold_tile(unsigned tcol, const unsigned char* xrow, const int* act, float (&r)[2][5]) {
+#pragma unroll
+  for (int a2 = 0; a2 < 2; ++a2)
+#pragma unroll
+    for (int jj = 0; jj < 5; ++jj) r[a2][jj] = 0.f;
+#pragma unroll
+  for (int vh = 0; vh < 2; ++vh) {
+    unsigned g0[32], g1[32];
+    tmem_ld32(tcol + vh * 32, g0);
+    tmem_ld32(tcol + 64 + vh * 32, g1);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+#pragma unroll
+      for (int jj = 0; jj < NJ; ++jj) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xrow + act[jj] * 128 + (vh * 4 + c4) * 16);
+        const unsigned wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = bf16_lo(wds[e]), hi = bf16_hi(wds[e]);
+          r[0][jj] = fmaf(__uint_as_float(g0[c4 * 8 + 2 * e]), lo, r[0][jj]);
+          r[0][jj] = fmaf(__uint_as_float(g0[c4 * 8 + 2 * e + 1]), hi, r[0][jj]);
+          r[1][jj] = fmaf(__uint_as_float(g1[c4 * 8 + 2 * e]), lo, r[1][jj]);
+          r[1][jj] = fmaf(__uint_as_float(g1[c4 * 8 + 2 * e + 1]), hi, r[1][jj]);
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsG, 1) fctp_fused_gx_kernel(const __grid_constant__ CUtensorMap map_g,
+                                                                    const __grid_constant__ CUtensorMap map_w,
+                                                                    const __grid_constant__ GxParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* tilesA = smem;                                 // kMaxKG gout tiles, 16 KiB each
+  unsigned char* ringB = tilesA + kMaxKG * kTileAF;             // W rows
+  unsigned char* xtile = ringB + kStagesG * kTileBG;            // xb rows of the 128 samples, bf16, padded pitch
+  float* coef = reinterpret_cast<float*>(xtile + kXTile);       // [kMaxKG][25] compacted: coef[k][ia * 5 + jj]
+  int* act = reinterpret_cast<int*>(coef + kMaxKG * 25 + 2);    // [kMaxKG][8]: active jb ids, [7] = their count
+  unsigned long long* fullA = reinterpret_cast<unsigned long long*>(act + kMaxKG * 8);
+  unsigned long long* fullB = fullA + 1;
+  unsigned long long* emptyB = fullB + kStagesG;
+  unsigned long long* accfull = emptyB + kStagesG;
+  unsigned long long* accempty = accfull + 2;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(accempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const cueq_fctp_fused_unit& unit = p.units[blockIdx.y];
+  const int64_t z0 = (int64_t)blockIdx.x * FM;
+  const int nk = unit.nk;
+  constexpr int kGroups = 16;   // 64 a in groups of 4
+
+  if (threadIdx.x == 0) {
+    bar_init(fullA, 1);
+    for (int s = 0; s < kStagesG; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
+    for (int b = 0; b < 2; ++b) { bar_init(accfull + b, 1); bar_init(accempty + b, kConsumers / 32); }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // compact the coupling columns of every component of this CTA
+    for (int t = 0; t < kMaxKG * 25; ++t) coef[t] = 0.f;
+    for (int k = 0; k < nk; ++k) {
+      int nj = 0;
+      for (int j = 0; j < unit.db; ++j) {
+        bool any = false;
+        for (int i = 0; i < unit.da; ++i) any |= unit.c[k][i * 5 + j] != 0.f;
+        if (any || (j == unit.db - 1 && nj == 0)) {
+          for (int i = 0; i < 5; ++i) coef[k * 25 + i * 5 + nj] = i < unit.da ? unit.c[k][i * 5 + j] : 0.f;
+          act[k * 8 + nj++] = j;
+        }
+      }
+      act[k * 8 + 7] = nj;
+    }
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bar_expect_tx(fullA, nk * kTileAF);
+      for (int k = 0; k < nk; ++k) tma_load_2d(tilesA + k * kTileAF, &map_g, unit.goff[k], (int)z0, fullA);
+      for (int g = 0; g < kGroups; ++g) {
+        const int s = g % kStagesG;
+        if (!bar_wait(emptyB + s, ((g / kStagesG) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(fullB + s, kTileBG);
+        tma_load_2d(ringB + s * kTileBG, &map_w, 0, unit.w_row0 + g * GN, fullB + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // D = f32, A = B = bf16, both K-major, N = 256, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(GN >> 3) << 17) | ((unsigned)(FM >> 4) << 24);
+      bool ok = bar_wait(fullA, 0, p.status);
+      int t = 0;
+      for (int g = 0; g < kGroups && ok; ++g) {
+        const int s = g % kStagesG;
+        ok = bar_wait(fullB + s, (g / kStagesG) & 1, p.status);
+        for (int k = 0; k < nk && ok; ++k, ++t) {
+          const int buf = t & 1;
+          ok = bar_wait(accempty + buf, ((t >> 1) & 1) ^ 1, p.status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned long long da = smem_desc(tilesA + k * kTileAF);
+          const unsigned long long db = smem_desc(ringB + s * kTileBG);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem_base + buf * GN, da + 2ull * kk, db + 2ull * kk, idesc, kk != 0 ? 1u : 0u);
+          umma_commit(accfull + buf);
+        }
+        umma_commit(emptyB + s);
+      }
+    }
+  } else {
+    const int ctid = threadIdx.x - 64;
+    const int q = warp & 3, ah = (warp - 2) >> 2;          // lane quadrant, which pair of the group's 4 a
+    const int row = q * 32 + lane;
+    const int64_t z = z0 + row;
+    const bool valid = z < p.batch;
+    const int pitch = unit.db * 128 + 16;
+    for (int idx = ctid; idx < FM * unit.db * 8; idx += kConsumers) {
+      const int r = idx / (unit.db * 8), c = idx % (unit.db * 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (z0 + r < p.batch) v = __ldg(reinterpret_cast<const uint4*>(p.xb + (z0 + r) * p.ldb + unit.offb) + c);
+      *reinterpret_cast<uint4*>(xtile + r * pitch + c * 16) = v;
+    }
+    consumers_sync();
+    const unsigned char* xrow = xtile + row * pitch;
+    bool dead = false;
+    int t = 0;
+    for (int g = 0; g < kGroups; ++g) {
+      float gacc[5][2];
+#pragma unroll
+      for (int i = 0; i < 5; ++i) gacc[i][0] = gacc[i][1] = 0.f;
+      for (int k = 0; k < nk; ++k, ++t) {
+        const int buf = t & 1;
+        if (!dead) dead = !bar_wait(accfull + buf, (t >> 1) & 1, p.status);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        float r[2][5];
+        const unsigned tcol = tmem_base + ((unsigned)(q * 32) << 16) + buf * GN + ah * 128;
+        const int* actk = act + k * 8;
+        switch (actk[7]) {
+          case 1: fold_tile<1>(tcol, xrow, actk, r); break;
+          case 2: fold_tile<2>(tcol, xrow, actk, r); break;
+          case 3: fold_tile<3>(tcol, xrow, actk, r); break;
+          case 4: fold_tile<4>(tcol, xrow, actk, r); break;
+          default: fold_tile<5>(tcol, xrow, actk, r); break;
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive(accempty + buf);
+        const float* ck = coef + k * 25;
+#pragma unroll
+        for (int i = 0; i < 5; ++i)
+#pragma unroll
+          for (int jj = 0; jj < 5; ++jj) {
+            const float cij = ck[i * 5 + jj];   // zero beyond the active columns / rows
+            gacc[i][0] = fmaf(cij, r[0][jj], gacc[i][0]);
+            gacc[i][1] = fmaf(cij, r[1][jj], gacc[i][1]);
+          }
+      }
+      if (valid && !dead) {
+        float* dst = p.gxa + z * p.lda + unit.offa + g * 4 + ah * 2;
+#pragma unroll
+        for (int i = 0; i < 5; ++i)
+          if (i < unit.da)
+            asm volatile("red.global.add.v2.f32 [%0], {%1, %2};\n" ::"l"(dst + i * 64), "f"(gacc[i][0]), "f"(gacc[i][1]) : "memory");
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+int make_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cueq::fail("fctp fused: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cueq::fail("fctp fused: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
 }  // namespace
 
 extern "C" int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* a, void* stream) {
@@ -365,6 +608,48 @@ extern "C" int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* a, void*
   }
   dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_tasks);
   fctp_fused_forward_kernel<<<grid, kThreadsF, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mw, p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+
+extern "C" int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* a, void* stream) {
+  if (!a || !a->xb || !a->gout || !a->w || !a->gxa || !a->units) return cueq::fail("fctp fused gx: null argument");
+  if (a->batch <= 0) return 0;
+  if (a->num_units < 1 || a->num_units > CUEQ_FCTP_FUSED_MAX_UNITS) return cueq::fail("fctp fused gx: between 1 and %d units", CUEQ_FCTP_FUSED_MAX_UNITS);
+  for (int t = 0; t < a->num_units; ++t) {
+    const cueq_fctp_fused_unit& u = a->units[t];
+    const bool okd = (u.da == 1 || u.da == 3 || u.da == 5) && (u.db == 1 || u.db == 3 || u.db == 5);
+    if (!okd) return cueq::fail("fctp fused gx: irrep dimensions must be 1, 3 or 5 (unit %d: %d, %d)", t, u.da, u.db);
+    if (u.nk < 1 || u.nk > 2) return cueq::fail("fctp fused gx: a unit covers 1 or 2 components (unit %d: %d)", t, u.nk);
+    if (u.offa < 0 || u.offb < 0 || (u.offa % 8) || (u.offb % 8)) return cueq::fail("fctp fused gx: segment offsets must be non-negative multiples of 8 elements");
+    if (u.offa + u.da * 64 > a->lda || u.offb + u.db * 64 > a->ldb) return cueq::fail("fctp fused gx: segment of unit %d exceeds the row", t);
+    for (int k = 0; k < u.nk; ++k)
+      if (u.goff[k] < 0 || (u.goff[k] % 8) || u.goff[k] + 64 > a->ldg) return cueq::fail("fctp fused gx: cotangent block of unit %d is outside the row", t);
+    if (u.w_row0 < 0 || (int64_t)u.w_row0 + 4096 > a->w_rows) return cueq::fail("fctp fused gx: weight block of unit %d is outside the weight array", t);
+  }
+  if ((a->lda % 2) || (a->ldb % 8) || (a->ldg % 8)) return cueq::fail("fctp fused gx: row pitches must keep rows aligned (xb, gout: 8 elements; gxa: 2)");
+  if (((uintptr_t)a->xb | (uintptr_t)a->gout | (uintptr_t)a->w) & 15) return cueq::fail("fctp fused gx: operands must be 16-byte aligned");
+  if ((uintptr_t)a->gxa & 7) return cueq::fail("fctp fused gx: the gradient must be 8-byte aligned");
+  if (a->batch > 2147483647LL) return cueq::fail("fctp fused gx: batch too large");
+  CUtensorMap mg, mw;
+  if (int rc = make_map_2d(&mg, a->gout, a->batch, a->ldg, a->ldg, 64, FM)) return rc;
+  if (int rc = make_map_2d(&mw, a->w, a->w_rows, 64, 64, 64, GN)) return rc;
+  GxParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.xb = reinterpret_cast<const __nv_bfloat16*>(a->xb);
+  p.gxa = reinterpret_cast<float*>(a->gxa);
+  p.ldb = a->ldb; p.lda = a->lda; p.batch = a->batch;
+  p.status = reinterpret_cast<int*>(a->status);
+  std::memcpy(p.units, a->units, sizeof(cueq_fctp_fused_unit) * a->num_units);
+  const size_t smem = kMaxKG * kTileAF + kStagesG * kTileBG + kXTile + 512 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_gx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_units);
+  fctp_fused_gx_kernel<<<grid, kThreadsG, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, mw, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

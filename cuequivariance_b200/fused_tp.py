@@ -146,14 +146,27 @@ class _TensorCoreUVW(torch.autograd.Function):
         d, off = owner.d, owner.offsets
         B, dev = x1.shape[0], x1.device
         need_w, need_x1, need_x2 = ctx.needs_input_grad[1], ctx.needs_input_grad[2], ctx.needs_input_grad[3]
+        status = ctx.status
+        fused_x = FUSED and owner._fused_tasks() is not None and owner._fused_units(1) is not None
+        gx1f = gx2f = None
+        if fused_x and (need_x1 or need_x2):
+            gout16 = gout.to(torch.bfloat16).contiguous()
+            x1b, x2b = x1.to(torch.bfloat16).contiguous(), x2.to(torch.bfloat16).contiguous()
+            if need_x1:
+                gx1f = owner._fused_gx(1, w.reshape(-1, 64).to(torch.bfloat16).contiguous(), x2b, gout16, status)
+            if need_x2:
+                wt = w.reshape(-1, 64, 64, 64).transpose(1, 2).reshape(-1, 64).to(torch.bfloat16).contiguous()
+                gx2f = owner._fused_gx(2, wt, x1b, gout16, status)
+            need_x1 = need_x2 = False
         x1c, x2c = owner._as_kernel_input(x1), owner._as_kernel_input(x2)
         gw = torch.zeros((1, w.shape[1]), dtype=torch.float32, device=dev) if need_w else None
         gx1 = torch.zeros(x1.shape, dtype=torch.float32, device=dev) if need_x1 else None
         gx2 = torch.zeros(x2.shape, dtype=torch.float32, device=dev) if need_x2 else None
-        status = ctx.status
         for k, p in enumerate(d.paths):
             sw, s1, s2, so = p.indices
             U, V, Wd = d.operands[0].segments[sw]
+            if not (need_w or need_x1 or need_x2):
+                break
             d3 = p.coefficients.shape[2]
             rows = B * d3
             rows_pad = (rows + 63) // 64 * 64
@@ -179,6 +192,10 @@ class _TensorCoreUVW(torch.autograd.Function):
                 with profiling.kernel("fctp_consume_gz"):
                     _lib.check(_lib.lib().cueq_b200_fctp_consume_gz(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
                 del gZ
+        if gx1f is not None:
+            gx1, need_x1 = gx1f, True
+        if gx2f is not None:
+            gx2, need_x2 = gx2f, True
         return (None, gw.to(w.dtype) if need_w else None, gx1.to(x1.dtype) if need_x1 else None,
                 gx2.to(x2.dtype) if need_x2 else None)
 
@@ -256,6 +273,58 @@ class DenseUVW:
             return None
         self._tasks = (_lib.FctpFusedTask * len(tasks))(*tasks)
         return self._tasks
+
+    def _fused_units(self, which: int):
+        """Unit table of the fused gradient kernel for x1 (``which`` = 1) or x2 (2)."""
+        key = f"_units{which}"
+        if hasattr(self, key):
+            return getattr(self, key)
+        from . import _lib
+
+        d, off = self.d, self.offsets
+        units = []
+        for p in d.paths:
+            sw, s1, s2, so = p.indices
+            d1, d2, d3 = p.coefficients.shape
+            for k0 in range(0, d3, 2):
+                u = _lib.FctpFusedUnit()
+                u.w_row0 = off[0][sw] // 64
+                u.nk = min(2, d3 - k0)
+                if which == 1:
+                    u.offa, u.offb, u.da, u.db = off[1][s1], off[2][s2], d1, d2
+                else:
+                    u.offa, u.offb, u.da, u.db = off[2][s2], off[1][s1], d2, d1
+                for kq in range(u.nk):
+                    u.goff[kq] = off[3][so] + (k0 + kq) * 64
+                    for i in range(d1):
+                        for j in range(d2):
+                            c = float(p.coefficients[i, j, k0 + kq])
+                            if which == 1:
+                                u.c[kq][i * 5 + j] = c
+                            else:
+                                u.c[kq][j * 5 + i] = c
+                units.append(u)
+        arr = (_lib.FctpFusedUnit * len(units))(*units) if len(units) <= 32 else None
+        setattr(self, key, arr)
+        return arr
+
+    def _fused_gx(self, which, w16, xb, gout16, status):
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        units = self._fused_units(which)
+        B = xb.shape[0]
+        gxa = torch.zeros((B, xb.shape[1]), dtype=torch.float32, device=xb.device)
+        a = _lib.FctpFusedGxArgs()
+        a.xb, a.gout, a.w, a.gxa = xb.data_ptr(), gout16.data_ptr(), w16.data_ptr(), gxa.data_ptr()
+        a.ldb, a.ldg, a.lda, a.batch, a.w_rows = xb.shape[1], gout16.shape[1], gxa.shape[1], B, w16.shape[0]
+        a.num_units = len(units)
+        a.units = C.cast(units, C.POINTER(_lib.FctpFusedUnit))
+        a.status = status.data_ptr()
+        with profiling.kernel(f"fctp_fused_gx{which}"):
+            _lib.check(_lib.lib().cueq_b200_fctp_fused_gx(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return gxa
 
     def _fused_forward(self, w, x1, x2, status):
         import ctypes as C

@@ -75,7 +75,7 @@ const char* cueq_b200_last_error(void);
 /* sizeof() of an argument block as this library was compiled, so that a binding can check its own
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
    3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
-   7 cueq_fctp_fused_task; -1 for any other number. */
+   7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -277,6 +277,35 @@ typedef struct {
   void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
 } cueq_fctp_fused_args;
 int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* args, void* stream);
+
+/* Gradient of the same product with respect to x1 or x2 ("a" = the operand being differentiated,
+ * "b" = the other one):
+ *   gxa[z, ia, a] += sum_k sum_jb C[ia, jb, k] sum_b (sum_w gout[z, k, w] W[(a, b), w]) xb[z, jb, b]
+ * `w` rows are ordered (a, b): the forward array for x1; for x2 a copy with every [64 u][64 v]
+ * block transposed to [v][u], and c[k][ia * 5 + jb] then holds C[jb_as_i, ia_as_j, k].
+ * A unit is one path and up to two components k (goff[k] = offset of that component's 64 values
+ * in a cotangent row).  gxa is float32 and is accumulated into (zero it first). */
+#define CUEQ_FCTP_FUSED_MAX_UNITS 32
+typedef struct {
+  int32_t offa, offb;   /* element offsets of the path's segments in a gxa row / an xb row          */
+  int32_t da, db;       /* irrep dimensions of the differentiated / the other operand              */
+  int32_t w_row0;       /* first row of the path's weight block                                    */
+  int32_t nk;           /* 1 or 2 components                                                       */
+  int32_t goff[2];
+  float c[2][25];
+} cueq_fctp_fused_unit;
+typedef struct {
+  const void* xb;       /* device bf16 [batch, ldb]                                                */
+  const void* gout;     /* device bf16 [batch, ldg]                                                */
+  const void* w;        /* device bf16 [w_rows, 64]                                                */
+  void* gxa;            /* device float32 [batch, lda], accumulated into                           */
+  int64_t ldb, ldg, lda, batch, w_rows;
+  int32_t num_units;    /* 1 .. CUEQ_FCTP_FUSED_MAX_UNITS                                          */
+  int32_t reserved;
+  const cueq_fctp_fused_unit* units;  /* HOST array                                                */
+  void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
+} cueq_fctp_fused_gx_args;
+int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* args, void* stream);
 
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *
