@@ -130,6 +130,22 @@ class FctpFusedGxArgs(C.Structure):
     ]
 
 
+class FctpFusedWUnit(C.Structure):
+    _fields_ = [
+        ("off1", C.c_int32), ("off2", C.c_int32), ("d1", C.c_int32), ("d2", C.c_int32), ("d3", C.c_int32),
+        ("w_row0", C.c_int32), ("goff", C.c_int32), ("reserved", C.c_int32), ("c", (C.c_float * 25) * 5),
+    ]
+
+
+class FctpFusedGwArgs(C.Structure):
+    _fields_ = [
+        ("x1", C.c_void_p), ("x2", C.c_void_p), ("gout", C.c_void_p), ("gw", C.c_void_p),
+        ("ld1", C.c_int64), ("ld2", C.c_int64), ("ldg", C.c_int64), ("batch", C.c_int64), ("w_rows", C.c_int64),
+        ("num_units", C.c_int32), ("reserved", C.c_int32),
+        ("units", C.POINTER(FctpFusedWUnit)), ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -181,10 +197,11 @@ def lib() -> C.CDLL:
     L.cueq_b200_fctp_consume_gz.argtypes = [C.POINTER(FctpArgs), C.c_void_p]
     L.cueq_b200_fctp_fused_forward.argtypes = [C.POINTER(FctpFusedArgs), C.c_void_p]
     L.cueq_b200_fctp_fused_gx.argtypes = [C.POINTER(FctpFusedGxArgs), C.c_void_p]
+    L.cueq_b200_fctp_fused_gw.argtypes = [C.POINTER(FctpFusedGwArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     L.cueq_b200_sizeof.restype = C.c_int64
-    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask, FctpFusedGxArgs, FctpFusedUnit)):
+    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask, FctpFusedGxArgs, FctpFusedUnit, FctpFusedGwArgs, FctpFusedWUnit)):
         if L.cueq_b200_sizeof(which) != C.sizeof(struct):
             raise CueqError(f"{struct.__name__}: this binding declares {C.sizeof(struct)} bytes, the library "
                             f"{L.cueq_b200_sizeof(which)}; rebuild the library or update the binding")

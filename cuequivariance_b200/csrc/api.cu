@@ -32,6 +32,8 @@ extern "C" int64_t cueq_b200_sizeof(int which) {
     case 7: return sizeof(cueq_fctp_fused_task);
     case 8: return sizeof(cueq_fctp_fused_gx_args);
     case 9: return sizeof(cueq_fctp_fused_unit);
+    case 10: return sizeof(cueq_fctp_fused_gw_args);
+    case 11: return sizeof(cueq_fctp_fused_wunit);
     default: return -1;
   }
 }

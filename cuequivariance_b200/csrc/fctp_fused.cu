@@ -566,6 +566,249 @@ __global__ void __launch_bounds__(kThreadsG, 1) fctp_fused_gx_kernel(const __gri
   }
 }
 
+
+// ---- gradient with respect to the weights ------------------------------------------------------
+//
+//   gW[(u, v), w] += sum_z sum_k Z[z, k, (u, v)] * gout[z, k, w]
+//
+// A GEMM with K = samples: A = Z^T is built by the producer warps as an MN-major operand (rows =
+// samples, 128 consecutive (u, v) = 2 u per tile), B = a [64 samples x 64 w] block of the cotangent
+// (MN-major, TMA).  One CTA owns (path, 16 u, a range of samples) and keeps eight [128 x 64]
+// accumulators in TMEM (all 512 columns), so that x2 values, the cotangent block and the T
+// products of a (component, 64-sample block) are shared by eight MMA groups.  The partial sums
+// of the sample ranges are combined with red.global.add.
+// Warp roles: 0 = TMA, 1 = MMA issue + TMEM owner, 2-5 = epilogue, 6-13 = producers.
+constexpr int WK = 64;                         // samples per item (MMA K, 4 instructions)
+constexpr int kStagesWA = 6;                   // A ring (16 KiB: 2 blocks of [64 samples][64 (u,v)])
+constexpr int kStagesWB = 4;                   // cotangent blocks (8 KiB)
+constexpr int kTilesW = 8;                     // accumulators per CTA (2 u each)
+
+struct GwParams {
+  const __nv_bfloat16* x1;
+  const __nv_bfloat16* x2;
+  float* gw;
+  int64_t ld1, ld2, batch;
+  int blocks_per_split;    // 64-sample blocks handled by one CTA
+  int* status;
+  cueq_fctp_fused_wunit units[CUEQ_FCTP_FUSED_MAX_WUNITS];
+};
+
+// All items of one component k: for every 64-sample block of this CTA, 8 tiles of 2 u.
+// Thread = (sample row, u within the tile, half of v); lanes 8 apart hold the two halves.
+template <int D1, int NJ>
+__device__ __forceinline__ void produce_gw(const GwParams& p, const cueq_fctp_fused_wunit& unit, unsigned char* ringA,
+                                           const float* coef, const int* active, unsigned long long* fullA,
+                                           unsigned long long* emptyA, int item, bool& dead, int64_t zb0, int nblocks,
+                                           int u0, int ptid) {
+  const int lane = ptid & 31;
+  const int row = (ptid >> 5) * 8 + (lane & 7), ul = (lane >> 4) & 1, vh = (lane >> 3) & 1;
+  float cf[D1][NJ];
+#pragma unroll
+  for (int i = 0; i < D1; ++i)
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) cf[i][jj] = coef[i * 5 + jj];
+  const int swz = row & 7;
+  for (int b = 0; b < nblocks; ++b) {
+    const int64_t z = (zb0 + b) * WK + row;
+    const bool valid = z < p.batch;
+    uint4 x2r[4][NJ];
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x2 + (valid ? z : 0) * p.ld2 + unit.off2 + active[jj] * 64) + vh * 4;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) x2r[cc][jj] = valid ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
+    }
+    const unsigned short* x1row = reinterpret_cast<const unsigned short*>(p.x1 + (valid ? z : 0) * p.ld1 + unit.off1) + u0 + ul;
+    for (int t2i = 0; t2i < kTilesW; t2i += 2) {
+      // the two v-halves of a (row, u) compute T for tiles t2i and t2i + 1 and exchange them
+      unsigned tmine[NJ];
+      {
+        const int u = (t2i + vh) * 2;
+        float xf[D1];
+#pragma unroll
+        for (int i = 0; i < D1; ++i) xf[i] = valid ? bf16_lo(__ldg(x1row + i * 64 + u)) : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+          float t = cf[0][jj] * xf[0];
+#pragma unroll
+          for (int i = 1; i < D1; ++i) t = fmaf(cf[i][jj], xf[i], t);
+          tmine[jj] = pack_same(t);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q, ++item) {
+        unsigned t2[NJ];
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) t2[jj] = __shfl_sync(0xffffffffu, tmine[jj], (lane & ~8) | (q << 3));
+        const int s = item % kStagesWA;
+        if (!dead) dead = !bar_wait(emptyA + s, ((item / kStagesWA) & 1) ^ 1, p.status);
+        if (!dead) {
+          unsigned char* arow = ringA + s * kTileAF + ul * 8192 + row * 128;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint4 acc;
+            acc.x = hmul2_bits(t2[0], x2r[cc][0].x);
+            acc.y = hmul2_bits(t2[0], x2r[cc][0].y);
+            acc.z = hmul2_bits(t2[0], x2r[cc][0].z);
+            acc.w = hmul2_bits(t2[0], x2r[cc][0].w);
+#pragma unroll
+            for (int jj = 1; jj < NJ; ++jj) {
+              acc.x = hfma2_bits(t2[jj], x2r[cc][jj].x, acc.x);
+              acc.y = hfma2_bits(t2[jj], x2r[cc][jj].y, acc.y);
+              acc.z = hfma2_bits(t2[jj], x2r[cc][jj].z, acc.z);
+              acc.w = hfma2_bits(t2[jj], x2r[cc][jj].w, acc.w);
+            }
+            *reinterpret_cast<uint4*>(arow + (((vh * 4 + cc) ^ swz) << 4)) = acc;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive(fullA + s);
+      }
+    }
+  }
+}
+
+template <int D1>
+__device__ __forceinline__ void produce_gw_k(const GwParams& p, const cueq_fctp_fused_wunit& unit, int k, unsigned char* ringA,
+                                             float* coef, int* active, unsigned long long* fullA, unsigned long long* emptyA,
+                                             int item, bool& dead, int64_t zb0, int nblocks, int u0, int ptid) {
+  producers_sync();
+  if (ptid == 0) {
+    int nj = 0;
+    for (int j = 0; j < unit.d2; ++j) {
+      bool any = false;
+      for (int i = 0; i < D1; ++i) any |= unit.c[k][i * 5 + j] != 0.f;
+      if (any || (j == unit.d2 - 1 && nj == 0)) {
+        for (int i = 0; i < D1; ++i) coef[i * 5 + nj] = unit.c[k][i * 5 + j];
+        active[nj++] = j;
+      }
+    }
+    active[7] = nj;
+  }
+  producers_sync();
+  switch (active[7]) {
+    case 1: produce_gw<D1, 1>(p, unit, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+    case 2: produce_gw<D1, 2>(p, unit, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+    case 3: produce_gw<D1, 3>(p, unit, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+    case 4: produce_gw<D1, 4>(p, unit, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+    default: produce_gw<D1, 5>(p, unit, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_gw_kernel(const __grid_constant__ CUtensorMap map_g,
+                                                                    const __grid_constant__ GwParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* ringA = smem;
+  unsigned char* ringB = ringA + kStagesWA * kTileAF;
+  float* coef = reinterpret_cast<float*>(ringB + kStagesWB * kTileBF);
+  int* active = reinterpret_cast<int*>(coef + 32);
+  unsigned long long* fullA = reinterpret_cast<unsigned long long*>(active + 8);
+  unsigned long long* emptyA = fullA + kStagesWA;
+  unsigned long long* fullB = emptyA + kStagesWA;
+  unsigned long long* emptyB = fullB + kStagesWB;
+  unsigned long long* acc_ready = emptyB + kStagesWB;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const cueq_fctp_fused_wunit& unit = p.units[blockIdx.y];
+  const int u0 = blockIdx.z * (2 * kTilesW);
+  const int total_blocks = (int)((p.batch + WK - 1) / WK);
+  const int64_t zb0 = (int64_t)blockIdx.x * p.blocks_per_split;
+  const int nblocks = min(p.blocks_per_split, total_blocks - (int)zb0);
+  const int ngroups = unit.d3 * nblocks;       // (k, block) pairs, k outermost
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesWA; ++s) { bar_init(fullA + s, kProducers / 32); bar_init(emptyA + s, 1); }
+    for (int s = 0; s < kStagesWB; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
+    bar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int g = 0; g < ngroups; ++g) {
+        const int k = g / nblocks, b = g % nblocks;
+        const int s = g % kStagesWB;
+        if (!bar_wait(emptyB + s, ((g / kStagesWB) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(fullB + s, kTileBF);
+        tma_load_2d(ringB + s * kTileBF, &map_g, unit.goff + k * 64, (int)((zb0 + b) * WK), fullB + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // D = f32, A = B = bf16, both MN-major, N = 64, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((unsigned)(FN >> 3) << 17) | ((unsigned)(FM >> 4) << 24);
+      bool ok = true;
+      int item = 0;
+      for (int g = 0; g < ngroups && ok; ++g) {
+        const int sb = g % kStagesWB;
+        ok = bar_wait(fullB + sb, (g / kStagesWB) & 1, p.status);
+        const unsigned long long db = smem_desc_mn(ringB + sb * kTileBF);
+        for (int t = 0; t < kTilesW && ok; ++t, ++item) {
+          const int s = item % kStagesWA;
+          ok = bar_wait(fullA + s, (item / kStagesWA) & 1, p.status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned long long da = smem_desc_mn(ringA + s * kTileAF);
+#pragma unroll
+          for (int kk = 0; kk < WK / 16; ++kk) umma_bf16(tmem_base + t * FN, da + 128ull * kk, db + 128ull * kk, idesc, (g | kk) != 0 ? 1u : 0u);
+          umma_commit(emptyA + s);
+        }
+        umma_commit(emptyB + sb);
+      }
+      umma_commit(acc_ready);
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    const bool ok = bar_wait(acc_ready, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int m = q * 32 + lane;       // row of the tile: (u within the pair) * 64 + v
+    for (int t = 0; t < kTilesW; ++t) {
+      float* dst = p.gw + ((int64_t)unit.w_row0 + (int64_t)(u0 + 2 * t) * 64 + m) * 64;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        unsigned v[32];
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + t * FN + half * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (ok && ngroups > 0) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst + half * 32 + c), "f"(__uint_as_float(v[c])),
+                         "f"(__uint_as_float(v[c + 1])), "f"(__uint_as_float(v[c + 2])), "f"(__uint_as_float(v[c + 3])) : "memory");
+        }
+      }
+    }
+  } else {
+    const int ptid = threadIdx.x - 192;
+    bool dead = false;
+    for (int k = 0; k < unit.d3; ++k) {
+      const int item = k * nblocks * kTilesW;
+      switch (unit.d1) {
+        case 1: produce_gw_k<1>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+        case 3: produce_gw_k<3>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+        case 5: produce_gw_k<5>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
+        default: break;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 int make_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return cueq::fail("fctp fused: cuTensorMapEncodeTiled is not available from the driver");
@@ -650,6 +893,52 @@ extern "C" int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* a, void* s
   }
   dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_units);
   fctp_fused_gx_kernel<<<grid, kThreadsG, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, mw, p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+
+extern "C" int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* a, void* stream) {
+  if (!a || !a->x1 || !a->x2 || !a->gout || !a->gw || !a->units) return cueq::fail("fctp fused gw: null argument");
+  if (a->batch <= 0) return 0;
+  if (a->num_units < 1 || a->num_units > CUEQ_FCTP_FUSED_MAX_WUNITS) return cueq::fail("fctp fused gw: between 1 and %d units", CUEQ_FCTP_FUSED_MAX_WUNITS);
+  for (int t = 0; t < a->num_units; ++t) {
+    const cueq_fctp_fused_wunit& u = a->units[t];
+    const bool okd = (u.d1 == 1 || u.d1 == 3 || u.d1 == 5) && (u.d2 == 1 || u.d2 == 3 || u.d2 == 5) && (u.d3 == 1 || u.d3 == 3 || u.d3 == 5);
+    if (!okd) return cueq::fail("fctp fused gw: irrep dimensions must be 1, 3 or 5 (unit %d)", t);
+    if (u.off1 < 0 || u.off2 < 0 || (u.off1 % 8) || (u.off2 % 8)) return cueq::fail("fctp fused gw: segment offsets must be non-negative multiples of 8 elements");
+    if (u.off1 + u.d1 * 64 > a->ld1 || u.off2 + u.d2 * 64 > a->ld2) return cueq::fail("fctp fused gw: segment of unit %d exceeds the row", t);
+    if (u.goff < 0 || (u.goff % 8) || u.goff + u.d3 * 64 > a->ldg) return cueq::fail("fctp fused gw: cotangent block of unit %d is outside the row", t);
+    if (u.w_row0 < 0 || (int64_t)u.w_row0 + 4096 > a->w_rows) return cueq::fail("fctp fused gw: weight block of unit %d is outside the weight array", t);
+  }
+  if ((a->ld1 % 8) || (a->ld2 % 8) || (a->ldg % 8)) return cueq::fail("fctp fused gw: row pitches must be multiples of 8 elements");
+  if (((uintptr_t)a->x1 | (uintptr_t)a->x2 | (uintptr_t)a->gout | (uintptr_t)a->gw) & 15) return cueq::fail("fctp fused gw: operands must be 16-byte aligned");
+  if (a->batch > 2147483647LL - 64) return cueq::fail("fctp fused gw: batch too large");
+  CUtensorMap mg;
+  if (int rc = make_map_2d(&mg, a->gout, a->batch, a->ldg, a->ldg, 64, WK)) return rc;
+  GwParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.x1 = reinterpret_cast<const __nv_bfloat16*>(a->x1);
+  p.x2 = reinterpret_cast<const __nv_bfloat16*>(a->x2);
+  p.gw = reinterpret_cast<float*>(a->gw);
+  p.ld1 = a->ld1; p.ld2 = a->ld2; p.batch = a->batch;
+  p.status = reinterpret_cast<int*>(a->status);
+  std::memcpy(p.units, a->units, sizeof(cueq_fctp_fused_wunit) * a->num_units);
+  // sample ranges: enough CTAs to fill the GPU about four times over, at least 8 blocks each
+  const int total_blocks = (int)((a->batch + WK - 1) / WK);
+  int splits = (592 + a->num_units * 4 - 1) / (a->num_units * 4);
+  if (splits > total_blocks / 8) splits = total_blocks / 8;
+  if (splits < 1) splits = 1;
+  p.blocks_per_split = (total_blocks + splits - 1) / splits;
+  splits = (total_blocks + p.blocks_per_split - 1) / p.blocks_per_split;
+  const size_t smem = kStagesWA * kTileAF + kStagesWB * kTileBF + 512 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_gw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)splits, (unsigned)a->num_units, 64 / (2 * kTilesW));
+  fctp_fused_gw_kernel<<<grid, kThreadsF, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -34,6 +34,7 @@ from .executor import Uniform1dProgram
 from .polynomial import Polynomial
 
 FLATTEN_LIMIT = 20000  # flattened paths above which the composite route is taken
+FUSED_GW = True
 FUSED = True  # fully connected tensor-core route: build the coupled operand on chip when the shape allows
 
 
@@ -147,11 +148,14 @@ class _TensorCoreUVW(torch.autograd.Function):
         B, dev = x1.shape[0], x1.device
         need_w, need_x1, need_x2 = ctx.needs_input_grad[1], ctx.needs_input_grad[2], ctx.needs_input_grad[3]
         status = ctx.status
-        fused_x = FUSED and owner._fused_tasks() is not None and owner._fused_units(1) is not None
-        gx1f = gx2f = None
-        if fused_x and (need_x1 or need_x2):
+        fused_x = FUSED and owner._fused_tasks() is not None and owner._fused_units(1) is not None and owner._fused_wunits() is not None
+        gx1f = gx2f = gwf = None
+        if fused_x and (need_x1 or need_x2 or need_w):
             gout16 = gout.to(torch.bfloat16).contiguous()
             x1b, x2b = x1.to(torch.bfloat16).contiguous(), x2.to(torch.bfloat16).contiguous()
+            if need_w and FUSED_GW:
+                gwf = owner._fused_gw(w, x1b, x2b, gout16, status)
+                need_w = False
             if need_x1:
                 gx1f = owner._fused_gx(1, w.reshape(-1, 64).to(torch.bfloat16).contiguous(), x2b, gout16, status)
             if need_x2:
@@ -192,6 +196,8 @@ class _TensorCoreUVW(torch.autograd.Function):
                 with profiling.kernel("fctp_consume_gz"):
                     _lib.check(_lib.lib().cueq_b200_fctp_consume_gz(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
                 del gZ
+        if gwf is not None:
+            gw, need_w = gwf, True
         if gx1f is not None:
             gx1, need_x1 = gx1f, True
         if gx2f is not None:
@@ -325,6 +331,44 @@ class DenseUVW:
         with profiling.kernel(f"fctp_fused_gx{which}"):
             _lib.check(_lib.lib().cueq_b200_fctp_fused_gx(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return gxa
+
+    def _fused_wunits(self):
+        if hasattr(self, "_wunits"):
+            return self._wunits
+        from . import _lib
+
+        d, off = self.d, self.offsets
+        units = []
+        for p in d.paths:
+            sw, s1, s2, so = p.indices
+            d1, d2, d3 = p.coefficients.shape
+            u = _lib.FctpFusedWUnit()
+            u.off1, u.off2, u.d1, u.d2, u.d3 = off[1][s1], off[2][s2], d1, d2, d3
+            u.w_row0, u.goff = off[0][sw] // 64, off[3][so]
+            for k in range(d3):
+                for i in range(d1):
+                    for j in range(d2):
+                        u.c[k][i * 5 + j] = float(p.coefficients[i, j, k])
+            units.append(u)
+        self._wunits = (_lib.FctpFusedWUnit * len(units))(*units) if len(units) <= 16 else None
+        return self._wunits
+
+    def _fused_gw(self, w, x1b, x2b, gout16, status):
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        units = self._fused_wunits()
+        gw = torch.zeros((w.numel() // 64, 64), dtype=torch.float32, device=w.device)
+        a = _lib.FctpFusedGwArgs()
+        a.x1, a.x2, a.gout, a.gw = x1b.data_ptr(), x2b.data_ptr(), gout16.data_ptr(), gw.data_ptr()
+        a.ld1, a.ld2, a.ldg, a.batch, a.w_rows = x1b.shape[1], x2b.shape[1], gout16.shape[1], x1b.shape[0], gw.shape[0]
+        a.num_units = len(units)
+        a.units = C.cast(units, C.POINTER(_lib.FctpFusedWUnit))
+        a.status = status.data_ptr()
+        with profiling.kernel("fctp_fused_gw"):
+            _lib.check(_lib.lib().cueq_b200_fctp_fused_gw(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return gw.reshape(1, -1)
 
     def _fused_forward(self, w, x1, x2, status):
         import ctypes as C

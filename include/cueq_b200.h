@@ -75,7 +75,8 @@ const char* cueq_b200_last_error(void);
 /* sizeof() of an argument block as this library was compiled, so that a binding can check its own
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
    3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
-   7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit; -1 for any other number. */
+   7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit,
+   10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -306,6 +307,32 @@ typedef struct {
   void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
 } cueq_fctp_fused_gx_args;
 int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* args, void* stream);
+
+/* Gradient of the same product with respect to the (shared) weights:
+ *   gw[(u, v), w] += sum_z sum_k (sum_ij C[i, j, k] x1[z, i, u] x2[z, j, v]) gout[z, k, w]
+ * One unit per path; gw is the float32 array [w_rows, 64] laid out like W and is accumulated
+ * into (zero it first). */
+#define CUEQ_FCTP_FUSED_MAX_WUNITS 16
+typedef struct {
+  int32_t off1, off2;   /* element offsets of the path's x1 / x2 segments                          */
+  int32_t d1, d2, d3;
+  int32_t w_row0;       /* first row of the path's block in gw                                     */
+  int32_t goff;         /* element offset of the path's output irrep in a cotangent row            */
+  int32_t reserved;
+  float c[5][25];       /* c[k][i * 5 + j] = C[i, j, k]                                            */
+} cueq_fctp_fused_wunit;
+typedef struct {
+  const void* x1;       /* device bf16 [batch, ld1]                                                */
+  const void* x2;       /* device bf16 [batch, ld2]                                                */
+  const void* gout;     /* device bf16 [batch, ldg]                                                */
+  void* gw;             /* device float32 [w_rows, 64], accumulated into                           */
+  int64_t ld1, ld2, ldg, batch, w_rows;
+  int32_t num_units;    /* 1 .. CUEQ_FCTP_FUSED_MAX_WUNITS                                         */
+  int32_t reserved;
+  const cueq_fctp_fused_wunit* units;  /* HOST array                                               */
+  void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
+} cueq_fctp_fused_gw_args;
+int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* args, void* stream);
 
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *

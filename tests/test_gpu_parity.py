@@ -260,18 +260,24 @@ def test_fully_connected_dense_route_matches_oracle():
         _close(a, b, 1e-3, 2e-4, "gradgrad")
 
 
+@pytest.mark.parametrize("fused,B", [(True, 96), (True, 300), (False, 96)])
 @pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float32])
-def test_fully_connected_tensor_core_route(in_dtype):
-    """64 channels: the tensor-core route (bf16 operands, float32 accumulation).  Compared with
-    the CPU oracle evaluated in float32 on the same (bf16-rounded) inputs; tolerance is that of
-    bf16 operands (rtol 2e-2 of the tensor's scale; the reference's own bf16 tolerance is
-    rtol 1e-2 / atol 4.0, cuequivariance_torch/_tests/utils.py:282)."""
+def test_fully_connected_tensor_core_route(in_dtype, fused, B, monkeypatch):
+    """64 channels: the tensor-core routes (bf16 operands, float32 accumulation) - ``fused``: the
+    coupled operand is built on chip (four launches for forward + three gradients); otherwise
+    it is written to memory and contracted by the stand-alone GEMM.  Batches that are not a
+    multiple of the 128-sample tile exercise the ragged edge.  Compared with the CPU oracle
+    evaluated in float32 on the same (bf16-rounded) inputs; tolerance is that of bf16 operands
+    (rtol 2e-2 of the tensor's scale; the reference's own bf16 tolerance is rtol 1e-2 /
+    atol 4.0, cuequivariance_torch/_tests/utils.py:282)."""
+    from cuequivariance_b200 import fused_tp
+
+    monkeypatch.setattr(fused_tp, "FUSED", fused)
     s = "64x0e+64x1o+64x2e"
     e = D.fully_connected_tensor_product(s, s, s)
     m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.ir_mul, internal_weights=False, shared_weights=True,
                                        options={"tensor_cores": True})
     gen = torch.Generator().manual_seed(22)
-    B = 96
     x1 = torch.randn(B, m.irreps_in1.dim, generator=gen).to(in_dtype)
     x2 = torch.randn(B, m.irreps_in2.dim, generator=gen).to(in_dtype)
     w = (torch.randn(1, m.weight_numel, generator=gen) / 64.0).to(in_dtype)
@@ -284,8 +290,14 @@ def test_fully_connected_tensor_core_route(in_dtype):
 
     ref = grads(lambda w_, a, b: naive.segmented_polynomial(e.polynomial, [w_, a, b])[0], [w.float(), x1.float(), x2.float()], cot)
     profiling.reset()
-    got = grads(lambda w_, a, b: m(a, b, w_), [w.to(DEV), x1.to(DEV), x2.to(DEV)], cot.to(DEV))
-    assert profiling.launch_count >= 3 * 11, "the tensor-core route did not run"
+    profiling.enable()
+    try:
+        got = grads(lambda w_, a, b: m(a, b, w_), [w.to(DEV), x1.to(DEV), x2.to(DEV)], cot.to(DEV))
+        names = set(profiling.summary())
+    finally:
+        profiling.enable(False)
+    assert profiling.launch_count >= (4 if fused else 3 * 11), "the tensor-core route did not run"
+    assert ({"fctp_fused_forward", "fctp_fused_gw", "fctp_fused_gx1", "fctp_fused_gx2"} <= names) == fused, names
     for name, a, b in zip(["out", "gw", "gx1", "gx2"], got, ref):
         scale = float(b.abs().max())
         err = float((a.float().cpu() - b).abs().max())
