@@ -132,8 +132,8 @@ class FctpFusedGxArgs(C.Structure):
 
 class FctpFusedWUnit(C.Structure):
     _fields_ = [
-        ("off1", C.c_int32), ("off2", C.c_int32), ("d1", C.c_int32), ("d2", C.c_int32), ("d3", C.c_int32),
-        ("w_row0", C.c_int32), ("goff", C.c_int32), ("reserved", C.c_int32), ("c", (C.c_float * 25) * 5),
+        ("off1", C.c_int32), ("off2", C.c_int32), ("d1", C.c_int32), ("d2", C.c_int32),
+        ("w_row0", C.c_int32), ("goff", C.c_int32), ("c", C.c_float * 25), ("reserved", C.c_float),
     ]
 
 

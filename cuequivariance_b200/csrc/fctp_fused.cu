@@ -39,6 +39,9 @@ constexpr int kTileBF = FK * FN * 2;    // 8 KiB
 constexpr int kStageF = kTileAF;
 constexpr int kProducers = 256;
 constexpr int kThreadsF = 64 + 128 + kProducers;
+constexpr int kIssuers = 2;              // threads issuing tcgen05.mma in the forward kernel
+constexpr int kThreadsFwd = kThreadsF + 32 * (kIssuers - 1);
+constexpr int kFwdTmemCols = kIssuers * FN <= 64 ? 64 : kIssuers * FN <= 128 ? 128 : 256;   // allocations are powers of two
 
 struct FwdParams {
   const __nv_bfloat16* x1;
@@ -70,6 +73,17 @@ __device__ __forceinline__ unsigned pack_same(float t) {
   unsigned d;
   asm("cvt.rn.bf16x2.f32 %0, %1, %1;\n" : "=r"(d) : "f"(t));
   return d;
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr));
 }
 
 // The 64 stage items (u = 0..63) of one path for this CTA's component k.  `ptid` in [0, 256): a
@@ -184,7 +198,7 @@ __device__ __forceinline__ void produce_path(const FwdParams& p, const cueq_fctp
   }
 }
 
-__global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(kThreadsFwd, 1) fctp_fused_forward_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                          const __grid_constant__ FwdParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -206,11 +220,11 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesF; ++s) { bar_init(full + s, kProducers / 32); bar_init(empty + s, 1); }
     for (int s = 0; s < kStagesB; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
-    bar_init(acc_ready, 1);
+    bar_init(acc_ready, kIssuers);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(64u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"((unsigned)kFwdTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -228,11 +242,15 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const 
         tma_load_2d(ringB + s * kTileBF, &map_w, 0, row0, fullB + s);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp >= 6 + kProducers / 32) {
+    // MMA issue.  Consecutive tcgen05.mma of one thread were measured to start about 110 ns apart
+    // whatever their shape, while two issuing threads overlap, so the items are dealt round-robin
+    // to kIssuers threads, each with its own accumulator; the epilogue adds the accumulators.
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1 + (warp - (6 + kProducers / 32));
       // D = f32, A = B = bf16, A K-major, B MN-major ([K = (u,v)][N = w], w contiguous), N = 64, M = 128
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(FN >> 3) << 17) | ((unsigned)(FM >> 4) << 24);
-      for (int item = 0; item < total_items; ++item) {
+      for (int item = me; item < total_items; item += kIssuers) {
         const int s = item % kStagesF, sb = item % kStagesB;
         if (!bar_wait(fullB + sb, (item / kStagesB) & 1, p.status)) break;
         if (!bar_wait(full + s, (item / kStagesF) & 1, p.status)) break;
@@ -240,7 +258,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const 
         const unsigned long long da = smem_desc(smem + s * kStageF);
         const unsigned long long db = smem_desc_mn(ringB + sb * kTileBF);
 #pragma unroll
-        for (int kk = 0; kk < FK / 16; ++kk) umma_bf16(tmem_base, da + 2ull * kk, db + 128ull * kk, idesc, (item | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < FK / 16; ++kk) umma_bf16(tmem_base + me * FN, da + 2ull * kk, db + 128ull * kk, idesc, (item >= kIssuers || kk != 0) ? 1u : 0u);
         umma_commit(empty + s);
         umma_commit(emptyB + sb);
       }
@@ -254,16 +272,18 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const 
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       unsigned v[32];
-      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + half * 32;
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                   "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                   "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                     "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                     "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                     "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                   : "r"(taddr));
+      tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + half * 32, v);
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+      for (int r = 1; r < kIssuers; ++r) {
+        {
+          unsigned v2[32];
+          tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + r * FN + half * 32, v2);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(v2[c]));
+        }
+      }
       if (ok && z < p.batch) {
         const int64_t off = z * p.ldo + task.out_off + half * 32;
         if (p.out_bf16) {
@@ -301,7 +321,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_forward_kernel(const 
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(64u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)kFwdTmemCols) : "memory");
   }
 }
 
@@ -370,17 +390,6 @@ struct GxParams {
 };
 
 __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 2, %0;\n" ::"n"(kConsumers) : "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-               : "r"(taddr));
-}
 
 // Folds one [row, 2 a, 64 b] strip of a gZ tile against the NJ active rows of xb:
 // r[a2][jj] = sum_b gZ[a2, b] * xb[act[jj], b].
@@ -573,7 +582,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) fctp_fused_gx_kernel(const __gri
 //
 // A GEMM with K = samples: A = Z^T is built by the producer warps as an MN-major operand (rows =
 // samples, 128 consecutive (u, v) = 2 u per tile), B = a [64 samples x 64 w] block of the cotangent
-// (MN-major, TMA).  One CTA owns (path, 16 u, a range of samples) and keeps eight [128 x 64]
+// (MN-major, TMA).  One CTA owns (path, component k, 16 u, a range of samples) and keeps eight [128 x 64]
 // accumulators in TMEM (all 512 columns), so that x2 values, the cotangent block and the T
 // products of a (component, 64-sample block) are shared by eight MMA groups.  The partial sums
 // of the sample ranges are combined with red.global.add.
@@ -593,7 +602,7 @@ struct GwParams {
   cueq_fctp_fused_wunit units[CUEQ_FCTP_FUSED_MAX_WUNITS];
 };
 
-// All items of one component k: for every 64-sample block of this CTA, 8 tiles of 2 u.
+// All items of the CTA's (path, component): for every 64-sample block, 8 tiles of 2 u.
 // Thread = (sample row, u within the tile, half of v); lanes 8 apart hold the two halves.
 template <int D1, int NJ>
 __device__ __forceinline__ void produce_gw(const GwParams& p, const cueq_fctp_fused_wunit& unit, unsigned char* ringA,
@@ -670,7 +679,7 @@ __device__ __forceinline__ void produce_gw(const GwParams& p, const cueq_fctp_fu
 }
 
 template <int D1>
-__device__ __forceinline__ void produce_gw_k(const GwParams& p, const cueq_fctp_fused_wunit& unit, int k, unsigned char* ringA,
+__device__ __forceinline__ void produce_gw_k(const GwParams& p, const cueq_fctp_fused_wunit& unit, unsigned char* ringA,
                                              float* coef, int* active, unsigned long long* fullA, unsigned long long* emptyA,
                                              int item, bool& dead, int64_t zb0, int nblocks, int u0, int ptid) {
   producers_sync();
@@ -678,9 +687,9 @@ __device__ __forceinline__ void produce_gw_k(const GwParams& p, const cueq_fctp_
     int nj = 0;
     for (int j = 0; j < unit.d2; ++j) {
       bool any = false;
-      for (int i = 0; i < D1; ++i) any |= unit.c[k][i * 5 + j] != 0.f;
+      for (int i = 0; i < D1; ++i) any |= unit.c[i * 5 + j] != 0.f;
       if (any || (j == unit.d2 - 1 && nj == 0)) {
-        for (int i = 0; i < D1; ++i) coef[i * 5 + nj] = unit.c[k][i * 5 + j];
+        for (int i = 0; i < D1; ++i) coef[i * 5 + nj] = unit.c[i * 5 + j];
         active[nj++] = j;
       }
     }
@@ -696,7 +705,7 @@ __device__ __forceinline__ void produce_gw_k(const GwParams& p, const cueq_fctp_
   }
 }
 
-__global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_gw_kernel(const __grid_constant__ CUtensorMap map_g,
+__global__ void __launch_bounds__(kThreadsFwd, 1) fctp_fused_gw_kernel(const __grid_constant__ CUtensorMap map_g,
                                                                     const __grid_constant__ GwParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -717,12 +726,12 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_gw_kernel(const __gri
   const int total_blocks = (int)((p.batch + WK - 1) / WK);
   const int64_t zb0 = (int64_t)blockIdx.x * p.blocks_per_split;
   const int nblocks = min(p.blocks_per_split, total_blocks - (int)zb0);
-  const int ngroups = unit.d3 * nblocks;       // (k, block) pairs, k outermost
+  const int ngroups = nblocks;                 // one cotangent block per 64 samples
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesWA; ++s) { bar_init(fullA + s, kProducers / 32); bar_init(emptyA + s, 1); }
-    for (int s = 0; s < kStagesWB; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
-    bar_init(acc_ready, 1);
+    for (int s = 0; s < kStagesWB; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, kIssuers); }
+    bar_init(acc_ready, kIssuers);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -737,24 +746,25 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_gw_kernel(const __gri
   if (warp == 0) {
     if (lane == 0) {
       for (int g = 0; g < ngroups; ++g) {
-        const int k = g / nblocks, b = g % nblocks;
         const int s = g % kStagesWB;
         if (!bar_wait(emptyB + s, ((g / kStagesWB) & 1) ^ 1, p.status)) break;
         bar_expect_tx(fullB + s, kTileBF);
-        tma_load_2d(ringB + s * kTileBF, &map_g, unit.goff + k * 64, (int)((zb0 + b) * WK), fullB + s);
+        tma_load_2d(ringB + s * kTileBF, &map_g, unit.goff, (int)((zb0 + g) * WK), fullB + s);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp >= 6 + kProducers / 32) {
+    // kIssuers threads issue the MMAs (see the forward kernel): issuer r owns tiles t = r, r + kIssuers, ...
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1 + (warp - (6 + kProducers / 32));
       // D = f32, A = B = bf16, both MN-major, N = 64, M = 128
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((unsigned)(FN >> 3) << 17) | ((unsigned)(FM >> 4) << 24);
       bool ok = true;
-      int item = 0;
       for (int g = 0; g < ngroups && ok; ++g) {
         const int sb = g % kStagesWB;
         ok = bar_wait(fullB + sb, (g / kStagesWB) & 1, p.status);
         const unsigned long long db = smem_desc_mn(ringB + sb * kTileBF);
-        for (int t = 0; t < kTilesW && ok; ++t, ++item) {
+        for (int t = me; t < kTilesW && ok; t += kIssuers) {
+          const int item = g * kTilesW + t;
           const int s = item % kStagesWA;
           ok = bar_wait(fullA + s, (item / kStagesWA) & 1, p.status);
           if (!ok) break;
@@ -791,14 +801,11 @@ __global__ void __launch_bounds__(kThreadsF, 1) fctp_fused_gw_kernel(const __gri
   } else {
     const int ptid = threadIdx.x - 192;
     bool dead = false;
-    for (int k = 0; k < unit.d3; ++k) {
-      const int item = k * nblocks * kTilesW;
-      switch (unit.d1) {
-        case 1: produce_gw_k<1>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
-        case 3: produce_gw_k<3>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
-        case 5: produce_gw_k<5>(p, unit, k, ringA, coef, active, fullA, emptyA, item, dead, zb0, nblocks, u0, ptid); break;
-        default: break;
-      }
+    switch (unit.d1) {
+      case 1: produce_gw_k<1>(p, unit, ringA, coef, active, fullA, emptyA, 0, dead, zb0, nblocks, u0, ptid); break;
+      case 3: produce_gw_k<3>(p, unit, ringA, coef, active, fullA, emptyA, 0, dead, zb0, nblocks, u0, ptid); break;
+      case 5: produce_gw_k<5>(p, unit, ringA, coef, active, fullA, emptyA, 0, dead, zb0, nblocks, u0, ptid); break;
+      default: break;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -850,7 +857,7 @@ extern "C" int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* a, void*
     configured = true;
   }
   dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_tasks);
-  fctp_fused_forward_kernel<<<grid, kThreadsF, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mw, p);
+  fctp_fused_forward_kernel<<<grid, kThreadsFwd, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mw, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -904,11 +911,11 @@ extern "C" int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* a, void* s
   if (a->num_units < 1 || a->num_units > CUEQ_FCTP_FUSED_MAX_WUNITS) return cueq::fail("fctp fused gw: between 1 and %d units", CUEQ_FCTP_FUSED_MAX_WUNITS);
   for (int t = 0; t < a->num_units; ++t) {
     const cueq_fctp_fused_wunit& u = a->units[t];
-    const bool okd = (u.d1 == 1 || u.d1 == 3 || u.d1 == 5) && (u.d2 == 1 || u.d2 == 3 || u.d2 == 5) && (u.d3 == 1 || u.d3 == 3 || u.d3 == 5);
+    const bool okd = (u.d1 == 1 || u.d1 == 3 || u.d1 == 5) && (u.d2 == 1 || u.d2 == 3 || u.d2 == 5);
     if (!okd) return cueq::fail("fctp fused gw: irrep dimensions must be 1, 3 or 5 (unit %d)", t);
     if (u.off1 < 0 || u.off2 < 0 || (u.off1 % 8) || (u.off2 % 8)) return cueq::fail("fctp fused gw: segment offsets must be non-negative multiples of 8 elements");
     if (u.off1 + u.d1 * 64 > a->ld1 || u.off2 + u.d2 * 64 > a->ld2) return cueq::fail("fctp fused gw: segment of unit %d exceeds the row", t);
-    if (u.goff < 0 || (u.goff % 8) || u.goff + u.d3 * 64 > a->ldg) return cueq::fail("fctp fused gw: cotangent block of unit %d is outside the row", t);
+    if (u.goff < 0 || (u.goff % 8) || u.goff + 64 > a->ldg) return cueq::fail("fctp fused gw: cotangent block of unit %d is outside the row", t);
     if (u.w_row0 < 0 || (int64_t)u.w_row0 + 4096 > a->w_rows) return cueq::fail("fctp fused gw: weight block of unit %d is outside the weight array", t);
   }
   if ((a->ld1 % 8) || (a->ld2 % 8) || (a->ldg % 8)) return cueq::fail("fctp fused gw: row pitches must be multiples of 8 elements");
@@ -938,7 +945,7 @@ extern "C" int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* a, void* s
     configured = true;
   }
   dim3 grid((unsigned)splits, (unsigned)a->num_units, 64 / (2 * kTilesW));
-  fctp_fused_gw_kernel<<<grid, kThreadsF, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, p);
+  fctp_fused_gw_kernel<<<grid, kThreadsFwd, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

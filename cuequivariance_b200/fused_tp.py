@@ -342,15 +342,15 @@ class DenseUVW:
         for p in d.paths:
             sw, s1, s2, so = p.indices
             d1, d2, d3 = p.coefficients.shape
-            u = _lib.FctpFusedWUnit()
-            u.off1, u.off2, u.d1, u.d2, u.d3 = off[1][s1], off[2][s2], d1, d2, d3
-            u.w_row0, u.goff = off[0][sw] // 64, off[3][so]
             for k in range(d3):
+                u = _lib.FctpFusedWUnit()
+                u.off1, u.off2, u.d1, u.d2 = off[1][s1], off[2][s2], d1, d2
+                u.w_row0, u.goff = off[0][sw] // 64, off[3][so] + k * 64
                 for i in range(d1):
                     for j in range(d2):
-                        u.c[k][i * 5 + j] = float(p.coefficients[i, j, k])
-            units.append(u)
-        self._wunits = (_lib.FctpFusedWUnit * len(units))(*units) if len(units) <= 16 else None
+                        u.c[i * 5 + j] = float(p.coefficients[i, j, k])
+                units.append(u)
+        self._wunits = (_lib.FctpFusedWUnit * len(units))(*units) if len(units) <= 48 else None
         return self._wunits
 
     def _fused_gw(self, w, x1b, x2b, gout16, status):

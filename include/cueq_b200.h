@@ -310,16 +310,16 @@ int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* args, void* stream);
 
 /* Gradient of the same product with respect to the (shared) weights:
  *   gw[(u, v), w] += sum_z sum_k (sum_ij C[i, j, k] x1[z, i, u] x2[z, j, v]) gout[z, k, w]
- * One unit per path; gw is the float32 array [w_rows, 64] laid out like W and is accumulated
- * into (zero it first). */
-#define CUEQ_FCTP_FUSED_MAX_WUNITS 16
+ * One unit per (path, component k); gw is the float32 array [w_rows, 64] laid out like W and
+ * is accumulated into (zero it first). */
+#define CUEQ_FCTP_FUSED_MAX_WUNITS 48
 typedef struct {
   int32_t off1, off2;   /* element offsets of the path's x1 / x2 segments                          */
-  int32_t d1, d2, d3;
+  int32_t d1, d2;
   int32_t w_row0;       /* first row of the path's block in gw                                     */
-  int32_t goff;         /* element offset of the path's output irrep in a cotangent row            */
-  int32_t reserved;
-  float c[5][25];       /* c[k][i * 5 + j] = C[i, j, k]                                            */
+  int32_t goff;         /* element offset of component k of the path's output irrep in a cotangent row */
+  float c[25];          /* c[i * 5 + j] = C[i, j, k]                                               */
+  float reserved;
 } cueq_fctp_fused_wunit;
 typedef struct {
   const void* x1;       /* device bf16 [batch, ld1]                                                */
