@@ -202,6 +202,7 @@ def main():
 
     import cuequivariance_b200 as cb
     from cuequivariance_b200 import profiling
+    from cuequivariance_b200.dense import linear_f32x3
     from cuequivariance_b200.distributed import ReceiverShardedChannelWise, shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -346,7 +347,8 @@ def main():
             d_rcv.copy_(h_rcv, non_blocking=True)
             nodes = d_x1.detach().requires_grad_(True)
             r = d_vec.norm(dim=1)
-            ww = mlp(bessel(r))
+            hidden = mlp[1](mlp[0](bessel(r)))
+            ww = linear_f32x3(hidden, mlp[2].weight, mlp[2].bias)   # the wide output layer on the tensor cores
             yy = sh(d_vec)
             out = op(nodes, yy, ww, d_snd, d_rcv)
             loss = (out * cot).sum()
@@ -371,7 +373,7 @@ def main():
         h2d = h_x1.numel() * 4 + h_vec.numel() * 4 + h_snd.numel() * 4 + h_rcv.numel() * 4
         e2e = {"value": E / (float(t[0]) * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                "ms_per_step": float(t[0]),
-               "includes": "H2D of node features, edge vectors, indices; radial MLP and spherical harmonics on device; "
+               "includes": "H2D of node features, edge vectors, indices; radial MLP (output layer: this library's 3xTF32 tcgen05 GEMM) and spherical harmonics on device; "
                            "TP fwd; backward to node features and MLP parameters; D2H of the scalar"}
 
     cpu = None

@@ -1,0 +1,273 @@
+// float32-accurate GEMM on the tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]), K = 32 or 64.
+//
+// The dense layer that turns per-edge radial features into the per-edge weights of a channelwise
+// tensor product (h[E,64] x W[2944,64]^T -> w[E,2944]; the pattern of
+// cuequivariance_torch/layers/tp_conv_fully_connected.py:145-152,219-238) is too large for the
+// CUDA cores to be cheap (0.39 TFLOP at 1M edges) and must keep float32 accuracy, which one TF32
+// pass (10 mantissa bits) does not.  Each operand is therefore split into two TF32-exact halves,
+// x = hi + lo with hi = x rounded to TF32 (19 bits) and lo = (x - hi) rounded likewise, and three
+// tcgen05.mma kind::tf32 passes accumulate hi*hi + hi*lo + lo*hi in float32 in TMEM; the dropped
+// lo*lo term and the rounding of lo are below 2^-21 relative.
+//
+// One CTA owns 128 rows of A: the tile arrives by TMA and is split in place by four warps (the
+// operation is element-wise, so it does not care about the 128-byte swizzle); B arrives already
+// split (two float32 arrays prepared once by the caller) in 128-row tiles; two threads issue the
+// MMAs for alternate column tiles, each with its own B stage and its own pair of TMEM
+// accumulators, and four epilogue warps add the bias and send the rows out through shared memory
+// and TMA stores (whole 128-byte lines).
+// Warp roles: 0 = TMA, 1 and 10 = MMA issue (1 owns TMEM), 2-5 = epilogue, 6-9 = split.
+// Every wait is bounded (status word 2 on timeout; the CTA still reaches its end and frees TMEM).
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace cueq_tc;
+
+constexpr int XM = 128, XN = 128, XKB = 32;            // tile; XKB float32 = 128 bytes = one swizzle row
+constexpr int kBlkA = XM * XKB * 4;                     // 16 KiB per K block of A
+constexpr int kBlkB = XN * XKB * 4;                     // 16 KiB per K block of a B tile
+constexpr int kMaxKB = 2;                               // K <= 64
+constexpr int kThreadsX = 11 * 32;
+
+struct XParams {
+  float* C;
+  const float* bias;
+  int64_t ldc;
+  int M, N, nkb;
+  int* status;
+};
+
+__device__ __forceinline__ void umma_tf32(unsigned tmem_c, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+               ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// float32 bits rounded to TF32 (10 mantissa bits, ties away from zero; the low 13 bits come out zero)
+__device__ __forceinline__ unsigned rna_tf32(unsigned bits) {
+  unsigned r;
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(__uint_as_float(bits)));
+  return r;
+}
+__device__ __forceinline__ void bar_arrive1(unsigned long long* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(b)) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_bhi,
+                                                                  const __grid_constant__ CUtensorMap map_blo,
+                                                                  const __grid_constant__ CUtensorMap map_c,
+                                                                  const XParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_hi = smem;                                  // [nkb][128 rows][128 B]
+  unsigned char* a_lo = a_hi + kMaxKB * kBlkA;
+  unsigned char* b_st = a_lo + kMaxKB * kBlkA;                 // 2 stages x (hi [nkb] + lo [nkb])
+  constexpr int kStageB = 2 * kMaxKB * kBlkB;
+  unsigned char* stage_c = b_st + 2 * kStageB;                 // per epilogue warp: 2 x [32 rows][128 B], swizzled
+  unsigned long long* fullA = reinterpret_cast<unsigned long long*>(stage_c + 4 * 2 * 4096);
+  unsigned long long* readyA = fullA + 1;
+  unsigned long long* fullB = readyA + 1;      // [2]
+  unsigned long long* emptyB = fullB + 2;      // [2]
+  unsigned long long* accfull = emptyB + 2;    // [4]
+  unsigned long long* accempty = accfull + 4;  // [4]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(accempty + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * XM;
+  const int ntiles = (p.N + XN - 1) / XN;
+  const int nkb = p.nkb;
+
+  if (threadIdx.x == 0) {
+    bar_init(fullA, 1);
+    bar_init(readyA, 4);
+    for (int s = 0; s < 2; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
+    for (int b = 0; b < 4; ++b) { bar_init(accfull + b, 1); bar_init(accempty + b, 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bar_expect_tx(fullA, nkb * kBlkA);
+      for (int kb = 0; kb < nkb; ++kb) tma_load_2d(a_hi + kb * kBlkA, &map_a, kb * XKB, m0, fullA);
+      for (int t = 0; t < ntiles; ++t) {
+        const int s = t & 1;
+        if (!bar_wait(emptyB + s, ((t >> 1) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(fullB + s, 2 * nkb * kBlkB);
+        unsigned char* st = b_st + s * kStageB;
+        for (int kb = 0; kb < nkb; ++kb) {
+          tma_load_2d(st + kb * kBlkB, &map_bhi, kb * XKB, t * XN, fullB + s);
+          tma_load_2d(st + (kMaxKB + kb) * kBlkB, &map_blo, kb * XKB, t * XN, fullB + s);
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 10) {
+    if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
+      // D = f32, A = B = tf32, both K-major, N = 128, M = 128
+      const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(XN >> 3) << 17) | ((unsigned)(XM >> 4) << 24);
+      bool ok = bar_wait(readyA, 0, p.status);
+      for (int t = me; t < ntiles && ok; t += 2) {
+        const int n = t >> 1;                 // this issuer's n-th tile
+        const int buf = me * 2 + (n & 1);
+        ok = bar_wait(fullB + me, n & 1, p.status);
+        if (ok) ok = bar_wait(accempty + buf, ((n >> 1) & 1) ^ 1, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned char* st = b_st + me * kStageB;
+        unsigned acc = 0;
+        for (int kb = 0; kb < nkb; ++kb) {
+          const unsigned long long dah = smem_desc(a_hi + kb * kBlkA), dal = smem_desc(a_lo + kb * kBlkA);
+          const unsigned long long dbh = smem_desc(st + kb * kBlkB), dbl = smem_desc(st + (kMaxKB + kb) * kBlkB);
+#pragma unroll
+          for (int kk = 0; kk < XKB / 8; ++kk) {   // one instruction covers 8 float32 of K = 32 bytes = 2 descriptor units
+            umma_tf32(tmem_base + buf * XN, dal + 2ull * kk, dbh + 2ull * kk, idesc, acc);
+            acc = 1;
+            umma_tf32(tmem_base + buf * XN, dah + 2ull * kk, dbl + 2ull * kk, idesc, 1u);
+            umma_tf32(tmem_base + buf * XN, dah + 2ull * kk, dbh + 2ull * kk, idesc, 1u);
+          }
+        }
+        umma_commit(emptyB + me);
+        umma_commit(accfull + buf);
+      }
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    bool dead = false;
+    for (int t = 0; t < ntiles; ++t) {
+      const int me = t & 1, n = t >> 1;
+      const int buf = me * 2 + (n & 1);
+      if (!dead) dead = !bar_wait(accfull + buf, (n >> 1) & 1, p.status);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int part = 0; part < XN / 32; ++part) {
+        unsigned v[32];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                       "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                       "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                     : "r"(tmem_base + ((unsigned)(q * 32) << 16) + buf * XN + part * 32));
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        const int col0 = t * XN + part * 32;
+        // rows leave through shared memory and a TMA store, so that global writes are whole 128-byte
+        // lines (a lane-per-row store would touch 32 rows per instruction)
+        unsigned char* mine = stage_c + (q * 2 + (part & 1)) * 4096;
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");   // the store that used this buffer two parts ago has read it
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+          if (p.bias && col0 + c < p.N) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + c));
+            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+          }
+          *reinterpret_cast<float4*>(mine + lane * 128 + (((c >> 2) ^ (lane & 7)) << 4)) = o;
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (!dead && col0 < p.N && m0 + q * 32 < p.M)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                         ::"l"(&map_c), "r"(s32(mine)), "r"(col0), "r"(m0 + q * 32) : "memory");
+          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive1(accempty + buf);
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+  } else if (warp < 10) {
+    // split the A tile: hi overwrites the raw values, lo goes to the twin buffer at the same offset
+    const int tid = threadIdx.x - 6 * 32;
+    const bool ok = bar_wait(fullA, 0, p.status);
+    if (ok) {
+      uint4* hi = reinterpret_cast<uint4*>(a_hi);
+      uint4* lo = reinterpret_cast<uint4*>(a_lo);
+      for (int idx = tid; idx < nkb * kBlkA / 16; idx += 128) {
+        uint4 x = hi[idx], h, l;
+        h.x = rna_tf32(x.x); h.y = rna_tf32(x.y); h.z = rna_tf32(x.z); h.w = rna_tf32(x.w);
+        l.x = rna_tf32(__float_as_uint(__uint_as_float(x.x) - __uint_as_float(h.x)));
+        l.y = rna_tf32(__float_as_uint(__uint_as_float(x.y) - __uint_as_float(h.y)));
+        l.z = rna_tf32(__float_as_uint(__uint_as_float(x.z) - __uint_as_float(h.z)));
+        l.w = rna_tf32(__float_as_uint(__uint_as_float(x.w) - __uint_as_float(h.w)));
+        hi[idx] = h;
+        lo[idx] = l;
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) bar_arrive1(readyA);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// float32 [rows][cols] with `ld` elements between rows; box = 32 columns (128 bytes) x box_rows
+int make_map_f32(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cueq::fail("gemm f32x3: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)XKB, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cueq::fail("gemm f32x3: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream) {
+  if (!g || !g->A || !g->B_hi || !g->B_lo || !g->C) return cueq::fail("gemm f32x3: null operand");
+  if (g->M <= 0 || g->N <= 0) return 0;
+  if (g->K != 32 && g->K != 64) return cueq::fail("gemm f32x3: K must be 32 or 64 (got %lld)", (long long)g->K);
+  if (g->N % 4) return cueq::fail("gemm f32x3: N must be a multiple of 4");
+  if ((g->lda % 4) || (g->ldb % 4) || (g->ldc % 4)) return cueq::fail("gemm f32x3: leading dimensions must keep rows 16-byte aligned");
+  if (((uintptr_t)g->A | (uintptr_t)g->B_hi | (uintptr_t)g->B_lo | (uintptr_t)g->C | (uintptr_t)g->bias) & 15)
+    return cueq::fail("gemm f32x3: operands must be 16-byte aligned");
+  if (g->M > 2147483647LL - XM || g->N > 2147483647LL - XN) return cueq::fail("gemm f32x3: dimension too large");
+  CUtensorMap ma, mh, ml;
+  if (int rc = make_map_f32(&ma, g->A, g->M, g->K, g->lda, XM)) return rc;
+  if (int rc = make_map_f32(&mh, g->B_hi, g->N, g->K, g->ldb, XN)) return rc;
+  if (int rc = make_map_f32(&ml, g->B_lo, g->N, g->K, g->ldb, XN)) return rc;
+  CUtensorMap mc;
+  if (int rc = make_map_f32(&mc, g->C, g->M, g->N, g->ldc, 32)) return rc;
+  XParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.C = reinterpret_cast<float*>(g->C);
+  p.bias = reinterpret_cast<const float*>(g->bias);
+  p.ldc = g->ldc; p.M = (int)g->M; p.N = (int)g->N; p.nkb = (int)(g->K / XKB);
+  p.status = reinterpret_cast<int*>(g->status);
+  const size_t smem = 2 * kMaxKB * kBlkA + 2 * 2 * kMaxKB * kBlkB + 4 * 2 * 4096 + 256 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)((g->M + XM - 1) / XM));
+  gemm_f32x3_kernel<<<grid, kThreadsX, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mh, ml, mc, p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -76,7 +76,7 @@ const char* cueq_b200_last_error(void);
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
    3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
    7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit,
-   10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit; -1 for any other number. */
+   10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit, 12 cueq_gemm_f32x3_args; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -208,6 +208,24 @@ int cueq_b200_gemm_bf16(const cueq_gemm_args* args, void* stream);
 int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
                            int64_t lda, int64_t ldb, int64_t ldc, int32_t accumulate, void* status,
                            void* stream);
+
+/* float32-accurate dense layer on the tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]),
+ * K = 32 or 64, every operand float32.  Three TF32 passes over operands split as x = hi + lo
+ * (hi = x rounded to TF32, i.e. to 10 mantissa bits, lo = (x - hi) rounded likewise): the caller
+ * passes B already split (B_hi, B_lo, same shape and pitch), A is split inside the kernel.
+ * The layer that produces per-edge tensor-product weights from edge scalars in the reference's
+ * convolution (cuequivariance_torch/layers/tp_conv_fully_connected.py:145-152,219-238) has this
+ * shape.  C is written (not accumulated); rows of A, B, C and bias must be 16-byte aligned. */
+typedef struct {
+  const void* A;        /* device float32 [M, lda]                                                 */
+  const void* B_hi;     /* device float32 [N, ldb]                                                 */
+  const void* B_lo;     /* device float32 [N, ldb]                                                 */
+  const void* bias;     /* nullable device float32 [N]                                             */
+  void* C;              /* device float32 [M, ldc]                                                 */
+  int64_t M, N, K, lda, ldb, ldc;
+  void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
+} cueq_gemm_f32x3_args;
+int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* args, void* stream);
 
 /* ---- fully connected ("uvw") tensor product: kernels around the tensor-core GEMM -----------------
  *

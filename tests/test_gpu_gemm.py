@@ -8,6 +8,8 @@ import torch
 
 from cuequivariance_b200 import _lib
 
+DEV = "cuda:0"
+
 pytestmark = pytest.mark.gpu
 
 
@@ -81,3 +83,28 @@ def test_gemm_grouped_rows_and_bf16_output():
     assert torch.count_nonzero(buf[:, :8]) == 0 and torch.count_nonzero(buf[:, 200:]) == 0
     got = _gemm_general(a, b, M, N, K, out_bf16=True)
     assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-1)
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(1000, 2944, 64, True), (300, 132, 32, True), (128, 128, 64, False), (5, 4, 32, True)])
+def test_linear_f32x3_against_float64(M, N, K, bias):
+    """Three-pass TF32 dense layer (csrc/gemm_f32x3.cu) against a float64 matmul of the same float32
+    inputs: float32 accuracy, |err| <= 1e-5 of the result's scale (a single TF32 pass is ~1e-3);
+    ragged M and N exercise the clipped TMA loads and stores.  Gradients: against torch autograd."""
+    from cuequivariance_b200.dense import linear_f32x3, split_tf32
+
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    x = torch.randn(M, K, generator=g, device=DEV, requires_grad=True)
+    w = (torch.randn(N, K, generator=g, device=DEV) / 8).requires_grad_(True)
+    b = torch.randn(N, generator=g, device=DEV, requires_grad=True) if bias else None
+    hi, lo = split_tf32(w.detach())
+    assert int((hi.view(torch.int32) & 8191).abs().max()) == 0 and int((lo.view(torch.int32) & 8191).abs().max()) == 0
+    assert float((hi + lo - w.detach()).abs().max()) <= 2.0 ** -20 * float(w.detach().abs().max())
+    y = linear_f32x3(x, w, b)
+    ref = x.detach().double() @ w.detach().double().t() + (b.detach().double() if bias else 0.0)
+    scale = float(ref.abs().max())
+    assert float((y.detach().double() - ref).abs().max()) <= 1e-5 * scale
+    cot = torch.randn(M, N, generator=g, device=DEV)
+    got = torch.autograd.grad(y, [x, w] + ([b] if bias else []), cot)
+    want = torch.autograd.grad(torch.nn.functional.linear(x, w, b), [x, w] + ([b] if bias else []), cot)
+    for a, c in zip(got, want):
+        assert float((a - c).abs().max()) <= 1e-4 * max(1.0, float(c.abs().max()))
