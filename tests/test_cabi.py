@@ -110,3 +110,76 @@ def test_lowering_matches_reference_serialisation(golden):
     assert s["num_paths"] == [353]
     assert np.array_equal(np.array(s["path_indices"]).reshape(353, 4), g["cw_l3_flat/op0_indices"])
     assert np.abs(np.array(s["path_coefficients"]) - g["cw_l3_flat/op0_coefficients"]).max() < 1e-14
+
+
+def test_binding_struct_sizes_match_the_library():
+    L = _lib.lib()
+    structs = (_lib.U1dDesc, _lib.Buffer, _lib.CwArgs, _lib.CwNoAllocArgs, _lib.GemmArgs, _lib.FctpArgs, _lib.FctpFusedArgs,
+               _lib.FctpFusedTask, _lib.FctpFusedGxArgs, _lib.FctpFusedUnit, _lib.FctpFusedGwArgs, _lib.FctpFusedWUnit,
+               _lib.GemmF32x3Args)
+    for which, st in enumerate(structs):
+        assert L.cueq_b200_sizeof(which) == C.sizeof(st), st.__name__
+    assert L.cueq_b200_sizeof(len(structs)) == -1
+
+
+def test_tensor_core_entry_points_validate_before_launching():
+    """Argument checks run on the host before any CUDA call, so they can be exercised without a GPU."""
+    L = _lib.lib()
+    a = _lib.FctpFusedArgs()
+    assert L.cueq_b200_fctp_fused_forward(C.byref(a), None) != 0 and b"null" in L.cueq_b200_last_error()
+    g = _lib.FctpFusedGxArgs()
+    assert L.cueq_b200_fctp_fused_gx(C.byref(g), None) != 0 and b"null" in L.cueq_b200_last_error()
+    w = _lib.FctpFusedGwArgs()
+    assert L.cueq_b200_fctp_fused_gw(C.byref(w), None) != 0 and b"null" in L.cueq_b200_last_error()
+    x = _lib.GemmF32x3Args()
+    x.A = x.B_hi = x.B_lo = x.C = 4096
+    x.M, x.N, x.K, x.lda, x.ldb, x.ldc = 128, 128, 48, 48, 48, 128
+    assert L.cueq_b200_gemm_f32x3(C.byref(x), None) != 0 and b"K must be 32 or 64" in L.cueq_b200_last_error()
+    x.K = x.lda = x.ldb = 64
+    x.N = 130
+    assert L.cueq_b200_gemm_f32x3(C.byref(x), None) != 0 and b"multiple of 4" in L.cueq_b200_last_error()
+
+
+def test_fused_fully_connected_tables():
+    """Host tables of the fused fully connected kernels for 64x0e+64x1o+64x2e (11 paths):
+    9 forward tasks = (output irrep, component), 23 x-gradient units (<= 2 components each),
+    35 weight-gradient units = (path, component); the coupling columns they carry reproduce the
+    descriptor's coefficients."""
+    import numpy as np
+
+    from cuequivariance_b200 import descriptors as D
+    from cuequivariance_b200.fused_tp import DenseUVW
+
+    s = "64x0e+64x1o+64x2e"
+    e = D.fully_connected_tensor_product(s, s, s)
+    dense = DenseUVW(e.polynomial, None)
+    tasks, u1, u2, wu = dense._fused_tasks(), dense._fused_units(1), dense._fused_units(2), dense._fused_wunits()
+    assert len(tasks) == 9 and len(u1) == 23 and len(u2) == 23 and len(wu) == 35
+    assert sorted(t.num_paths for t in tasks) == [3, 4, 4, 4, 4, 4, 4, 4, 4]
+    d = dense.d
+    total = sum(float(np.abs(p.coefficients).sum()) for p in d.paths)
+    from_tasks = sum(abs(t.paths[q].c[i]) for t in tasks for q in range(t.num_paths) for i in range(25))
+    from_w = sum(abs(u.c[i]) for u in wu for i in range(25))
+    from_x = sum(abs(u.c[k][i]) for u in u1 for k in range(u.nk) for i in range(25))
+    for got in (from_tasks, from_w, from_x):
+        assert abs(got - total) <= 1e-5 * total
+    # x2 units carry the transposed coupling
+    p0 = d.paths[-1]
+    ua, ub = u1[-1], u2[-1]
+    k = ua.nk - 1
+    for i in range(p0.coefficients.shape[0]):
+        for j in range(p0.coefficients.shape[1]):
+            assert ua.c[k][i * 5 + j] == ub.c[k][j * 5 + i]
+
+
+def test_split_tf32_halves():
+    import torch
+
+    from cuequivariance_b200.dense import split_tf32
+
+    x = torch.randn(4096, generator=torch.Generator().manual_seed(0)) * 3
+    hi, lo = split_tf32(x)
+    assert int((hi.view(torch.int32) & 8191).abs().max()) == 0
+    assert int((lo.view(torch.int32) & 8191).abs().max()) == 0
+    assert float((hi + lo - x).abs().max()) <= 2.0 ** -21 * float(x.abs().max())
+    assert float((hi - x).abs().max()) <= 2.0 ** -11 * float(x.abs().max())
