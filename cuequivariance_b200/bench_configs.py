@@ -131,9 +131,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="all")
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--edges4", type=int, default=65536, help="config 4: number of edges (nodes = edges / 16 ... 32)")
+    ap.add_argument("--nodes4", type=int, default=4096)
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
-    fns = {"0": config0, "1": config1, "2": config2, "2bf16": config2_bf16, "4": config4}
+    fns = {"0": config0, "1": config1, "2": config2, "2bf16": config2_bf16,
+           "4": lambda steps, dev: config4(steps, dev, a.edges4, a.nodes4)}
     for key in (fns if a.config == "all" else [a.config]):
         print(json.dumps(fns[key](a.steps, dev)), flush=True)
 
