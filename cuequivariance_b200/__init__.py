@@ -15,6 +15,7 @@ from .operations import (
     SphericalHarmonics,
     spherical_harmonics,
     EquivariantTensorProduct,
+    Linear,
 )
 
 __version__ = "0.1.0"

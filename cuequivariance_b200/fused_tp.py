@@ -59,9 +59,39 @@ def flattened_path_count(poly: Polynomial) -> int:
     return n
 
 
+def _flatten_everything(poly: Polynomial) -> Polynomial:
+    def fn(d):
+        return d.flatten_modes("".join(d.modes()))
+
+    return poly.map_tensor_products(fn)
+
+
+def _total_path_count(poly: Polynomial) -> int:
+    n = 0
+    for _, d in poly.operations:
+        for p in d.paths:
+            dims = d.path_dims(p)
+            extra = int(np.prod([v for k, v in dims.items() if k not in d.coefficient_subscripts] or [1]))
+            n += extra * int(np.count_nonzero(p.coefficients)) if d.coefficient_subscripts else extra
+    return n
+
+
 class FusedTPProgram(Uniform1dProgram):
+    """Keeps the innermost mode of the output as the channel axis of the generic kernel and
+    flattens the rest.  When the segments that remain are not uniform (e.g. a linear map between
+    irreps of different multiplicities) every mode is flattened instead, as long as that stays
+    below ``FLATTEN_LIMIT`` paths."""
+
     def __init__(self, polynomial: Polynomial, math_dtype, output_dtype_map=None, name="segmented_polynomial"):
-        super().__init__(_flatten_all_but_inner(polynomial), math_dtype, output_dtype_map, name)
+        try:
+            super().__init__(_flatten_all_but_inner(polynomial), math_dtype, output_dtype_map, name)
+        except ValueError:
+            if _total_path_count(polynomial) > FLATTEN_LIMIT:
+                raise ValueError(
+                    f"{name}: the operands' segments are not uniform and flattening every mode would need "
+                    f"{_total_path_count(polynomial)} paths (limit {FLATTEN_LIMIT}); a dense route for this shape is not written"
+                )
+            super().__init__(_flatten_everything(polynomial), math_dtype, output_dtype_map, name)
 
 
 def is_fully_connected(poly: Polynomial) -> bool:

@@ -302,3 +302,41 @@ def test_fully_connected_tensor_core_route(in_dtype, fused, B, monkeypatch):
         scale = float(b.abs().max())
         err = float((a.float().cpu() - b).abs().max())
         assert err <= 2e-2 * scale, f"{name}: max abs diff {err:.3e} at scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+@pytest.mark.parametrize("classes", [1, 3])
+def test_linear_module_against_oracle(tag, classes):
+    """`Linear` (surface of cuequivariance_torch/operations/linear.py:30-191) against the oracle on the
+    descriptor's polynomial, with and without weight classes selected by `weight_indices`; the mul_ir
+    variant must equal the ir_mul one up to the layout transposition."""
+    dtype = DT[tag]
+    s_in, s_out = "6x0e+5x1o+4x2e", "3x0e+7x1o+2x2e+4x3o"
+    e = D.linear(s_in, s_out)
+    m = cb.Linear(s_in, s_out, layout=cb.ir_mul, internal_weights=False, shared_weights=True, weight_classes=classes, dtype=dtype)
+    gen = torch.Generator().manual_seed(5 + classes)
+    B = 11
+    x = torch.randn(B, m.irreps_in.dim, generator=gen, dtype=dtype)
+    w = torch.randn(classes, m.weight_numel, generator=gen, dtype=dtype)
+    cot = torch.randn(B, m.irreps_out.dim, generator=gen, dtype=dtype)
+    idx = torch.randint(0, classes, (B,), generator=gen) if classes > 1 else None
+
+    def ref_fn(w_, x_):
+        return naive.segmented_polynomial(e.polynomial, [w_, x_], {0: idx} if idx is not None else {})[0]
+
+    def got_fn(w_, x_):
+        return m(x_, w_, weight_indices=idx.to(DEV) if idx is not None else None)
+
+    ref = _derivatives(ref_fn, [w, x], cot)
+    got = _derivatives(got_fn, [w.to(DEV), x.to(DEV)], cot.to(DEV))
+    rtol, atol = TOL[tag]
+    _close(got[0], ref[0], rtol, atol, "out")
+    for a, b in zip(got[1], ref[1]):
+        _close(a, b, 10 * rtol, 10 * atol, "grad")
+    for a, b in zip(got[2], ref[2]):
+        _close(a, b, 100 * rtol, 100 * atol, "gradgrad")
+    m2 = cb.Linear(s_in, s_out, layout=cb.mul_ir, internal_weights=False, shared_weights=True, weight_classes=classes, dtype=dtype)
+    to_mul_ir = cb.TransposeIrrepsLayout(s_in, source=cb.ir_mul, target=cb.mul_ir)
+    back = cb.TransposeIrrepsLayout(s_out, source=cb.mul_ir, target=cb.ir_mul)
+    y2 = back(m2(to_mul_ir(x.to(DEV)), w.to(DEV), weight_indices=idx.to(DEV) if idx is not None else None))
+    _close(y2, got[0], rtol, atol, "mul_ir")
