@@ -1,4 +1,4 @@
-// float32-accurate GEMM on the tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]), K = 32 or 64.
+// float32-accurate GEMM on the tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]), K a multiple of 32.
 //
 // The dense layer that turns per-edge radial features into the per-edge weights of a channelwise
 // tensor product (h[E,64] x W[2944,64]^T -> w[E,2944]; the pattern of
@@ -52,6 +52,17 @@ __device__ __forceinline__ unsigned rna_tf32(unsigned bits) {
   unsigned r;
   asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(__uint_as_float(bits)));
   return r;
+}
+__device__ __forceinline__ void tmem_ld32x(unsigned taddr, unsigned (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 __device__ __forceinline__ void bar_arrive1(unsigned long long* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(b)) : "memory");
@@ -222,6 +233,166 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
   }
 }
 
+// ---- the same product for any K (a multiple of 32): both operands stream through a ring -----------
+//
+// Used when K is large (the input gradient of the layer above: gout[E,2944] x W[2944,64]).  Per
+// 32-wide K block a stage holds the raw A block (split in place by four warps into hi / lo twins)
+// and the matching pre-split B blocks; two threads issue the MMAs of alternate K blocks, dealt
+// round-robin to several accumulators, which the epilogue adds.  Warp roles as above.
+template <int NT>
+struct StreamCfg {
+  static constexpr int kBlkBn = NT * XKB * 4;
+  static constexpr int kStage = 2 * kBlkA + 2 * kBlkBn;
+  static constexpr int kStages = NT == 128 ? 3 : 4;
+  // The tensor core's float32 accumulation is not round-to-nearest: along one accumulator the error
+  // grew linearly with the number of instructions (3e-4 at K = 2944 against 1.4e-5 for a CUDA-core
+  // float32 GEMM).  K blocks are therefore dealt round-robin to kAcc accumulators (all 512 TMEM
+  // columns), which the epilogue adds on the CUDA cores.
+  static constexpr int kAcc = 512 / NT;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_stream_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                         const __grid_constant__ CUtensorMap map_bhi,
+                                                                         const __grid_constant__ CUtensorMap map_blo,
+                                                                         const __grid_constant__ CUtensorMap map_c,
+                                                                         const XParams p) {
+  using Cfg = StreamCfg<NT>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_c = smem + Cfg::kStages * Cfg::kStage;     // per epilogue warp: 2 x [32 rows][128 B], swizzled
+  unsigned long long* fullraw = reinterpret_cast<unsigned long long*>(stage_c + 4 * 2 * 4096);
+  unsigned long long* ready = fullraw + Cfg::kStages;
+  unsigned long long* empty = ready + Cfg::kStages;
+  unsigned long long* acc_ready = empty + Cfg::kStages;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * XM, n0 = blockIdx.y * NT;
+  const int nkb = p.nkb;
+  constexpr unsigned kCols = 512;      // Cfg::kAcc accumulators
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) { bar_init(fullraw + s, 1); bar_init(ready + s, 4); bar_init(empty + s, 1); }
+    bar_init(acc_ready, 2);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(kCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % Cfg::kStages;
+        if (!bar_wait(empty + s, ((kb / Cfg::kStages) & 1) ^ 1, p.status)) break;
+        unsigned char* st = smem + s * Cfg::kStage;
+        bar_expect_tx(fullraw + s, kBlkA + 2 * Cfg::kBlkBn);
+        tma_load_2d(st, &map_a, kb * XKB, m0, fullraw + s);
+        tma_load_2d(st + 2 * kBlkA, &map_bhi, kb * XKB, n0, fullraw + s);
+        tma_load_2d(st + 2 * kBlkA + Cfg::kBlkBn, &map_blo, kb * XKB, n0, fullraw + s);
+      }
+    }
+  } else if (warp == 1 || warp == 10) {
+    if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
+      const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(NT >> 3) << 17) | ((unsigned)(XM >> 4) << 24);
+      for (int kb = me; kb < nkb; kb += 2) {
+        const int s = kb % Cfg::kStages;
+        if (!bar_wait(ready + s, (kb / Cfg::kStages) & 1, p.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned char* st = smem + s * Cfg::kStage;
+        const unsigned long long dah = smem_desc(st), dal = smem_desc(st + kBlkA);
+        const unsigned long long dbh = smem_desc(st + 2 * kBlkA), dbl = smem_desc(st + 2 * kBlkA + Cfg::kBlkBn);
+        const unsigned tacc = tmem_base + (kb % Cfg::kAcc) * NT;
+        unsigned acc = kb >= Cfg::kAcc ? 1u : 0u;   // first block of this accumulator overwrites
+#pragma unroll
+        for (int kk = 0; kk < XKB / 8; ++kk) {
+          umma_tf32(tacc, dal + 2ull * kk, dbh + 2ull * kk, idesc, acc);
+          acc = 1;
+          umma_tf32(tacc, dah + 2ull * kk, dbl + 2ull * kk, idesc, 1u);
+          umma_tf32(tacc, dah + 2ull * kk, dbh + 2ull * kk, idesc, 1u);
+        }
+        umma_commit(empty + s);
+      }
+      umma_commit(acc_ready);
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    const bool ok = bar_wait(acc_ready, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+    for (int part = 0; part < NT / 32; ++part) {
+      unsigned v[32];
+      tmem_ld32x(tmem_base + ((unsigned)(q * 32) << 16) + part * 32, v);
+      for (int a = 1; a < Cfg::kAcc && a < nkb; ++a) {   // accumulators that received at least one K block
+        unsigned v2[32];
+        tmem_ld32x(tmem_base + ((unsigned)(q * 32) << 16) + a * NT + part * 32, v2);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(v2[c]));
+      }
+      const int col0 = n0 + part * 32;
+      unsigned char* mine = stage_c + (q * 2 + (part & 1)) * 4096;
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        float4 o = make_float4(__uint_as_float(v[c]), __uint_as_float(v[c + 1]), __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+        if (p.bias && col0 + c < p.N) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + c));
+          o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+        }
+        *reinterpret_cast<float4*>(mine + lane * 128 + (((c >> 2) ^ (lane & 7)) << 4)) = o;
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (ok && col0 < p.N && m0 + q * 32 < p.M)
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                       ::"l"(&map_c), "r"(s32(mine)), "r"(col0), "r"(m0 + q * 32) : "memory");
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+      }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+  } else if (warp < 10) {
+    const int tid = threadIdx.x - 6 * 32;
+    bool dead = false;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int s = kb % Cfg::kStages;
+      if (!dead) dead = !bar_wait(fullraw + s, (kb / Cfg::kStages) & 1, p.status);
+      if (!dead) {
+        uint4* hi = reinterpret_cast<uint4*>(smem + s * Cfg::kStage);
+        uint4* lo = reinterpret_cast<uint4*>(smem + s * Cfg::kStage + kBlkA);
+#pragma unroll 4
+        for (int idx = tid; idx < kBlkA / 16; idx += 128) {
+          uint4 x = hi[idx], h, l;
+          h.x = rna_tf32(x.x); h.y = rna_tf32(x.y); h.z = rna_tf32(x.z); h.w = rna_tf32(x.w);
+          l.x = rna_tf32(__float_as_uint(__uint_as_float(x.x) - __uint_as_float(h.x)));
+          l.y = rna_tf32(__float_as_uint(__uint_as_float(x.y) - __uint_as_float(h.y)));
+          l.z = rna_tf32(__float_as_uint(__uint_as_float(x.z) - __uint_as_float(h.z)));
+          l.w = rna_tf32(__float_as_uint(__uint_as_float(x.w) - __uint_as_float(h.w)));
+          hi[idx] = h;
+          lo[idx] = l;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive1(ready + s);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kCols) : "memory");
+  }
+}
+
 // float32 [rows][cols] with `ld` elements between rows; box = 32 columns (128 bytes) x box_rows
 int make_map_f32(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -242,17 +413,18 @@ int make_map_f32(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
 extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream) {
   if (!g || !g->A || !g->B_hi || !g->B_lo || !g->C) return cueq::fail("gemm f32x3: null operand");
   if (g->M <= 0 || g->N <= 0) return 0;
-  if (g->K != 32 && g->K != 64) return cueq::fail("gemm f32x3: K must be 32 or 64 (got %lld)", (long long)g->K);
+  if (g->K <= 0 || (g->K % 32)) return cueq::fail("gemm f32x3: K must be a positive multiple of 32 (got %lld)", (long long)g->K);
   if (g->N % 4) return cueq::fail("gemm f32x3: N must be a multiple of 4");
   if ((g->lda % 4) || (g->ldb % 4) || (g->ldc % 4)) return cueq::fail("gemm f32x3: leading dimensions must keep rows 16-byte aligned");
   if (((uintptr_t)g->A | (uintptr_t)g->B_hi | (uintptr_t)g->B_lo | (uintptr_t)g->C | (uintptr_t)g->bias) & 15)
     return cueq::fail("gemm f32x3: operands must be 16-byte aligned");
-  if (g->M > 2147483647LL - XM || g->N > 2147483647LL - XN) return cueq::fail("gemm f32x3: dimension too large");
-  CUtensorMap ma, mh, ml;
+  if (g->M > 2147483647LL - XM || g->N > 2147483647LL - XN || g->K > 2147483647LL) return cueq::fail("gemm f32x3: dimension too large");
+  const bool resident = g->K <= kMaxKB * XKB;          // A tile split once, reused for every column tile
+  const int nt = resident ? XN : (g->N <= 64 ? 64 : 128);
+  CUtensorMap ma, mh, ml, mc;
   if (int rc = make_map_f32(&ma, g->A, g->M, g->K, g->lda, XM)) return rc;
-  if (int rc = make_map_f32(&mh, g->B_hi, g->N, g->K, g->ldb, XN)) return rc;
-  if (int rc = make_map_f32(&ml, g->B_lo, g->N, g->K, g->ldb, XN)) return rc;
-  CUtensorMap mc;
+  if (int rc = make_map_f32(&mh, g->B_hi, g->N, g->K, g->ldb, nt)) return rc;
+  if (int rc = make_map_f32(&ml, g->B_lo, g->N, g->K, g->ldb, nt)) return rc;
   if (int rc = make_map_f32(&mc, g->C, g->M, g->N, g->ldc, 32)) return rc;
   XParams p;
   std::memset(&p, 0, sizeof(p));
@@ -260,14 +432,35 @@ extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream)
   p.bias = reinterpret_cast<const float*>(g->bias);
   p.ldc = g->ldc; p.M = (int)g->M; p.N = (int)g->N; p.nkb = (int)(g->K / XKB);
   p.status = reinterpret_cast<int*>(g->status);
-  const size_t smem = 2 * kMaxKB * kBlkA + 2 * 2 * kMaxKB * kBlkB + 4 * 2 * 4096 + 256 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned mtiles = (unsigned)((g->M + XM - 1) / XM);
+  if (resident) {
+    const size_t smem = 2 * kMaxKB * kBlkA + 2 * 2 * kMaxKB * kBlkB + 4 * 2 * 4096 + 256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+      CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    gemm_f32x3_kernel<<<dim3(mtiles), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
+  } else if (nt == 64) {
+    using Cfg = StreamCfg<64>;
+    const size_t smem = Cfg::kStages * Cfg::kStage + 4 * 2 * 4096 + 256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+      CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    gemm_f32x3_stream_kernel<64><<<dim3(mtiles, (unsigned)((g->N + 63) / 64)), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
+  } else {
+    using Cfg = StreamCfg<128>;
+    const size_t smem = Cfg::kStages * Cfg::kStage + 4 * 2 * 4096 + 256 + 1024;
+    static bool configured = false;
+    if (!configured) {
+      CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    gemm_f32x3_stream_kernel<128><<<dim3(mtiles, (unsigned)((g->N + 127) / 128)), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
   }
-  dim3 grid((unsigned)((g->M + XM - 1) / XM));
-  gemm_f32x3_kernel<<<grid, kThreadsX, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mh, ml, mc, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -1,15 +1,15 @@
 """float32-accurate dense layer on the tensor cores (three TF32 passes).
 
 ``linear_f32x3(x, weight, bias)`` computes ``x @ weight.T + bias`` like ``torch.nn.functional.linear``
-for float32 CUDA tensors with 32 or 64 input features.  It is meant for the layer that produces
+for float32 CUDA tensors whose number of input features is a multiple of 32.  It is meant for the layer that produces
 the per-edge weights of a channelwise tensor product from a few edge scalars (the pattern of the
 reference's convolution layer, cuequivariance_torch/layers/tp_conv_fully_connected.py:145-152,219-238):
 at 1M edges x 2,944 weights that layer is 0.39 TFLOP, an order of magnitude more time than the
 tensor product itself when it runs on the CUDA cores.
 
-The forward runs on this library's tcgen05 kernel (``csrc/gemm_f32x3.cu``).  The backward (input
-gradient and weight gradient, both reductions over the wide axis) uses device-side torch matmuls:
-INTERIM, a fused kernel for them is not written.
+The forward and the input gradient run on this library's tcgen05 kernels (``csrc/gemm_f32x3.cu``:
+one that keeps the split A tile resident for K <= 64, one that streams both operands for larger K).
+The weight gradient (a reduction over the rows) uses a device-side torch matmul: INTERIM.
 """
 from __future__ import annotations
 
@@ -29,52 +29,71 @@ def split_tf32(x: torch.Tensor):
     return hi, lo
 
 
+def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = "gemm_f32x3") -> torch.Tensor:
+    """``a [M, K] @ b[N, K].T (+ bias[N])`` in float32 accuracy on the tensor cores; K a multiple of 32,
+    N a multiple of 4."""
+    import ctypes as C
+
+    from . import _lib, profiling
+
+    if not (a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32):
+        raise RuntimeError("gemm_f32x3 needs float32 CUDA tensors (there is no CPU fallback)")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1] or a.shape[1] % 32 or a.shape[1] == 0:
+        raise ValueError(f"gemm_f32x3: a [M, K] and b [N, K] with K a multiple of 32; got {tuple(a.shape)}, {tuple(b.shape)}")
+    if b.shape[0] % 4:
+        raise ValueError("gemm_f32x3: the number of output columns must be a multiple of 4")
+    ac = a.contiguous()
+    hi, lo = split_tf32(b)
+    out = torch.empty((a.shape[0], b.shape[0]), dtype=torch.float32, device=a.device)
+    if a.shape[0] == 0:
+        return out
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    g = _lib.GemmF32x3Args()
+    g.A, g.B_hi, g.B_lo, g.C = ac.data_ptr(), hi.data_ptr(), lo.data_ptr(), out.data_ptr()
+    bc = None
+    if bias is not None:
+        bc = bias.contiguous()
+        g.bias = bc.data_ptr()
+    g.M, g.N, g.K = ac.shape[0], b.shape[0], ac.shape[1]
+    g.lda, g.ldb, g.ldc = ac.shape[1], hi.shape[1], out.shape[1]
+    g.status = status.data_ptr()
+    with torch.cuda.device(a.device):
+        with profiling.kernel(name):
+            _lib.check(_lib.lib().cueq_b200_gemm_f32x3(C.byref(g), C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)))
+    return out
+
+
 class _LinearF32x3(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
-        import ctypes as C
-
-        from . import _lib, profiling
-
-        if not (x.is_cuda and x.dtype == torch.float32 and weight.dtype == torch.float32):
-            raise RuntimeError("linear_f32x3 needs float32 CUDA tensors (there is no CPU fallback)")
-        if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1] or x.shape[1] not in (32, 64):
-            raise ValueError(f"linear_f32x3: x [M, K] and weight [N, K] with K = 32 or 64; got {tuple(x.shape)}, {tuple(weight.shape)}")
-        if weight.shape[0] % 4:
-            raise ValueError("linear_f32x3: the number of output features must be a multiple of 4")
-        xc = x.contiguous()
-        hi, lo = split_tf32(weight.detach())
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
-        status = torch.zeros(1, dtype=torch.int32, device=x.device)
-        a = _lib.GemmF32x3Args()
-        a.A, a.B_hi, a.B_lo, a.C = xc.data_ptr(), hi.data_ptr(), lo.data_ptr(), out.data_ptr()
-        bc = None
-        if bias is not None:
-            bc = bias.detach().contiguous()
-            a.bias = bc.data_ptr()
-        a.M, a.N, a.K = xc.shape[0], weight.shape[0], xc.shape[1]
-        a.lda, a.ldb, a.ldc = xc.shape[1], hi.shape[1], out.shape[1]
-        a.status = status.data_ptr()
-        with torch.cuda.device(x.device):
-            with profiling.kernel("gemm_f32x3"):
-                _lib.check(_lib.lib().cueq_b200_gemm_f32x3(C.byref(a), C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)))
+        out = gemm_f32x3(x, weight.detach(), bias.detach() if bias is not None else None)
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
-        ctx.status = status
         return out
 
     @staticmethod
     def backward(ctx, gout):
         x, weight = ctx.saved_tensors
-        prev = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = False
-        try:
-            gx = gout @ weight if ctx.needs_input_grad[0] else None
-            gw = gout.t() @ x if ctx.needs_input_grad[1] else None
-        finally:
-            torch.backends.cuda.matmul.allow_tf32 = prev
+        gout = gout.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            if weight.shape[0] % 32 == 0 and weight.shape[1] % 4 == 0:
+                gx = gemm_f32x3(gout, weight.detach().t().contiguous(), name="gemm_f32x3_gx")   # gout [M, N] x (W^T [K, N])^T
+            else:
+                gx = _full_precision_matmul(gout, weight)
+        if ctx.needs_input_grad[1]:
+            gw = _full_precision_matmul(gout.t(), x)   # INTERIM: library GEMM (reduction over the long axis)
         gb = gout.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return gx, gw, gb
+
+
+def _full_precision_matmul(a, b):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return a @ b
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
 
 
 def linear_f32x3(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -210,7 +210,7 @@ int cueq_b200_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, in
                            void* stream);
 
 /* float32-accurate dense layer on the tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]),
- * K = 32 or 64, every operand float32.  Three TF32 passes over operands split as x = hi + lo
+ * K a multiple of 32, every operand float32.  Three TF32 passes over operands split as x = hi + lo
  * (hi = x rounded to TF32, i.e. to 10 mantissa bits, lo = (x - hi) rounded likewise): the caller
  * passes B already split (B_hi, B_lo, same shape and pitch), A is split inside the kernel.
  * The layer that produces per-edge tensor-product weights from edge scalars in the reference's

@@ -134,7 +134,7 @@ def test_tensor_core_entry_points_validate_before_launching():
     x = _lib.GemmF32x3Args()
     x.A = x.B_hi = x.B_lo = x.C = 4096
     x.M, x.N, x.K, x.lda, x.ldb, x.ldc = 128, 128, 48, 48, 48, 128
-    assert L.cueq_b200_gemm_f32x3(C.byref(x), None) != 0 and b"K must be 32 or 64" in L.cueq_b200_last_error()
+    assert L.cueq_b200_gemm_f32x3(C.byref(x), None) != 0 and b"multiple of 32" in L.cueq_b200_last_error()
     x.K = x.lda = x.ldb = 64
     x.N = 130
     assert L.cueq_b200_gemm_f32x3(C.byref(x), None) != 0 and b"multiple of 4" in L.cueq_b200_last_error()

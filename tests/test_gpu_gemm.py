@@ -85,7 +85,8 @@ def test_gemm_grouped_rows_and_bf16_output():
     assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-1)
 
 
-@pytest.mark.parametrize("M,N,K,bias", [(1000, 2944, 64, True), (300, 132, 32, True), (128, 128, 64, False), (5, 4, 32, True)])
+@pytest.mark.parametrize("M,N,K,bias", [(1000, 2944, 64, True), (300, 132, 32, True), (128, 128, 64, False), (5, 4, 32, True),
+                                          (700, 64, 2944, False), (260, 200, 160, True), (64, 36, 96, True)])
 def test_linear_f32x3_against_float64(M, N, K, bias):
     """Three-pass TF32 dense layer (csrc/gemm_f32x3.cu) against a float64 matmul of the same float32
     inputs: float32 accuracy, |err| <= 1e-5 of the result's scale (a single TF32 pass is ~1e-3);
