@@ -29,9 +29,15 @@ def split_tf32(x: torch.Tensor):
     return hi, lo
 
 
-def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = "gemm_f32x3") -> torch.Tensor:
+def _rows_view_ok(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.data_ptr() % 16 == 0
+
+
+def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = "gemm_f32x3",
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a [M, K] @ b[N, K].T (+ bias[N])`` in float32 accuracy on the tensor cores; K a multiple of 32,
-    N a multiple of 4."""
+    N a multiple of 4.  ``a`` and ``out`` may be column slices of wider row-major tensors (unit stride
+    along the row, 16-byte aligned); ``out`` is overwritten."""
     import ctypes as C
 
     from . import _lib, profiling
@@ -42,9 +48,12 @@ def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = 
         raise ValueError(f"gemm_f32x3: a [M, K] and b [N, K] with K a multiple of 32; got {tuple(a.shape)}, {tuple(b.shape)}")
     if b.shape[0] % 4:
         raise ValueError("gemm_f32x3: the number of output columns must be a multiple of 4")
-    ac = a.contiguous()
+    ac = a if _rows_view_ok(a) else a.contiguous()
     hi, lo = split_tf32(b)
-    out = torch.empty((a.shape[0], b.shape[0]), dtype=torch.float32, device=a.device)
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[0]), dtype=torch.float32, device=a.device)
+    elif not (_rows_view_ok(out) and out.shape == (a.shape[0], b.shape[0]) and out.dtype == torch.float32):
+        raise ValueError("gemm_f32x3: `out` must be a float32 [M, N] view with unit stride along rows and 16-byte alignment")
     if a.shape[0] == 0:
         return out
     status = torch.zeros(1, dtype=torch.int32, device=a.device)
@@ -55,7 +64,7 @@ def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = 
         bc = bias.contiguous()
         g.bias = bc.data_ptr()
     g.M, g.N, g.K = ac.shape[0], b.shape[0], ac.shape[1]
-    g.lda, g.ldb, g.ldc = ac.shape[1], hi.shape[1], out.shape[1]
+    g.lda, g.ldb, g.ldc = ac.stride(0), hi.shape[1], out.stride(0)
     g.status = status.data_ptr()
     with torch.cuda.device(a.device):
         with profiling.kernel(name):

@@ -14,15 +14,73 @@ from ..segmented_polynomial import SegmentedPolynomial
 from ..transpose import TransposeIrrepsLayout
 
 
+DENSE_ROUTE = True      # float32, one weight set, multiplicities that are multiples of 32: tensor-core GEMMs
+DENSE_MIN_ROWS = 256    # below this the generic kernel is used
+
+
+class _DenseLinear(torch.autograd.Function):
+    """``uv,iu,iv`` with one shared weight set as one float32-accurate tensor-core GEMM per
+    (path, component): ``out[:, i-th block of the output irrep] = c * x[:, i-th block] @ W``.
+    Inputs and outputs are in the descriptor's ir_mul layout, so every block is a column slice."""
+
+    @staticmethod
+    def forward(ctx, plan, weight, x):
+        from ..dense import gemm_f32x3
+
+        out = torch.zeros((x.shape[0], plan["out_size"]), dtype=torch.float32, device=x.device)
+        seen = set()
+        for (wo, u, v, xo, oo, d, c) in plan["paths"]:
+            wt = (weight[0, wo : wo + u * v].reshape(u, v).t() * c).contiguous()       # [N = v][K = u]
+            for i in range(d):
+                dst = out[:, oo + i * v : oo + (i + 1) * v]
+                if oo in seen:
+                    dst += gemm_f32x3(x[:, xo + i * u : xo + (i + 1) * u], wt, name="linear_f32x3")
+                else:
+                    gemm_f32x3(x[:, xo + i * u : xo + (i + 1) * u], wt, name="linear_f32x3", out=dst)
+            seen.add(oo)
+        ctx.plan = plan
+        ctx.save_for_backward(weight, x)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gout):
+        from ..dense import _full_precision_matmul, gemm_f32x3
+
+        plan = ctx.plan
+        weight, x = ctx.saved_tensors
+        gout = gout.contiguous()
+        gw = torch.zeros_like(weight) if ctx.needs_input_grad[1] else None
+        gx = torch.zeros_like(x) if ctx.needs_input_grad[2] else None
+        seen = set()
+        for (wo, u, v, xo, oo, d, c) in plan["paths"]:
+            if gx is not None:
+                wc = (weight[0, wo : wo + u * v].reshape(u, v) * c).contiguous()        # [N = u][K = v]
+                for i in range(d):
+                    dst = gx[:, xo + i * u : xo + (i + 1) * u]
+                    if xo in seen:
+                        dst += gemm_f32x3(gout[:, oo + i * v : oo + (i + 1) * v], wc, name="linear_f32x3_gx")
+                    else:
+                        gemm_f32x3(gout[:, oo + i * v : oo + (i + 1) * v], wc, name="linear_f32x3_gx", out=dst)
+                seen.add(xo)
+            if gw is not None:
+                # reduction over the rows: INTERIM library GEMM
+                xs = x[:, xo : xo + d * u].reshape(-1, u)
+                gs = gout[:, oo : oo + d * v].reshape(-1, v)
+                gw[0, wo : wo + u * v] += (_full_precision_matmul(xs.t(), gs) * c).reshape(-1)
+        return None, gw, gx
+
+
 class Linear(torch.nn.Module):
     """``forward(x, weight=None, weight_indices=None)``; ``x``: ``[batch, irreps_in.dim]``;
     ``weight``: ``[1 or weight_classes, weight_numel]`` when shared (the module's own parameter
     when ``internal_weights``), ``[batch, weight_numel]`` otherwise; ``weight_indices``:
     ``[batch]`` class ids, required when ``weight_classes > 1``.
 
-    Executed by the CUDA executor on the polynomial ``uv,iu,iv`` flattened over ``u`` (the generic
-    kernel; a dense tensor-core route for large multiplicities is not written yet).  There is no
-    ``naive`` method and no fallback."""
+    float32 with one weight set and multiplicities that are multiples of 32 runs as float32-accurate
+    tensor-core GEMMs (``dense.gemm_f32x3``; first derivatives only, the weight gradient uses a library
+    GEMM for now); everything else runs on the generic kernel over the polynomial ``uv,iu,iv``
+    flattened over ``u``.  There is no ``naive`` method and no fallback."""
 
     def __init__(
         self,
@@ -67,7 +125,25 @@ class Linear(torch.nn.Module):
         self.transpose_out = TransposeIrrepsLayout(irreps_out, source=e.outputs[0].layout, target=IrrepsLayout.parse(layout_out or layout), device=device)
         if math_dtype is None and dtype in (torch.float32, torch.float64):
             math_dtype = dtype
-        self.f = SegmentedPolynomial(e.polynomial, method=self.method, math_dtype=math_dtype, name="linear")
+        # dense route: every multiplicity a multiple of 32 (K of the forward and of the input gradient)
+        _, d = e.polynomial.operations[0]
+        offs = [op.offsets() for op in d.operands]
+        paths = []
+        for p in d.paths:
+            sw, si, so = p.indices
+            u, v = d.operands[0].segments[sw]
+            dim = d.operands[1].segments[si][0]
+            paths.append((offs[0][sw], u, v, offs[1][si], offs[2][so], dim, float(p.coefficients)))
+        self._dense_plan = None
+        if paths and all(u % 32 == 0 and v % 32 == 0 for (_, u, v, _, _, _, _) in paths):
+            self._dense_plan = {"paths": paths, "out_size": d.operands[2].size}
+        try:
+            self.f = SegmentedPolynomial(e.polynomial, method=self.method, math_dtype=math_dtype, name="linear")
+            self._generic_error = None
+        except ValueError as err:   # mixed large multiplicities: only the dense route can run this shape
+            if self._dense_plan is None:
+                raise
+            self.f, self._generic_error = None, str(err)
 
     def extra_repr(self) -> str:
         return (f"shared_weights={self.shared_weights}, internal_weights={self.internal_weights}, "
@@ -85,5 +161,12 @@ class Linear(torch.nn.Module):
             input_indices[0] = weight_indices
         if weight is None:
             raise ValueError("Weights should not be None")
-        out = self.f([weight, self.transpose_in(x)], input_indices=input_indices)
+        xin = self.transpose_in(x)
+        if (self._dense_plan is not None and DENSE_ROUTE and not input_indices and weight.shape[0] == 1 and xin.is_cuda
+                and xin.dtype == torch.float32 and weight.dtype == torch.float32 and xin.shape[0] >= DENSE_MIN_ROWS):
+            return self.transpose_out(_DenseLinear.apply(self._dense_plan, weight, xin.contiguous()))
+        if self.f is None:
+            raise ValueError("Linear: this shape runs only on the dense route (float32 CUDA tensors, one weight set, at least "
+                             f"{DENSE_MIN_ROWS} rows); the generic kernel cannot take it: {self._generic_error}")
+        out = self.f([weight, xin], input_indices=input_indices)
         return self.transpose_out(out[0])

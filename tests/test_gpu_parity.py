@@ -340,3 +340,49 @@ def test_linear_module_against_oracle(tag, classes):
     back = cb.TransposeIrrepsLayout(s_out, source=cb.mul_ir, target=cb.ir_mul)
     y2 = back(m2(to_mul_ir(x.to(DEV)), w.to(DEV), weight_indices=idx.to(DEV) if idx is not None else None))
     _close(y2, got[0], rtol, atol, "mul_ir")
+
+
+def test_linear_dense_route_against_oracle():
+    """Multiplicities that are multiples of 32: `Linear` runs as float32-accurate tensor-core GEMMs
+    (three TF32 passes).  Output and first derivatives against the oracle in float32; the same module on
+    the generic kernel (dense route switched off) must agree as well."""
+    from cuequivariance_b200.operations import linear as linear_mod
+
+    s_in, s_out = "64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"
+    e = D.linear(s_in, s_out)
+    m = cb.Linear(s_in, s_out, layout=cb.mul_ir, internal_weights=False, shared_weights=True)
+    gen = torch.Generator().manual_seed(77)
+    B = 300
+    x = torch.randn(B, m.irreps_in.dim, generator=gen)
+    w = torch.randn(1, m.weight_numel, generator=gen)
+    cot = torch.randn(B, m.irreps_out.dim, generator=gen)
+    t_in = cb.TransposeIrrepsLayout(s_in, source=cb.mul_ir, target=cb.ir_mul, device="cpu") if False else None
+    del t_in
+
+    def grads(fn, xs, c):
+        xs = [t.clone().requires_grad_(True) for t in xs]
+        out = fn(*xs)
+        return [out.detach()] + list(torch.autograd.grad((out * c).sum(), xs))
+
+    profiling.reset()
+    profiling.enable()
+    try:
+        got = grads(lambda w_, x_: m(x_, w_), [w.to(DEV), x.to(DEV)], cot.to(DEV))
+        names = set(profiling.summary())
+    finally:
+        profiling.enable(False)
+    assert "linear_f32x3" in names and "linear_f32x3_gx" in names, names
+    old = linear_mod.DENSE_ROUTE
+    linear_mod.DENSE_ROUTE = False
+    try:
+        gen_route = grads(lambda w_, x_: m(x_, w_), [w.to(DEV), x.to(DEV)], cot.to(DEV))
+    finally:
+        linear_mod.DENSE_ROUTE = old
+    for name, a, b in zip(["out", "gw", "gx"], got, gen_route):
+        _close(a, b, 1e-4, 2e-5, name + " (dense vs generic)")
+    # oracle on the ir_mul polynomial: transpose on the device with the module's own transposes
+    to_ir_mul = cb.TransposeIrrepsLayout(s_in, source=cb.mul_ir, target=cb.ir_mul)
+    back = cb.TransposeIrrepsLayout(s_out, source=cb.mul_ir, target=cb.ir_mul)
+    x_im = to_ir_mul(x.to(DEV)).cpu()
+    ref = naive.segmented_polynomial(e.polynomial, [w, x_im])[0]
+    _close(back(got[0]).cpu(), ref, 1e-5, 2e-6, "out vs oracle")
