@@ -154,6 +154,14 @@ class GemmF32x3Args(C.Structure):
     ]
 
 
+class GemmF32x3TnArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("colsum", C.c_void_p),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+        ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -207,10 +215,11 @@ def lib() -> C.CDLL:
     L.cueq_b200_fctp_fused_gx.argtypes = [C.POINTER(FctpFusedGxArgs), C.c_void_p]
     L.cueq_b200_fctp_fused_gw.argtypes = [C.POINTER(FctpFusedGwArgs), C.c_void_p]
     L.cueq_b200_gemm_f32x3.argtypes = [C.POINTER(GemmF32x3Args), C.c_void_p]
+    L.cueq_b200_gemm_f32x3_tn.argtypes = [C.POINTER(GemmF32x3TnArgs), C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     L.cueq_b200_sizeof.restype = C.c_int64
-    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask, FctpFusedGxArgs, FctpFusedUnit, FctpFusedGwArgs, FctpFusedWUnit, GemmF32x3Args)):
+    for which, struct in enumerate((U1dDesc, Buffer, CwArgs, CwNoAllocArgs, GemmArgs, FctpArgs, FctpFusedArgs, FctpFusedTask, FctpFusedGxArgs, FctpFusedUnit, FctpFusedGwArgs, FctpFusedWUnit, GemmF32x3Args, GemmF32x3TnArgs)):
         if L.cueq_b200_sizeof(which) != C.sizeof(struct):
             raise CueqError(f"{struct.__name__}: this binding declares {C.sizeof(struct)} bytes, the library "
                             f"{L.cueq_b200_sizeof(which)}; rebuild the library or update the binding")

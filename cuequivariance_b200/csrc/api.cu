@@ -35,6 +35,7 @@ extern "C" int64_t cueq_b200_sizeof(int which) {
     case 10: return sizeof(cueq_fctp_fused_gw_args);
     case 11: return sizeof(cueq_fctp_fused_wunit);
     case 12: return sizeof(cueq_gemm_f32x3_args);
+    case 13: return sizeof(cueq_gemm_f32x3_tn_args);
     default: return -1;
   }
 }

@@ -393,6 +393,222 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_stream_kernel(const _
   }
 }
 
+// ---- reduction over rows: C[M,N] += sum_k A[k,M] * B[k,N]  (and colsum[M] += sum_k A[k,M]) --------
+//
+// The weight gradient of a dense layer (gout[E,2944]^T x h[E,64]) and its bias gradient.  Both
+// operands are stored with the reduction index as the row, i.e. transposed with respect to what
+// the K-major MMA wants: raw [32 x 128] / [32 x 64] blocks arrive by TMA without swizzle, and the
+// four split warps transpose them while they split them, writing K-major 128-byte-swizzled hi / lo
+// tiles (a thread reads four consecutive k of one column and stores one 16-byte chunk, so reads
+// and writes are both free of bank conflicts).  A constant extra row of B holding ones gives the
+// column sums of A from the same MMAs.  The K range is cut into slices of kTnBlocks blocks per CTA
+// (short accumulation chains, see StreamCfg) whose partial results are added with red.global.add.
+constexpr int TN_N = 64;                       // columns of B per CTA
+constexpr int TN_NB = 80;                      // rows of the B operand tile: 64 + ones row + padding to a multiple of 16
+constexpr int kTnRawA = 32 * XM * 4;           // 16 KiB
+constexpr int kTnRawB = 32 * TN_N * 4;         // 8 KiB
+constexpr int kTnRaw = kTnRawA + kTnRawB;      // 24 KiB
+constexpr int kTnRawStages = 3;
+constexpr int kTnOpB = TN_NB * 128;            // 10 KiB
+constexpr int kTnOp = 2 * kBlkA + 2 * kTnOpB + 3072;   // hi/lo of A and B, padded to a multiple of 1 KiB (55 KiB... 56 KiB)
+constexpr int kTnOpStages = 2;
+constexpr int kTnBlocks = 64;                  // K blocks (of 32 rows) per CTA
+
+struct TnParams {
+  float* C;
+  float* colsum;
+  int64_t ldc;
+  int M, N, K;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                     const __grid_constant__ CUtensorMap map_b,
+                                                                     const TnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* ops = smem;                                   // kTnOpStages x [A_hi | A_lo | B_hi | B_lo]
+  unsigned char* raws = ops + kTnOpStages * kTnOp;             // kTnRawStages x [raw A | raw B]
+  unsigned long long* fullraw = reinterpret_cast<unsigned long long*>(raws + kTnRawStages * kTnRaw);
+  unsigned long long* rawempty = fullraw + kTnRawStages;
+  unsigned long long* opready = rawempty + kTnRawStages;
+  unsigned long long* opempty = opready + kTnOpStages;
+  unsigned long long* acc_ready = opempty + kTnOpStages;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * XM, n0 = blockIdx.y * TN_N;
+  const int total_kb = (p.K + XKB - 1) / XKB;
+  const int kb0 = blockIdx.z * kTnBlocks;
+  const int nkb = min(kTnBlocks, total_kb - kb0);
+  const bool with_sum = p.colsum != nullptr && blockIdx.y == 0;
+  constexpr int kAcc = 4;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTnRawStages; ++s) { bar_init(fullraw + s, 1); bar_init(rawempty + s, 4); }
+    for (int s = 0; s < kTnOpStages; ++s) { bar_init(opready + s, 4); bar_init(opempty + s, 1); }
+    bar_init(acc_ready, 2);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int r = kb % kTnRawStages;
+        if (!bar_wait(rawempty + r, ((kb / kTnRawStages) & 1) ^ 1, p.status)) break;
+        unsigned char* raw = raws + r * kTnRaw;
+        bar_expect_tx(fullraw + r, kTnRaw);
+        tma_load_2d(raw, &map_a, m0, (kb0 + kb) * XKB, fullraw + r);
+        tma_load_2d(raw + kTnRawA, &map_b, n0, (kb0 + kb) * XKB, fullraw + r);
+      }
+    }
+  } else if (warp == 1 || warp == 10) {
+    if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
+      const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(TN_NB >> 3) << 17) | ((unsigned)(XM >> 4) << 24);
+      for (int kb = me; kb < nkb; kb += 2) {
+        const int o = kb % kTnOpStages;
+        if (!bar_wait(opready + o, (kb / kTnOpStages) & 1, p.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned char* st = ops + o * kTnOp;
+        const unsigned long long dah = smem_desc(st), dal = smem_desc(st + kBlkA);
+        const unsigned long long dbh = smem_desc(st + 2 * kBlkA), dbl = smem_desc(st + 2 * kBlkA + kTnOpB);
+        const unsigned tacc = tmem_base + (kb % kAcc) * 128;
+        unsigned acc = kb >= kAcc ? 1u : 0u;
+#pragma unroll
+        for (int kk = 0; kk < XKB / 8; ++kk) {
+          umma_tf32(tacc, dal + 2ull * kk, dbh + 2ull * kk, idesc, acc);
+          acc = 1;
+          umma_tf32(tacc, dah + 2ull * kk, dbl + 2ull * kk, idesc, 1u);
+          umma_tf32(tacc, dah + 2ull * kk, dbh + 2ull * kk, idesc, 1u);
+        }
+        umma_commit(opempty + o);
+      }
+      umma_commit(acc_ready);
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    const bool ok = bar_wait(acc_ready, 0, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int m = m0 + q * 32 + lane;
+#pragma unroll
+    for (int part = 0; part < 3; ++part) {     // columns 0-31, 32-63, 64-95 (only column 64 of the last part is used)
+      if (part == 2 && !with_sum) break;
+      unsigned v[32];
+      tmem_ld32x(tmem_base + ((unsigned)(q * 32) << 16) + part * 32, v);
+      for (int a = 1; a < kAcc && a < nkb; ++a) {
+        unsigned v2[32];
+        tmem_ld32x(tmem_base + ((unsigned)(q * 32) << 16) + a * 128 + part * 32, v2);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(v2[c]));
+      }
+      if (ok && nkb > 0 && m < p.M) {
+        if (part < 2) {
+          float* dst = p.C + (int64_t)m * p.ldc + n0 + part * 32;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            if (n0 + part * 32 + c < p.N)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst + c), "f"(__uint_as_float(v[c])),
+                           "f"(__uint_as_float(v[c + 1])), "f"(__uint_as_float(v[c + 2])), "f"(__uint_as_float(v[c + 3])) : "memory");
+        } else {
+          atomicAdd(p.colsum + m, __uint_as_float(v[0]));
+        }
+      }
+    }
+  } else if (warp < 10) {
+    const int tid = threadIdx.x - 6 * 32;
+    // constant rows of the B operand tiles: row 64 = ones (hi) / zeros (lo), rows 65..79 zeros
+    for (int o = 0; o < kTnOpStages; ++o) {
+      float* bh = reinterpret_cast<float*>(ops + o * kTnOp + 2 * kBlkA);
+      float* bl = reinterpret_cast<float*>(ops + o * kTnOp + 2 * kBlkA + kTnOpB);
+      for (int idx = tid; idx < (TN_NB - TN_N) * 32; idx += 128) {
+        bh[TN_N * 32 + idx] = idx < 32 ? 1.0f : 0.f;    // a row of identical values is unchanged by the swizzle
+        bl[TN_N * 32 + idx] = 0.f;
+      }
+    }
+    bool dead = false;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int r = kb % kTnRawStages, o = kb % kTnOpStages;
+      if (!dead) dead = !bar_wait(fullraw + r, (kb / kTnRawStages) & 1, p.status);
+      if (!dead) dead = !bar_wait(opempty + o, ((kb / kTnOpStages) & 1) ^ 1, p.status);
+      if (!dead) {
+        const float* rawA = reinterpret_cast<const float*>(raws + r * kTnRaw);
+        const float* rawB = reinterpret_cast<const float*>(raws + r * kTnRaw + kTnRawA);
+        unsigned char* st = ops + o * kTnOp;
+        {  // A: thread = column m of the raw block = row m of the operand tile
+          const int m = tid;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            uint4 h, l;
+            unsigned x[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = __float_as_uint(rawA[(4 * g + j) * XM + m]);
+            h.x = rna_tf32(x[0]); h.y = rna_tf32(x[1]); h.z = rna_tf32(x[2]); h.w = rna_tf32(x[3]);
+            l.x = rna_tf32(__float_as_uint(__uint_as_float(x[0]) - __uint_as_float(h.x)));
+            l.y = rna_tf32(__float_as_uint(__uint_as_float(x[1]) - __uint_as_float(h.y)));
+            l.z = rna_tf32(__float_as_uint(__uint_as_float(x[2]) - __uint_as_float(h.z)));
+            l.w = rna_tf32(__float_as_uint(__uint_as_float(x[3]) - __uint_as_float(h.w)));
+            const int off = m * 128 + ((g ^ (m & 7)) << 4);
+            *reinterpret_cast<uint4*>(st + off) = h;
+            *reinterpret_cast<uint4*>(st + kBlkA + off) = l;
+          }
+        }
+        {  // B: 64 columns, two halves of the k range
+          const int n = tid & 63, g0 = (tid >> 6) * 4;
+#pragma unroll
+          for (int gg = 0; gg < 4; ++gg) {
+            const int g = g0 + gg;
+            uint4 h, l;
+            unsigned x[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = __float_as_uint(rawB[(4 * g + j) * TN_N + n]);
+            h.x = rna_tf32(x[0]); h.y = rna_tf32(x[1]); h.z = rna_tf32(x[2]); h.w = rna_tf32(x[3]);
+            l.x = rna_tf32(__float_as_uint(__uint_as_float(x[0]) - __uint_as_float(h.x)));
+            l.y = rna_tf32(__float_as_uint(__uint_as_float(x[1]) - __uint_as_float(h.y)));
+            l.z = rna_tf32(__float_as_uint(__uint_as_float(x[2]) - __uint_as_float(h.z)));
+            l.w = rna_tf32(__float_as_uint(__uint_as_float(x[3]) - __uint_as_float(h.w)));
+            const int off = n * 128 + ((g ^ (n & 7)) << 4);
+            *reinterpret_cast<uint4*>(st + 2 * kBlkA + off) = h;
+            *reinterpret_cast<uint4*>(st + 2 * kBlkA + kTnOpB + off) = l;
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) { bar_arrive1(opready + o); bar_arrive1(rawempty + r); }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// float32 [rows][cols], no swizzle; box = box_cols x 32 rows
+int make_map_f32_plain(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cueq::fail("gemm f32x3: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, 32u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cueq::fail("gemm f32x3: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
 // float32 [rows][cols] with `ld` elements between rows; box = 32 columns (128 bytes) x box_rows
 int make_map_f32(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -461,6 +677,36 @@ extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream)
     }
     gemm_f32x3_stream_kernel<128><<<dim3(mtiles, (unsigned)((g->N + 127) / 128)), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
   }
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int cueq_b200_gemm_f32x3_tn(const cueq_gemm_f32x3_tn_args* g, void* stream) {
+  if (!g || !g->A || !g->B || !g->C) return cueq::fail("gemm f32x3 tn: null operand");
+  if (g->M <= 0 || g->N <= 0 || g->K <= 0) return 0;
+  if ((g->M % 4) || (g->N % 4)) return cueq::fail("gemm f32x3 tn: M and N must be multiples of 4");
+  if ((g->lda % 4) || (g->ldb % 4) || (g->ldc % 4)) return cueq::fail("gemm f32x3 tn: leading dimensions must keep rows 16-byte aligned");
+  if (((uintptr_t)g->A | (uintptr_t)g->B | (uintptr_t)g->C) & 15) return cueq::fail("gemm f32x3 tn: operands must be 16-byte aligned");
+  if (g->M > 2147483647LL - XM || g->N > 2147483647LL - TN_N || g->K > 2147483647LL - XKB) return cueq::fail("gemm f32x3 tn: dimension too large");
+  CUtensorMap ma, mb;
+  if (int rc = make_map_f32_plain(&ma, g->A, g->K, g->M, g->lda, XM)) return rc;
+  if (int rc = make_map_f32_plain(&mb, g->B, g->K, g->N, g->ldb, TN_N)) return rc;
+  TnParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.C = reinterpret_cast<float*>(g->C);
+  p.colsum = reinterpret_cast<float*>(g->colsum);
+  p.ldc = g->ldc; p.M = (int)g->M; p.N = (int)g->N; p.K = (int)g->K;
+  p.status = reinterpret_cast<int*>(g->status);
+  const size_t smem = kTnOpStages * kTnOp + kTnRawStages * kTnRaw + 256 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const int64_t total_kb = (g->K + XKB - 1) / XKB;
+  dim3 grid((unsigned)((g->M + XM - 1) / XM), (unsigned)((g->N + TN_N - 1) / TN_N), (unsigned)((total_kb + kTnBlocks - 1) / kTnBlocks));
+  if (grid.z > 65535) return cueq::fail("gemm f32x3 tn: K too large for one launch");
+  gemm_f32x3_tn_kernel<<<grid, kThreadsX, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

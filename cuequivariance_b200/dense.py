@@ -7,9 +7,9 @@ reference's convolution layer, cuequivariance_torch/layers/tp_conv_fully_connect
 at 1M edges x 2,944 weights that layer is 0.39 TFLOP, an order of magnitude more time than the
 tensor product itself when it runs on the CUDA cores.
 
-The forward and the input gradient run on this library's tcgen05 kernels (``csrc/gemm_f32x3.cu``:
-one that keeps the split A tile resident for K <= 64, one that streams both operands for larger K).
-The weight gradient (a reduction over the rows) uses a device-side torch matmul: INTERIM.
+Forward, input gradient, weight gradient and bias gradient all run on this library's tcgen05 kernels
+(``csrc/gemm_f32x3.cu``: one that keeps the split A tile resident for K <= 64, one that streams both
+operands for larger K, one that reduces over rows and transposes the blocks in shared memory).
 """
 from __future__ import annotations
 
@@ -72,6 +72,41 @@ def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = 
     return out
 
 
+def gemm_f32x3_tn(a: torch.Tensor, b: torch.Tensor, with_colsum: bool = False, name: str = "gemm_f32x3_tn",
+                  out: Optional[torch.Tensor] = None):
+    """``a[K, M].T @ b[K, N]`` (and, with ``with_colsum``, ``a.sum(0)``) in float32 accuracy on the tensor
+    cores: the reduction runs over the rows of both operands.  M and N multiples of 4; ``a`` and ``b`` may
+    be column slices of wider row-major tensors.  ``out`` (float32 [M, N], contiguous rows) is ADDED to."""
+    import ctypes as C
+
+    from . import _lib, profiling
+
+    if not (a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32):
+        raise RuntimeError("gemm_f32x3_tn needs float32 CUDA tensors (there is no CPU fallback)")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[0] != b.shape[0] or a.shape[1] % 4 or b.shape[1] % 4:
+        raise ValueError(f"gemm_f32x3_tn: a [K, M] and b [K, N] with M, N multiples of 4; got {tuple(a.shape)}, {tuple(b.shape)}")
+    ac = a if _rows_view_ok(a) else a.contiguous()
+    bc = b if _rows_view_ok(b) else b.contiguous()
+    if out is None:
+        out = torch.zeros((a.shape[1], b.shape[1]), dtype=torch.float32, device=a.device)
+    elif not (_rows_view_ok(out) and out.shape == (a.shape[1], b.shape[1]) and out.dtype == torch.float32):
+        raise ValueError("gemm_f32x3_tn: `out` must be a float32 [M, N] view with unit stride along rows and 16-byte alignment")
+    colsum = torch.zeros(a.shape[1], dtype=torch.float32, device=a.device) if with_colsum else None
+    if a.shape[0] > 0:
+        status = torch.zeros(1, dtype=torch.int32, device=a.device)
+        g = _lib.GemmF32x3TnArgs()
+        g.A, g.B, g.C = ac.data_ptr(), bc.data_ptr(), out.data_ptr()
+        if colsum is not None:
+            g.colsum = colsum.data_ptr()
+        g.M, g.N, g.K = a.shape[1], b.shape[1], a.shape[0]
+        g.lda, g.ldb, g.ldc = ac.stride(0), bc.stride(0), out.stride(0)
+        g.status = status.data_ptr()
+        with torch.cuda.device(a.device):
+            with profiling.kernel(name):
+                _lib.check(_lib.lib().cueq_b200_gemm_f32x3_tn(C.byref(g), C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)))
+    return (out, colsum) if with_colsum else out
+
+
 class _LinearF32x3(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -90,9 +125,15 @@ class _LinearF32x3(torch.autograd.Function):
                 gx = gemm_f32x3(gout, weight.detach().t().contiguous(), name="gemm_f32x3_gx")   # gout [M, N] x (W^T [K, N])^T
             else:
                 gx = _full_precision_matmul(gout, weight)
-        if ctx.needs_input_grad[1]:
-            gw = _full_precision_matmul(gout.t(), x)   # INTERIM: library GEMM (reduction over the long axis)
-        gb = gout.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        gb = None
+        want_gb = ctx.has_bias and ctx.needs_input_grad[2]
+        if ctx.needs_input_grad[1] and gout.shape[1] % 4 == 0 and x.shape[1] % 4 == 0:
+            res = gemm_f32x3_tn(gout, x.detach(), with_colsum=want_gb, name="gemm_f32x3_gw")
+            gw, gb = res if want_gb else (res, None)
+        elif ctx.needs_input_grad[1]:
+            gw = _full_precision_matmul(gout.t(), x)
+        if want_gb and gb is None:
+            gb = gout.sum(0)
         return gx, gw, gb
 
 

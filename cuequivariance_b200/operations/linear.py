@@ -45,7 +45,7 @@ class _DenseLinear(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, gout):
-        from ..dense import _full_precision_matmul, gemm_f32x3
+        from ..dense import gemm_f32x3, gemm_f32x3_tn
 
         plan = ctx.plan
         weight, x = ctx.saved_tensors
@@ -64,10 +64,11 @@ class _DenseLinear(torch.autograd.Function):
                         gemm_f32x3(gout[:, oo + i * v : oo + (i + 1) * v], wc, name="linear_f32x3_gx", out=dst)
                 seen.add(xo)
             if gw is not None:
-                # reduction over the rows: INTERIM library GEMM
-                xs = x[:, xo : xo + d * u].reshape(-1, u)
-                gs = gout[:, oo : oo + d * v].reshape(-1, v)
-                gw[0, wo : wo + u * v] += (_full_precision_matmul(xs.t(), gs) * c).reshape(-1)
+                acc = torch.zeros((u, v), dtype=torch.float32, device=x.device)
+                for i in range(d):   # reduction over the rows, component by component, into one accumulator
+                    gemm_f32x3_tn(x[:, xo + i * u : xo + (i + 1) * u], gout[:, oo + i * v : oo + (i + 1) * v], out=acc,
+                                  name="linear_f32x3_gw")
+                gw[0, wo : wo + u * v] += (acc * c).reshape(-1)
         return None, gw, gx
 
 
@@ -78,8 +79,8 @@ class Linear(torch.nn.Module):
     ``[batch]`` class ids, required when ``weight_classes > 1``.
 
     float32 with one weight set and multiplicities that are multiples of 32 runs as float32-accurate
-    tensor-core GEMMs (``dense.gemm_f32x3``; first derivatives only, the weight gradient uses a library
-    GEMM for now); everything else runs on the generic kernel over the polynomial ``uv,iu,iv``
+    tensor-core GEMMs (``dense.gemm_f32x3`` / ``gemm_f32x3_tn``; first derivatives only); everything else
+    runs on the generic kernel over the polynomial ``uv,iu,iv``
     flattened over ``u``.  There is no ``naive`` method and no fallback."""
 
     def __init__(

@@ -76,7 +76,8 @@ const char* cueq_b200_last_error(void);
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
    3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
    7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit,
-   10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit, 12 cueq_gemm_f32x3_args; -1 for any other number. */
+   10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit, 12 cueq_gemm_f32x3_args,
+   13 cueq_gemm_f32x3_tn_args; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -226,6 +227,20 @@ typedef struct {
   void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
 } cueq_gemm_f32x3_args;
 int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* args, void* stream);
+
+/* The same arithmetic for a reduction over rows: C[M,N] += sum_k A[k,M] * B[k,N], and optionally
+ * colsum[M] += sum_k A[k,M] - the weight and bias gradients of the layer above (A = cotangent,
+ * B = the layer's input).  C and colsum are float32 and are accumulated into with atomic adds (zero
+ * them first; the K range is spread over many CTAs).  M and N multiples of 4, rows 16-byte aligned. */
+typedef struct {
+  const void* A;        /* device float32 [K, lda]                                                 */
+  const void* B;        /* device float32 [K, ldb]                                                 */
+  void* C;              /* device float32 [M, ldc], accumulated into                               */
+  void* colsum;         /* nullable device float32 [M], accumulated into                           */
+  int64_t M, N, K, lda, ldb, ldc;
+  void* status;         /* nullable device int32: 2 if a bounded wait ran out                      */
+} cueq_gemm_f32x3_tn_args;
+int cueq_b200_gemm_f32x3_tn(const cueq_gemm_f32x3_tn_args* args, void* stream);
 
 /* ---- fully connected ("uvw") tensor product: kernels around the tensor-core GEMM -----------------
  *

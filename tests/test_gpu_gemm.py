@@ -109,3 +109,22 @@ def test_linear_f32x3_against_float64(M, N, K, bias):
     want = torch.autograd.grad(torch.nn.functional.linear(x, w, b), [x, w] + ([b] if bias else []), cot)
     for a, c in zip(got, want):
         assert float((a - c).abs().max()) <= 1e-4 * max(1.0, float(c.abs().max()))
+
+
+@pytest.mark.parametrize("K,M,N", [(32, 128, 64), (100, 128, 64), (5000, 2944, 64), (700, 132, 36), (9000, 260, 200)])
+def test_gemm_f32x3_tn_against_float64(K, M, N):
+    """Row-reduction product a[K, M].T @ b[K, N] with column sums (csrc/gemm_f32x3.cu, the weight / bias
+    gradient of a dense layer): float32 accuracy against a float64 product of the same inputs, ragged
+    K, M and N included."""
+    from cuequivariance_b200.dense import gemm_f32x3_tn
+
+    g = torch.Generator(device=DEV).manual_seed(K + M)
+    a = torch.randn(K, M, generator=g, device=DEV)
+    b = torch.randn(K, N, generator=g, device=DEV)
+    c, cs = gemm_f32x3_tn(a, b, with_colsum=True)
+    ref = a.double().t() @ b.double()
+    assert float((c.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    ref_cs = a.double().sum(0)
+    assert float((cs.double() - ref_cs).abs().max()) <= 1e-5 * max(1.0, float(ref_cs.abs().max()))
+    c2 = gemm_f32x3_tn(a[:, : M // 2 // 4 * 4], b)          # a column slice of a wider tensor, no column sums
+    assert float((c2.double() - ref[: M // 2 // 4 * 4]).abs().max()) <= 1e-5 * float(ref.abs().max())
