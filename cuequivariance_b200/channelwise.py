@@ -302,7 +302,7 @@ class _ChannelwiseBase:
 
     def _args(self, g, tabs, which, common, order, rowptr, nrecv, out_mul_ir, tensors, x1_is_block=False):
         """``x1_is_block``: tensors['x1'] (and 'gx1') hold only this group's irrep block,
-        ``[rows, extent * d1]`` contiguous, instead of full rows.  The constant part of the
+        ``[rows, extent * d1]`` (unit stride along the row, any row stride), instead of full rows.  The constant part of the
         argument block is built once per (group, direction) and copied."""
         import ctypes as C
 
@@ -340,8 +340,13 @@ class _ChannelwiseBase:
         a.tab_start, a.tab_j, a.tab_c = ts.data_ptr(), tj.data_ptr(), tc.data_ptr()
         a.num_receivers = nrecv
         if x1_is_block:
-            a.x1_stride = tensors["x1"].shape[1]
+            # may be a column slice of a wider tensor (several irrep blocks gathered together); a
+            # gradient block, if any, must then be the matching slice of an equally wide tensor
+            a.x1_stride = tensors["x1"].stride(0)
             a.x1_offset = 0
+            gx1 = tensors.get("gx1")
+            if gx1 is not None and gx1.stride(0) != a.x1_stride:
+                raise ValueError("channelwise: the x1 block and its gradient block must have the same row stride")
         a.x1_mul_ir = 1 if common["x1_mul_ir"] else 0
         a.out_mul_ir = 1 if out_mul_ir else 0
         a.channels_per_lane = CHANNELS_PER_LANE

@@ -94,21 +94,44 @@ def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
     return _AllGatherRows.apply(x, group)
 
 
+BUNDLES = 2   # exchanges per direction in the pipelined path (1: one collective, >= number of irreps: one per irrep)
+
+
 class _PipelinedShardedChannelwise(torch.autograd.Function):
     """Sharded channelwise product with the node-feature exchange pipelined against the
     per-irrep kernel launches.
 
-    Forward : the node features are all-gathered one irrep block at a time (asynchronous NCCL
-              calls, smallest block first); the launch for irrep l only waits for block l, so
-              every transfer but the first hides behind the previous launch.
-    Backward: launches run largest irrep first; as soon as a launch has produced its block of
-              the node-feature gradient, that block's reduce-scatter starts and overlaps the
-              next launch; the last (smallest) block is the only exposed transfer.
+    Forward : the node features are all-gathered in bundles of consecutive irrep blocks
+              (asynchronous NCCL calls, smallest first); the launches of a bundle only wait for
+              that bundle, so every transfer but the first hides behind earlier launches.
+    Backward: launches run largest irrep first; as soon as the launches of a bundle have produced
+              their part of the node-feature gradient, its reduce-scatter starts and overlaps
+              the next launches; the last (smallest) bundle is the only exposed transfer.
     First-order only (differentiating the result again is not supported on this path)."""
 
     @staticmethod
+    def _bundles(plan):
+        """Consecutive irrep blocks exchanged together: ``[(first group, last group + 1, column
+        offset, width)]``.  One collective per irrep hides the most transfer in theory, but at 8
+        ranks every collective costs 0.13-0.2 ms of latency whatever its size and the forward
+        pass became bound by its four all-gathers (0.54 ms for 0.68 ms of kernels); two bundles -
+        the small leading blocks, then the rest - keep the first wait short and the overlap."""
+        groups = plan.groups
+        n = len(groups)
+        cuts = [0, n] if n < 2 or BUNDLES <= 1 else [0, max(1, n // 2), n]
+        if BUNDLES >= n:
+            cuts = list(range(n + 1))
+        out = []
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            off = groups[a]["x1_off"]
+            end = groups[b - 1]["x1_off"] + groups[b - 1]["x1_width"]
+            if any(groups[i]["x1_off"] + groups[i]["x1_width"] != groups[i + 1]["x1_off"] for i in range(a, b - 1)):
+                return [(i, i + 1, groups[i]["x1_off"], groups[i]["x1_width"]) for i in range(n)]   # blocks not adjacent: one each
+            out.append((a, b, off, end - off))
+        return out
+
+    @staticmethod
     def forward(ctx, handler, group, x1_local, x2, weight, senders, receivers_local):
-        from . import _lib
         from .channelwise import _CSR
 
         plan = handler.plan
@@ -119,47 +142,56 @@ class _PipelinedShardedChannelwise(torch.autograd.Function):
         common = dict(x1_mul_ir=mul_ir, senders=_CSR.int32(senders))
         order, rowptr = _CSR.get(receivers_local, n_local)
         csr = (order, rowptr, n_local)
-        blocks, works = [], []
-        for g in plan.groups:  # irrep blocks in ascending size
-            loc = x1_local[:, g["x1_off"] : g["x1_off"] + g["x1_width"]].contiguous()
-            full = torch.empty((n_local * world, g["x1_width"]), dtype=loc.dtype, device=dev)
+        bundles = _PipelinedShardedChannelwise._bundles(plan)
+        wide, works = [], []
+        for (a, b, off, width) in bundles:  # irrep blocks in ascending size
+            loc = x1_local[:, off : off + width].contiguous()
+            full = torch.empty((n_local * world, width), dtype=loc.dtype, device=dev)
             works.append(dist.all_gather_into_tensor(full, loc, group=group, async_op=True))
-            blocks.append(full)
+            wide.append(full)
         out = torch.empty((n_local, plan.row_sizes[3]), dtype=torch.float32, device=dev)
-        for gi in range(len(plan.groups)):
-            works[gi].wait()
-            handler.launch_forward_group(gi, common, csr, mul_ir, weight, blocks[gi], x2, out)
-        ctx.handler, ctx.group, ctx.common, ctx.csr = handler, group, common, csr
-        ctx.save_for_backward(weight, x2, *blocks)
+        for bi, (a, b, off, width) in enumerate(bundles):
+            works[bi].wait()
+            for gi in range(a, b):
+                g = plan.groups[gi]
+                block = wide[bi][:, g["x1_off"] - off : g["x1_off"] - off + g["x1_width"]]
+                handler.launch_forward_group(gi, common, csr, mul_ir, weight, block, x2, out)
+        ctx.handler, ctx.group, ctx.common, ctx.csr, ctx.bundles = handler, group, common, csr, bundles
+        ctx.save_for_backward(weight, x2, *wide)
         ctx.n_local = n_local
-        del _lib
         return out
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, gout):
-        handler, group, common, csr = ctx.handler, ctx.group, ctx.common, ctx.csr
+        handler, group, common, csr, bundles = ctx.handler, ctx.group, ctx.common, ctx.csr, ctx.bundles
         plan = handler.plan
-        weight, x2, *blocks = ctx.saved_tensors
+        weight, x2, *wide = ctx.saved_tensors
         gout = gout.contiguous()
         need_x1, need_x2, need_w = ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4]
         gw = torch.empty_like(weight) if need_w else None
         gx2 = torch.zeros_like(x2) if need_x2 else None
         pieces, works = {}, []
-        for gi in reversed(range(len(plan.groups))):  # largest block first
-            gblock = torch.zeros_like(blocks[gi]) if need_x1 else None
-            handler.launch_backward_group(gi, common, csr, True, weight, blocks[gi], x2, gout, gw, gblock, gx2)
+        for bi in reversed(range(len(bundles))):  # largest blocks first
+            a, b, off, width = bundles[bi]
+            gwide = torch.zeros_like(wide[bi]) if need_x1 else None
+            for gi in reversed(range(a, b)):
+                g = plan.groups[gi]
+                lo = g["x1_off"] - off
+                block = wide[bi][:, lo : lo + g["x1_width"]]
+                gblock = gwide[:, lo : lo + g["x1_width"]] if need_x1 else None
+                handler.launch_backward_group(gi, common, csr, True, weight, block, x2, gout, gw, gblock, gx2)
             if need_x1:
-                mine = torch.empty((ctx.n_local, gblock.shape[1]), dtype=gblock.dtype, device=gblock.device)
-                works.append(dist.reduce_scatter_tensor(mine, gblock, op=dist.ReduceOp.SUM, group=group, async_op=True))
-                pieces[gi] = mine
+                mine = torch.empty((ctx.n_local, width), dtype=gwide.dtype, device=gwide.device)
+                works.append(dist.reduce_scatter_tensor(mine, gwide, op=dist.ReduceOp.SUM, group=group, async_op=True))
+                pieces[bi] = mine
         gx1 = None
         if need_x1:
             for wk in works:
                 wk.wait()
             gx1 = torch.empty((ctx.n_local, plan.row_sizes[1]), dtype=torch.float32, device=gout.device)
-            for gi, g in enumerate(plan.groups):
-                gx1[:, g["x1_off"] : g["x1_off"] + g["x1_width"]] = pieces[gi]
+            for bi, (a, b, off, width) in enumerate(bundles):
+                gx1[:, off : off + width] = pieces[bi]
         return None, None, gx1, gx2, gw, None, None
 
 
