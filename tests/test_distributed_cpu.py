@@ -73,3 +73,27 @@ def test_shard_helpers_reject_bad_input():
         shard_edges(torch.tensor([3, 1, 2]), 4, 2, 0)
     assert shard_bounds(8, 4, 3) == (6, 8)
     assert shard_edges(torch.tensor([0, 0, 1, 3, 3, 3]), 4, 2, 1) == (3, 6)
+
+
+def test_exchange_bundles_cover_every_block_once():
+    """Host logic of the pipelined path: irrep blocks are grouped into bundles of adjacent column ranges."""
+    from types import SimpleNamespace
+
+    from cuequivariance_b200 import distributed
+    from cuequivariance_b200.distributed import _PipelinedShardedChannelwise as P
+
+    groups = [dict(x1_off=0, x1_width=128), dict(x1_off=128, x1_width=384), dict(x1_off=512, x1_width=640), dict(x1_off=1152, x1_width=896)]
+    plan = SimpleNamespace(groups=groups)
+    old = distributed.BUNDLES
+    try:
+        distributed.BUNDLES = 2
+        assert P._bundles(plan) == [(0, 2, 0, 512), (2, 4, 512, 1536)]
+        distributed.BUNDLES = 1
+        assert P._bundles(plan) == [(0, 4, 0, 2048)]
+        distributed.BUNDLES = 4
+        assert P._bundles(plan) == [(0, 1, 0, 128), (1, 2, 128, 384), (2, 3, 512, 640), (3, 4, 1152, 896)]
+        distributed.BUNDLES = 2
+        gap = [dict(x1_off=0, x1_width=128), dict(x1_off=256, x1_width=128)]     # not adjacent: one exchange each
+        assert P._bundles(SimpleNamespace(groups=gap)) == [(0, 1, 0, 128), (1, 2, 256, 128)]
+    finally:
+        distributed.BUNDLES = old
