@@ -187,7 +187,7 @@ def main():
     ap.add_argument("--edges", type=int, default=E_TOTAL, help="total edges (default: the named configuration)")
     ap.add_argument("--nodes", type=int, default=N_TOTAL)
     ap.add_argument("--cpl", type=int, default=0, help="force channels per lane (2 or 4) in the channelwise kernels; 0 = library default")
-    ap.add_argument("--bundles", type=int, default=None, help="N>1: exchanges per direction (1, 2 or one per irrep = 4)")
+    ap.add_argument("--bundles", type=int, default=None, help="N>1: exchanges per direction (0 = one per irrep, 1, 2)")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="N>1: upper bound on the thread blocks of a collective (0: NCCL's choice)")
     ap.add_argument("--sender-passes", type=int, default=None, help="backward: sender-range passes (1 = off)")
     ap.add_argument("--staging", type=int, default=None, help="forward staging: 0 = cp.async per lane, 1 = bulk copies")

@@ -94,7 +94,7 @@ def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
     return _AllGatherRows.apply(x, group)
 
 
-BUNDLES = 2   # exchanges per direction in the pipelined path (1: one collective, >= number of irreps: one per irrep)
+BUNDLES = 0   # exchanges per direction in the pipelined path (0: one per irrep, 1: one collective, 2: two bundles)
 
 
 class _PipelinedShardedChannelwise(torch.autograd.Function):
@@ -112,15 +112,18 @@ class _PipelinedShardedChannelwise(torch.autograd.Function):
     @staticmethod
     def _bundles(plan):
         """Consecutive irrep blocks exchanged together: ``[(first group, last group + 1, column
-        offset, width)]``.  One collective per irrep hides the most transfer in theory, but at 8
-        ranks every collective costs 0.13-0.2 ms of latency whatever its size and the forward
-        pass became bound by its four all-gathers (0.54 ms for 0.68 ms of kernels); two bundles -
-        the small leading blocks, then the rest - keep the first wait short and the overlap."""
+        offset, width)]``.  Default: one exchange per irrep block.  Measured on 8 B200s (config 3,
+        ms per step): one per irrep 2.77, two bundles (the two small leading blocks, then the
+        rest) 2.87 - although every collective costs 0.13-0.2 ms of latency at 8 ranks, the finer
+        pipeline still wins."""
         groups = plan.groups
         n = len(groups)
-        cuts = [0, n] if n < 2 or BUNDLES <= 1 else [0, max(1, n // 2), n]
-        if BUNDLES >= n:
+        if BUNDLES == 0 or BUNDLES >= n:
             cuts = list(range(n + 1))
+        elif BUNDLES == 1 or n < 2:
+            cuts = [0, n]
+        else:
+            cuts = [0, max(1, n // 2), n]
         out = []
         for a, b in zip(cuts[:-1], cuts[1:]):
             off = groups[a]["x1_off"]

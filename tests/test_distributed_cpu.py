@@ -90,8 +90,9 @@ def test_exchange_bundles_cover_every_block_once():
         assert P._bundles(plan) == [(0, 2, 0, 512), (2, 4, 512, 1536)]
         distributed.BUNDLES = 1
         assert P._bundles(plan) == [(0, 4, 0, 2048)]
-        distributed.BUNDLES = 4
-        assert P._bundles(plan) == [(0, 1, 0, 128), (1, 2, 128, 384), (2, 3, 512, 640), (3, 4, 1152, 896)]
+        for per_irrep in (0, 4):
+            distributed.BUNDLES = per_irrep
+            assert P._bundles(plan) == [(0, 1, 0, 128), (1, 2, 128, 384), (2, 3, 512, 640), (3, 4, 1152, 896)]
         distributed.BUNDLES = 2
         gap = [dict(x1_off=0, x1_width=128), dict(x1_off=256, x1_width=128)]     # not adjacent: one exchange each
         assert P._bundles(SimpleNamespace(groups=gap)) == [(0, 1, 0, 128), (1, 2, 256, 128)]
