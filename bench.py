@@ -151,7 +151,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": "edges/s channelwise TP fwd+bwd (1M edges,128ch,lmax3)", "value": rate, "unit": "edges/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak" if False else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config 3 shape, CPU slice: " + sample, "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": rate, "unit": "edges/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -10,11 +10,11 @@
 // 32,768 samples.  Here it never leaves the SM: producer warps compute one [128 samples x 64 (u
 // fixed, all v)] slice at a time directly into 128-byte-swizzled shared memory in the layout
 // tcgen05.mma expects for a K-major A operand, the matching [64 x 64] slice of W arrives by TMA,
-// one thread issues the MMAs into a TMEM accumulator, and four epilogue warps write the finished
-// [128 x 64] block of the output.  One CTA owns (output irrep, component k, 128 samples) and runs
+// two threads issue the MMAs of alternate slices into two TMEM accumulators, and four epilogue warps
+// add them and write the finished [128 x 64] block of the output.  One CTA owns (output irrep, component k, 128 samples) and runs
 // over all paths that end in that irrep, so every output element is written exactly once.
 //
-// Warp roles: 0 = TMA (W slices), 1 = MMA issue + TMEM owner, 2-5 = epilogue, 6-13 = producers.
+// Warp roles: 0 = TMA (W slices), 1 and 14 = MMA issue (1 owns TMEM), 2-5 = epilogue, 6-13 = producers.
 // Every wait is bounded; a wait that runs out records status 2, the thread stops waiting and
 // working but keeps arriving on barriers, so the CTA always reaches its end and frees its TMEM.
 #include <cuda.h>
@@ -586,7 +586,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) fctp_fused_gx_kernel(const __gri
 // accumulators in TMEM (all 512 columns), so that x2 values, the cotangent block and the T
 // products of a (component, 64-sample block) are shared by eight MMA groups.  The partial sums
 // of the sample ranges are combined with red.global.add.
-// Warp roles: 0 = TMA, 1 = MMA issue + TMEM owner, 2-5 = epilogue, 6-13 = producers.
+// Warp roles: 0 = TMA, 1 and 14 = MMA issue (1 owns TMEM), 2-5 = epilogue, 6-13 = producers.
 constexpr int WK = 64;                         // samples per item (MMA K, 4 instructions)
 constexpr int kStagesWA = 6;                   // A ring (16 KiB: 2 blocks of [64 samples][64 (u,v)])
 constexpr int kStagesWB = 4;                   // cotangent blocks (8 KiB)
