@@ -12,10 +12,10 @@
 // One CTA owns 128 rows of A: the tile arrives by TMA and is split in place by four warps (the
 // operation is element-wise, so it does not care about the 128-byte swizzle); B arrives already
 // split (two float32 arrays prepared once by the caller) in 128-row tiles; two threads issue the
-// MMAs for alternate column tiles, each with its own B stage and its own pair of TMEM
-// accumulators, and four epilogue warps add the bias and send the rows out through shared memory
+// MMAs for alternate column tiles out of a ring of B blocks, each with its own pair of TMEM
+// accumulators, and eight epilogue warps add the bias and send the rows out through shared memory
 // and TMA stores (whole 128-byte lines).
-// Warp roles: 0 = TMA, 1 and 10 = MMA issue (1 owns TMEM), 2-5 = epilogue, 6-9 = split.
+// Warp roles: 0 = TMA, 1 and 10 = MMA issue (1 owns TMEM), 2-5 and 11-14 = epilogue, 6-9 = split.
 // Every wait is bounded (status word 2 on timeout; the CTA still reaches its end and frees TMEM).
 #include <cuda.h>
 
@@ -33,6 +33,7 @@ constexpr int kBlkA = XM * XKB * 4;                     // 16 KiB per K block of
 constexpr int kBlkB = XN * XKB * 4;                     // 16 KiB per K block of a B tile
 constexpr int kMaxKB = 2;                               // K <= 64
 constexpr int kThreadsX = 11 * 32;
+constexpr int kThreadsRes = 15 * 32;                    // the resident-A kernel has four more epilogue warps
 
 struct XParams {
   float* C;
@@ -68,7 +69,7 @@ __device__ __forceinline__ void bar_arrive1(unsigned long long* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(b)) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(kThreadsRes, 1) gemm_f32x3_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_bhi,
                                                                   const __grid_constant__ CUtensorMap map_blo,
                                                                   const __grid_constant__ CUtensorMap map_c,
@@ -77,14 +78,18 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_hi = smem;                                  // [nkb][128 rows][128 B]
   unsigned char* a_lo = a_hi + kMaxKB * kBlkA;
-  unsigned char* b_st = a_lo + kMaxKB * kBlkA;                 // 2 stages x (hi [nkb] + lo [nkb])
-  constexpr int kStageB = 2 * kMaxKB * kBlkB;
-  unsigned char* stage_c = b_st + 2 * kStageB;                 // per epilogue warp: 2 x [32 rows][128 B], swizzled
-  unsigned long long* fullA = reinterpret_cast<unsigned long long*>(stage_c + 4 * 2 * 4096);
+  unsigned char* b_st = a_lo + kMaxKB * kBlkA;                 // kBStages x (hi + lo) of one K block of one column tile
+  constexpr int kStageB = 2 * kBlkB;
+  // four stages: with items dealt tile by tile to two issuers, stage s is then always consumed by the same
+  // issuer, so every waiter sees consecutive phases of its barriers (with two stages an issuer would skip a
+  // phase and the parity test would alias)
+  constexpr int kBStages = 4;
+  unsigned char* stage_c = b_st + kBStages * kStageB;          // per epilogue warp: [32 rows][128 B], swizzled
+  unsigned long long* fullA = reinterpret_cast<unsigned long long*>(stage_c + 8 * 4096);
   unsigned long long* readyA = fullA + 1;
-  unsigned long long* fullB = readyA + 1;      // [2]
-  unsigned long long* emptyB = fullB + 2;      // [2]
-  unsigned long long* accfull = emptyB + 2;    // [4]
+  unsigned long long* fullB = readyA + 1;      // [4]
+  unsigned long long* emptyB = fullB + 4;      // [4]
+  unsigned long long* accfull = emptyB + 4;    // [4]
   unsigned long long* accempty = accfull + 4;  // [4]
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(accempty + 4);
 
@@ -96,8 +101,8 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
   if (threadIdx.x == 0) {
     bar_init(fullA, 1);
     bar_init(readyA, 4);
-    for (int s = 0; s < 2; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
-    for (int b = 0; b < 4; ++b) { bar_init(accfull + b, 1); bar_init(accempty + b, 4); }
+    for (int s = 0; s < kBStages; ++s) { bar_init(fullB + s, 1); bar_init(emptyB + s, 1); }
+    for (int b = 0; b < 4; ++b) { bar_init(accfull + b, 1); bar_init(accempty + b, 8); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -113,15 +118,16 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
     if (lane == 0) {
       bar_expect_tx(fullA, nkb * kBlkA);
       for (int kb = 0; kb < nkb; ++kb) tma_load_2d(a_hi + kb * kBlkA, &map_a, kb * XKB, m0, fullA);
-      for (int t = 0; t < ntiles; ++t) {
-        const int s = t & 1;
-        if (!bar_wait(emptyB + s, ((t >> 1) & 1) ^ 1, p.status)) break;
-        bar_expect_tx(fullB + s, 2 * nkb * kBlkB);
+      // items = (column tile, K block) in order; the ring runs up to four items ahead of the MMAs,
+      // which hides the L2 latency of the loads
+      for (int item = 0; item < ntiles * nkb; ++item) {
+        const int s = item % kBStages;
+        const int t = item / nkb, kb = item % nkb;
+        if (!bar_wait(emptyB + s, ((item / kBStages) & 1) ^ 1, p.status)) break;
+        bar_expect_tx(fullB + s, kStageB);
         unsigned char* st = b_st + s * kStageB;
-        for (int kb = 0; kb < nkb; ++kb) {
-          tma_load_2d(st + kb * kBlkB, &map_bhi, kb * XKB, t * XN, fullB + s);
-          tma_load_2d(st + (kMaxKB + kb) * kBlkB, &map_blo, kb * XKB, t * XN, fullB + s);
-        }
+        tma_load_2d(st, &map_bhi, kb * XKB, t * XN, fullB + s);
+        tma_load_2d(st + kBlkB, &map_blo, kb * XKB, t * XN, fullB + s);
       }
     }
   } else if (warp == 1 || warp == 10) {
@@ -133,15 +139,16 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
       for (int t = me; t < ntiles && ok; t += 2) {
         const int n = t >> 1;                 // this issuer's n-th tile
         const int buf = me * 2 + (n & 1);
-        ok = bar_wait(fullB + me, n & 1, p.status);
-        if (ok) ok = bar_wait(accempty + buf, ((n >> 1) & 1) ^ 1, p.status);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned char* st = b_st + me * kStageB;
+        ok = bar_wait(accempty + buf, ((n >> 1) & 1) ^ 1, p.status);
         unsigned acc = 0;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const int item = t * nkb + kb, s = item % kBStages;
+          ok = bar_wait(fullB + s, (item / kBStages) & 1, p.status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned char* st = b_st + s * kStageB;
           const unsigned long long dah = smem_desc(a_hi + kb * kBlkA), dal = smem_desc(a_lo + kb * kBlkA);
-          const unsigned long long dbh = smem_desc(st + kb * kBlkB), dbl = smem_desc(st + (kMaxKB + kb) * kBlkB);
+          const unsigned long long dbh = smem_desc(st), dbl = smem_desc(st + kBlkB);
 #pragma unroll
           for (int kk = 0; kk < XKB / 8; ++kk) {   // one instruction covers 8 float32 of K = 32 bytes = 2 descriptor units
             umma_tf32(tmem_base + buf * XN, dal + 2ull * kk, dbh + 2ull * kk, idesc, acc);
@@ -149,13 +156,15 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
             umma_tf32(tmem_base + buf * XN, dah + 2ull * kk, dbl + 2ull * kk, idesc, 1u);
             umma_tf32(tmem_base + buf * XN, dah + 2ull * kk, dbh + 2ull * kk, idesc, 1u);
           }
+          umma_commit(emptyB + s);
         }
-        umma_commit(emptyB + me);
+        if (!ok) break;
         umma_commit(accfull + buf);
       }
     }
-  } else if (warp < 6) {
-    const int q = warp & 3;
+  } else if (warp < 6 || warp > 10) {
+    // eight epilogue warps: lane quadrant = warp % 4; warps 2-5 take columns 0-63 of a tile, warps 11-14 columns 64-127
+    const int q = warp & 3, ph = warp > 10 ? 1 : 0, ew = ph * 4 + q;
     bool dead = false;
     for (int t = 0; t < ntiles; ++t) {
       const int me = t & 1, n = t >> 1;
@@ -163,7 +172,8 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
       if (!dead) dead = !bar_wait(accfull + buf, (n >> 1) & 1, p.status);
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-      for (int part = 0; part < XN / 32; ++part) {
+      for (int pp = 0; pp < 2; ++pp) {
+        const int part = ph * 2 + pp;
         unsigned v[32];
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -177,8 +187,8 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_kernel(const __grid_c
         const int col0 = t * XN + part * 32;
         // rows leave through shared memory and a TMA store, so that global writes are whole 128-byte
         // lines (a lane-per-row store would touch 32 rows per instruction)
-        unsigned char* mine = stage_c + (q * 2 + (part & 1)) * 4096;
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");   // the store that used this buffer two parts ago has read it
+        unsigned char* mine = stage_c + ew * 4096;
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // the previous store has read the buffer
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
@@ -651,13 +661,13 @@ extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream)
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const unsigned mtiles = (unsigned)((g->M + XM - 1) / XM);
   if (resident) {
-    const size_t smem = 2 * kMaxKB * kBlkA + 2 * 2 * kMaxKB * kBlkB + 4 * 2 * 4096 + 256 + 1024;
+    const size_t smem = 2 * kMaxKB * kBlkA + 4 * 2 * kBlkB + 8 * 4096 + 256 + 1024;
     static bool configured = false;
     if (!configured) {
       CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = true;
     }
-    gemm_f32x3_kernel<<<dim3(mtiles), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
+    gemm_f32x3_kernel<<<dim3(mtiles), kThreadsRes, smem, st>>>(ma, mh, ml, mc, p);
   } else if (nt == 64) {
     using Cfg = StreamCfg<64>;
     const size_t smem = Cfg::kStages * Cfg::kStage + 4 * 2 * 4096 + 256 + 1024;
