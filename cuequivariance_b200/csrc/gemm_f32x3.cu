@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_stream_kernel(const _
 // The weight gradient of a dense layer (gout[E,2944]^T x h[E,64]) and its bias gradient.  Both
 // operands are stored with the reduction index as the row, i.e. transposed with respect to what
 // the K-major MMA wants: raw [32 x 128] / [32 x 64] blocks arrive by TMA without swizzle, and the
-// four split warps transpose them while they split them, writing K-major 128-byte-swizzled hi / lo
+// eight split warps transpose them while they split them, writing K-major 128-byte-swizzled hi / lo
 // tiles (a thread reads four consecutive k of one column and stores one 16-byte chunk, so reads
 // and writes are both free of bank conflicts).  A constant extra row of B holding ones gives the
 // column sums of A from the same MMAs.  The K range is cut into slices of kTnBlocks blocks per CTA
@@ -432,7 +432,7 @@ struct TnParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(kThreadsRes, 1) gemm_f32x3_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const TnParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -455,8 +455,8 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __gri
   constexpr int kAcc = 4;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kTnRawStages; ++s) { bar_init(fullraw + s, 1); bar_init(rawempty + s, 4); }
-    for (int s = 0; s < kTnOpStages; ++s) { bar_init(opready + s, 4); bar_init(opempty + s, 1); }
+    for (int s = 0; s < kTnRawStages; ++s) { bar_init(fullraw + s, 1); bar_init(rawempty + s, 8); }
+    for (int s = 0; s < kTnOpStages; ++s) { bar_init(opready + s, 8); bar_init(opempty + s, 1); }
     bar_init(acc_ready, 2);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -533,13 +533,14 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __gri
         }
       }
     }
-  } else if (warp < 10) {
-    const int tid = threadIdx.x - 6 * 32;
+  } else {
+    // eight split warps: 6-9 and 11-14
+    const int tid = warp < 10 ? threadIdx.x - 6 * 32 : threadIdx.x - 11 * 32 + 128;
     // constant rows of the B operand tiles: row 64 = ones (hi) / zeros (lo), rows 65..79 zeros
     for (int o = 0; o < kTnOpStages; ++o) {
       float* bh = reinterpret_cast<float*>(ops + o * kTnOp + 2 * kBlkA);
       float* bl = reinterpret_cast<float*>(ops + o * kTnOp + 2 * kBlkA + kTnOpB);
-      for (int idx = tid; idx < (TN_NB - TN_N) * 32; idx += 128) {
+      for (int idx = tid; idx < (TN_NB - TN_N) * 32; idx += 256) {
         bh[TN_N * 32 + idx] = idx < 32 ? 1.0f : 0.f;    // a row of identical values is unchanged by the swizzle
         bl[TN_N * 32 + idx] = 0.f;
       }
@@ -553,10 +554,11 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __gri
         const float* rawA = reinterpret_cast<const float*>(raws + r * kTnRaw);
         const float* rawB = reinterpret_cast<const float*>(raws + r * kTnRaw + kTnRawA);
         unsigned char* st = ops + o * kTnOp;
-        {  // A: thread = column m of the raw block = row m of the operand tile
-          const int m = tid;
+        {  // A: thread = (column m of the raw block = row m of the operand tile, half of the k range)
+          const int m = tid & 127, ga = (tid >> 7) * 4;
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
+          for (int gg = 0; gg < 4; ++gg) {
+            const int g = ga + gg;
             uint4 h, l;
             unsigned x[4];
 #pragma unroll
@@ -571,10 +573,10 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_tn_kernel(const __gri
             *reinterpret_cast<uint4*>(st + kBlkA + off) = l;
           }
         }
-        {  // B: 64 columns, two halves of the k range
-          const int n = tid & 63, g0 = (tid >> 6) * 4;
+        {  // B: 64 columns, four quarters of the k range
+          const int n = tid & 63, g0 = (tid >> 6) * 2;
 #pragma unroll
-          for (int gg = 0; gg < 4; ++gg) {
+          for (int gg = 0; gg < 2; ++gg) {
             const int g = g0 + gg;
             uint4 h, l;
             unsigned x[4];
@@ -716,7 +718,7 @@ extern "C" int cueq_b200_gemm_f32x3_tn(const cueq_gemm_f32x3_tn_args* g, void* s
   const int64_t total_kb = (g->K + XKB - 1) / XKB;
   dim3 grid((unsigned)((g->M + XM - 1) / XM), (unsigned)((g->N + TN_N - 1) / TN_N), (unsigned)((total_kb + kTnBlocks - 1) / kTnBlocks));
   if (grid.z > 65535) return cueq::fail("gemm f32x3 tn: K too large for one launch");
-  gemm_f32x3_tn_kernel<<<grid, kThreadsX, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  gemm_f32x3_tn_kernel<<<grid, kThreadsRes, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ma, mb, p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
