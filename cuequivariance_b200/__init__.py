@@ -18,4 +18,6 @@ from .operations import (
     Linear,
 )
 
+from ._lib import check_status  # noqa: E402  (raises if a kernel reported a bounded wait that ran out)
+
 __version__ = "0.1.0"

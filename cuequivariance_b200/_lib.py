@@ -232,6 +232,38 @@ def check(status: int) -> None:
         raise CueqError(lib().cueq_b200_last_error().decode())
 
 
+_status_words: dict = {}
+
+
+def status_word(device):
+    """One int32 on ``device`` shared by every launch that takes a ``status`` pointer: kernels with
+    bounded waits write a non-zero code there instead of hanging (1: a bulk copy of the channelwise
+    staging variant ran out of time, 2: a wait inside a tensor-core kernel did).  Launches never read
+    it back (that would synchronise); call :func:`check_status` at a point where a sync is acceptable."""
+    import torch
+
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    t = _status_words.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status_words[dev] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises :class:`CueqError` if any kernel since the last check reported a wait that
+    ran out (its results are then incomplete).  The word is cleared."""
+    for dev, t in list(_status_words.items()):
+        if device is not None and dev != __import__("torch").device(device):
+            continue
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise CueqError(f"a kernel on {dev} gave up on a bounded wait (status {code}); its outputs are incomplete")
+
+
 def int32_array(values):
     values = list(values)
     return (C.c_int32 * max(len(values), 1))(*values)

@@ -353,6 +353,8 @@ class _ChannelwiseBase:
         # (config 3: forward 0.58 -> 0.46 ms, backward 1.15 -> 1.00 ms; every other group is slower with four)
         a.channels_per_lane = CHANNELS_PER_LANE or (4 if g.get("l1") == 0 and plan.extent % 128 == 0 else 0)
         a.staging = STAGING if which == "fwd_tab" else 0
+        if a.staging:
+            a.status = _lib.status_word(tensors["w"].device).data_ptr()
         return a, tmpl[1]
 
     # -- kernel launches shared by the first- and second-order handlers ------------------------

@@ -56,7 +56,7 @@ def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = 
         raise ValueError("gemm_f32x3: `out` must be a float32 [M, N] view with unit stride along rows and 16-byte alignment")
     if a.shape[0] == 0:
         return out
-    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    status = _lib.status_word(a.device)
     g = _lib.GemmF32x3Args()
     g.A, g.B_hi, g.B_lo, g.C = ac.data_ptr(), hi.data_ptr(), lo.data_ptr(), out.data_ptr()
     bc = None
@@ -93,7 +93,7 @@ def gemm_f32x3_tn(a: torch.Tensor, b: torch.Tensor, with_colsum: bool = False, n
         raise ValueError("gemm_f32x3_tn: `out` must be a float32 [M, N] view with unit stride along rows and 16-byte alignment")
     colsum = torch.zeros(a.shape[1], dtype=torch.float32, device=a.device) if with_colsum else None
     if a.shape[0] > 0:
-        status = torch.zeros(1, dtype=torch.int32, device=a.device)
+        status = _lib.status_word(a.device)
         g = _lib.GemmF32x3TnArgs()
         g.A, g.B, g.C = ac.data_ptr(), bc.data_ptr(), out.data_ptr()
         if colsum is not None:

@@ -140,7 +140,9 @@ class _TensorCoreUVW(torch.autograd.Function):
         d, off = owner.d, owner.offsets
         B = x1.shape[0]
         dev = x1.device
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        from . import _lib
+
+        status = _lib.status_word(dev)
         if FUSED and owner._fused_tasks() is not None:
             out = owner._fused_forward(w, x1, x2, status)
             ctx.owner, ctx.status = owner, status

@@ -33,3 +33,16 @@ def golden():
         return np.load(os.path.join(GOLDEN, name), allow_pickle=False)
 
     return load
+
+
+@pytest.fixture(autouse=True)
+def _kernel_status_is_clean(request):
+    """After every GPU test: no kernel may have reported a bounded wait that ran out."""
+    yield
+    if "gpu" in request.keywords:
+        import torch
+
+        if torch.cuda.is_available():
+            from cuequivariance_b200 import _lib
+
+            _lib.check_status()
