@@ -216,6 +216,7 @@ def lib() -> C.CDLL:
     L.cueq_b200_fctp_fused_gw.argtypes = [C.POINTER(FctpFusedGwArgs), C.c_void_p]
     L.cueq_b200_gemm_f32x3.argtypes = [C.POINTER(GemmF32x3Args), C.c_void_p]
     L.cueq_b200_gemm_f32x3_tn.argtypes = [C.POINTER(GemmF32x3TnArgs), C.c_void_p]
+    L.cueq_b200_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     if L.cueq_b200_abi_version() != 1:
         raise CueqError("libcueq_b200.so has an unexpected ABI version; rebuild it")
     L.cueq_b200_sizeof.restype = C.c_int64

@@ -367,6 +367,12 @@ typedef struct {
 } cueq_fctp_fused_gw_args;
 int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* args, void* stream);
 
+/* Self-test (no counterpart in the reference): launches one thread that waits on a barrier nothing
+ * arrives on.  After about half a second the wait gives up, `status` (device int32) becomes 2 and
+ * `waited_cycles` (nullable device int64) receives the SM cycles spent; the context stays usable.
+ * This is the time-out path of every bounded wait in the tensor-core kernels. */
+int cueq_b200_selftest_bounded_wait(void* status, void* waited_cycles, void* stream);
+
 /* ---- channelwise forward for callers that cannot allocate ----------------------------------
  *
  * No counterpart in the reference.  cueq_b200_cw_forward expects the caller to keep the CSR row

@@ -128,3 +128,33 @@ def test_gemm_f32x3_tn_against_float64(K, M, N):
     assert float((cs.double() - ref_cs).abs().max()) <= 1e-5 * max(1.0, float(ref_cs.abs().max()))
     c2 = gemm_f32x3_tn(a[:, : M // 2 // 4 * 4], b)          # a column slice of a wider tensor, no column sums
     assert float((c2.double() - ref[: M // 2 // 4 * 4]).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+
+def test_bounded_wait_times_out_and_reports():
+    """A wait that nothing satisfies must come back by itself: the kernel returns within about a
+    second, the shared status word reads 2, `check_status()` raises and clears it, and the device
+    keeps working afterwards."""
+    import time
+
+    import cuequivariance_b200 as cb
+    from cuequivariance_b200._lib import CueqError
+
+    cb.check_status()                                   # clean before
+    status = _lib.status_word(DEV)
+    cycles = torch.zeros(1, dtype=torch.int64, device=DEV)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _lib.check(_lib.lib().cueq_b200_selftest_bounded_wait(status.data_ptr(), cycles.data_ptr(),
+                                                          C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    assert 0.05 < elapsed < 5.0, elapsed
+    assert int(status.item()) == 2 and int(cycles.item()) >= 1 << 30
+    with pytest.raises(CueqError):
+        cb.check_status()
+    cb.check_status()                                   # cleared by the raising call
+    a = torch.randn(256, 64, device=DEV)
+    from cuequivariance_b200.dense import gemm_f32x3
+
+    y = gemm_f32x3(a, a[:64])
+    assert torch.isfinite(y).all()
