@@ -49,4 +49,6 @@ def main(root, outdir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", os.path.dirname(os.path.abspath(__file__)))
+    if len(sys.argv) < 2:
+        raise SystemExit(f"usage: python {sys.argv[0]} <path of the cuEquivariance reference checkout>")
+    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))

@@ -12,7 +12,8 @@ from cuequivariance_b200 import compat
 from cuequivariance_b200.executor import Uniform1dProgram
 from oracle import naive
 
-REFERENCE = "/root/reference"
+# the reference checkout, when present, sits next to this repository
+REFERENCE = os.environ.get("CUEQ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 
 
 def _call_like_the_frontend(prog, inputs, input_indices, output_shapes, output_indices, math_dtype):
