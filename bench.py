@@ -345,16 +345,26 @@ def main():
         h_loss = torch.empty(1).pin_memory()
         params = list(mlp.parameters())
 
+        copy_stream = torch.cuda.Stream(device=dev)
+        x1_ready = torch.cuda.Event()
+
         def e2e_step():
-            d_x1.copy_(h_x1, non_blocking=True)
-            d_vec.copy_(h_vec, non_blocking=True)
+            # the node features (the largest upload) travel on a copy stream while the radial MLP and the
+            # spherical harmonics, which only need the edge vectors, already run
+            main = torch.cuda.current_stream()
+            copy_stream.wait_stream(main)
+            d_vec.copy_(h_vec, non_blocking=True)      # small uploads first: the copy engine serves them in issue order
             d_snd.copy_(h_snd, non_blocking=True)
             d_rcv.copy_(h_rcv, non_blocking=True)
-            nodes = d_x1.detach().requires_grad_(True)
+            with torch.cuda.stream(copy_stream):
+                d_x1.copy_(h_x1, non_blocking=True)
+                x1_ready.record(copy_stream)
             r = d_vec.norm(dim=1)
             hidden = mlp[1](mlp[0](bessel(r)))
             ww = linear_f32x3(hidden, mlp[2].weight, mlp[2].bias)   # the wide output layer on the tensor cores
             yy = sh(d_vec)
+            main.wait_event(x1_ready)
+            nodes = d_x1.detach().requires_grad_(True)
             out = op(nodes, yy, ww, d_snd, d_rcv)
             loss = (out * cot).sum()
             torch.autograd.grad(loss, [nodes] + params)
