@@ -183,3 +183,32 @@ def test_split_tf32_halves():
     assert int((lo.view(torch.int32) & 8191).abs().max()) == 0
     assert float((hi + lo - x).abs().max()) <= 2.0 ** -21 * float(x.abs().max())
     assert float((hi - x).abs().max()) <= 2.0 ** -11 * float(x.abs().max())
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 and as C++ on its own, and a C program that
+    only includes it must link against the library and read the ABI version without CUDA or torch."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    header = os.path.join(ROOT, "include", "cueq_b200.h")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", header], check=True)
+    gxx = shutil.which("g++")
+    if gxx:
+        subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-x", "c++", header], check=True)
+    src = tmp_path / "probe.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "cueq_b200.h"\n'
+        "int main(void) {\n"
+        "  cueq_gemm_f32x3_args a = {0};\n"
+        '  printf("%d %lld %d\\n", cueq_b200_abi_version(), (long long)cueq_b200_sizeof(2), cueq_b200_gemm_f32x3(&a, 0) != 0);\n'
+        "  return 0;\n}\n")
+    exe = tmp_path / "probe"
+    libdir = os.path.dirname(str(_lib.LIB_PATH))
+    subprocess.run([gcc, "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-L", libdir,
+                    "-l:libcueq_b200.so", f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out[0] == "1" and int(out[1]) == C.sizeof(_lib.CwArgs) and out[2] == "1"
