@@ -212,3 +212,21 @@ def test_header_is_plain_c(tmp_path):
                     "-l:libcueq_b200.so", f"-Wl,-rpath,{libdir}"], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
     assert out[0] == "1" and int(out[1]) == C.sizeof(_lib.CwArgs) and out[2] == "1"
+
+
+def test_product_never_touches_the_oracle_or_scratch_files():
+    """The oracle is test infrastructure: nothing under the package may import or execute it, and no
+    committed file may reach into the scratch directory."""
+    import re
+
+    pkg = os.path.join(ROOT, "cuequivariance_b200")
+    bad = []
+    for base, _dirs, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(base, f), errors="ignore").read()
+                if re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M) or "_work/" in text or "_work." in text:
+                    bad.append(os.path.relpath(os.path.join(base, f), ROOT))
+    assert not bad, bad
+    for f in ("bench.py", "__graft_entry__.py"):
+        assert "_work" not in open(os.path.join(ROOT, f)).read(), f
