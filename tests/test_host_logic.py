@@ -105,3 +105,47 @@ def test_merged_symmetric_paths_counts():
     bwd = m.f.polynomial.backward([True, True], [True])
     merged = static_poly.merge_symmetric_paths(bwd)
     assert sorted(len(d.paths) for _, d in merged.operations) == [4, 4, 51, 86, 425, 1072]
+
+
+def test_fused_tp_flattening_choices():
+    """`uv,iu,iv` with equal multiplicities keeps v as the channel axis (one path per (irrep, i, u)); with mixed
+    small multiplicities every mode is flattened; with mixed large ones only the dense route remains."""
+    from cuequivariance_b200.fused_tp import FusedTPProgram
+
+    e = D.linear("8x0e+8x1o", "8x0e+8x1o")
+    prog = FusedTPProgram(e.polynomial, torch.float32)
+    assert prog.extent == 8 and sum(len(d.paths) for _, d in prog.flat.operations) == 8 * (1 + 3)
+    e = D.linear("6x0e+5x1o", "3x0e+7x1o")
+    prog = FusedTPProgram(e.polynomial, torch.float32)
+    assert prog.extent == 1 and sum(len(d.paths) for _, d in prog.flat.operations) == 6 * 3 + 3 * 5 * 7
+    m = cb.Linear("128x0e+128x1o", "64x0e+96x1o", layout=cb.ir_mul)
+    assert m.f is None and m._dense_plan is not None and len(m._dense_plan["paths"]) == 2
+    try:
+        m(torch.zeros(4, m.irreps_in.dim))
+    except ValueError as err:
+        assert "dense route" in str(err)
+    else:
+        raise AssertionError("a CPU tensor must not be accepted")
+
+
+def test_module_argument_errors():
+    """Same error behaviour as the reference modules for inconsistent weight arguments; CPU tensors raise."""
+    import pytest
+
+    m = cb.Linear("4x0e+4x1o", "4x0e+4x1o", layout=cb.ir_mul, weight_classes=3)
+    assert m.weight.shape == (3, m.weight_numel)
+    with pytest.raises(ValueError, match="weight_indices"):
+        m(torch.zeros(2, m.irreps_in.dim))
+    with pytest.raises(ValueError, match="Internal weights"):
+        m(torch.zeros(2, m.irreps_in.dim), torch.zeros(3, m.weight_numel), weight_indices=torch.zeros(2, dtype=torch.int64))
+    with pytest.raises(ValueError, match="shared"):
+        cb.Linear("4x0e", "4x0e", layout=cb.ir_mul, shared_weights=False, internal_weights=True)
+    tp = cb.ChannelWiseTensorProduct("4x0e+4x1o", "0e+1o", ["0e", "1o"], layout=cb.mul_ir, shared_weights=False, internal_weights=False)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        tp(torch.zeros(3, tp.irreps_in1.dim), torch.zeros(3, tp.irreps_in2.dim), torch.zeros(3, tp.weight_numel))
+    from cuequivariance_b200.dense import gemm_f32x3, gemm_f32x3_tn, linear_f32x3
+
+    for fn, args in ((gemm_f32x3, (torch.zeros(4, 32), torch.zeros(8, 32))), (gemm_f32x3_tn, (torch.zeros(4, 8), torch.zeros(4, 8))),
+                     (linear_f32x3, (torch.zeros(4, 32), torch.zeros(8, 32)))):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            fn(*args)
