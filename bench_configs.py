@@ -1,6 +1,6 @@
 """Throughput of the other benchmark configurations (the headline one is ``bench.py``).
 
-    python -m cuequivariance_b200.bench_configs [--config 0|1|2|4|all] [--steps K]
+    python bench_configs.py [--config 0|1|2|2bf16|4|all] [--steps K]
 
 Prints one JSON line per configuration: device-timed (CUDA events) steps on seeded
 synthetic inputs of the configuration's shapes, with the per-kernel breakdown of the native
@@ -15,8 +15,12 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import cuequivariance_b200 as cb
 from cuequivariance_b200 import profiling

@@ -21,7 +21,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC,-O3",
-    "--use_fast_math=false" if False else "-DCUEQ_B200",
+    "-DCUEQ_B200",
 ]
 
 

@@ -25,6 +25,26 @@ int fail(const char* fmt, ...);
 
 static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
+// One flag per device ordinal.  Function attributes such as the dynamic shared-memory limit
+// belong to the device that was current when they were set, so a launcher that has configured
+// its kernel on one GPU still has to do it on the next GPU the same process uses.
+struct PerDeviceFlag {
+  static constexpr int kMax = 64;
+  bool done[kMax] = {};
+  static int current() {
+    int d = -1;
+    return cudaGetDevice(&d) == cudaSuccess ? d : -1;
+  }
+  bool get() const {
+    const int d = current();
+    return d >= 0 && d < kMax && done[d];
+  }
+  void set() {
+    const int d = current();
+    if (d >= 0 && d < kMax) done[d] = true;
+  }
+};
+
 // Load one element of a buffer whose element type is only known at run time.
 template <typename M>
 __device__ __forceinline__ M load_as(const void* p, int dtype, int64_t i) {

@@ -593,10 +593,10 @@ int grid_x(int num_receivers) {
 template <class G, int C, bool A>
 int launch_fwd_t(const CwParams& p, cudaStream_t st) {
   const size_t smem = Smem<G, C>::bytes_fwd();
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_fwd_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
   cw_fwd_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p);
@@ -607,10 +607,10 @@ int launch_fwd_t(const CwParams& p, cudaStream_t st) {
 template <class G, int C, bool A>
 int launch_fwd_bulk_t(const CwParams& p, cudaStream_t st) {
   const size_t smem = SmemBulk<G, C>::bytes();
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_fwd_bulk_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
   cw_fwd_bulk_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p);
@@ -633,10 +633,10 @@ int launch_fwd_bulk(const CwParams& p, int mul_ir, int cpl, cudaStream_t st) {
 template <class G, int C, bool A>
 int launch_bwd_t(const CwParams& p, const CwCoef& coef, cudaStream_t st) {
   const size_t smem = Smem<G, C>::bytes_bwd();
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_kernel<G, C, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid(grid_x(p.num_receivers), (p.extent + 32 * C - 1) / (32 * C));
   cw_bwd_kernel<G, C, A><<<grid, kWarps * 32, smem, st>>>(p, coef);

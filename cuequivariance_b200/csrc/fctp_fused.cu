@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1) fctp_fused_forward_kernel(cons
           for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(v2[c]));
         }
       }
-      if (ok && z < p.batch) {
+      if (ok && status_clean(p.status) && z < p.batch) {
         const int64_t off = z * p.ldo + task.out_off + half * 32;
         if (p.out_bf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) fctp_fused_gx_kernel(const __gri
             gacc[i][1] = fmaf(cij, r[1][jj], gacc[i][1]);
           }
       }
-      if (valid && !dead) {
+      if (valid && !dead && status_clean(p.status)) {
         float* dst = p.gxa + z * p.lda + unit.offa + g * 4 + ah * 2;
 #pragma unroll
         for (int i = 0; i < 5; ++i)
@@ -790,7 +790,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1) fctp_fused_gw_kernel(const __g
         unsigned v[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + t * FN + half * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (ok && ngroups > 0) {
+        if (ok && status_clean(p.status) && ngroups > 0) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst + half * 32 + c), "f"(__uint_as_float(v[c])),
@@ -851,10 +851,10 @@ extern "C" int cueq_b200_fctp_fused_forward(const cueq_fctp_fused_args* a, void*
   p.status = reinterpret_cast<int*>(a->status);
   std::memcpy(p.tasks, a->tasks, sizeof(cueq_fctp_fused_task) * a->num_tasks);
   const size_t smem = kStagesF * kStageF + kStagesB * kTileBF + 160 + 40 * 8 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_tasks);
   fctp_fused_forward_kernel<<<grid, kThreadsFwd, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mw, p);
@@ -893,10 +893,10 @@ extern "C" int cueq_b200_fctp_fused_gx(const cueq_fctp_fused_gx_args* a, void* s
   p.status = reinterpret_cast<int*>(a->status);
   std::memcpy(p.units, a->units, sizeof(cueq_fctp_fused_unit) * a->num_units);
   const size_t smem = kMaxKG * kTileAF + kStagesG * kTileBG + kXTile + 512 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_gx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid((unsigned)((a->batch + FM - 1) / FM), (unsigned)a->num_units);
   fctp_fused_gx_kernel<<<grid, kThreadsG, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, mw, p);
@@ -939,10 +939,10 @@ extern "C" int cueq_b200_fctp_fused_gw(const cueq_fctp_fused_gw_args* a, void* s
   p.blocks_per_split = (total_blocks + splits - 1) / splits;
   splits = (total_blocks + p.blocks_per_split - 1) / p.blocks_per_split;
   const size_t smem = kStagesWA * kTileAF + kStagesWB * kTileBF + 512 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(fctp_fused_gw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   dim3 grid((unsigned)splits, (unsigned)a->num_units, 64 / (2 * kTilesW));
   fctp_fused_gw_kernel<<<grid, kThreadsFwd, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mg, p);

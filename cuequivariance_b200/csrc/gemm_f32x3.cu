@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreadsRes, 1) gemm_f32x3_kernel(const __grid
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          if (!dead && col0 < p.N && m0 + q * 32 < p.M)
+          if (!dead && status_clean(p.status) && col0 < p.N && m0 + q * 32 < p.M)
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
                          ::"l"(&map_c), "r"(s32(mine)), "r"(col0), "r"(m0 + q * 32) : "memory");
           asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
@@ -362,7 +362,7 @@ __global__ void __launch_bounds__(kThreadsX, 1) gemm_f32x3_stream_kernel(const _
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        if (ok && col0 < p.N && m0 + q * 32 < p.M)
+        if (ok && status_clean(p.status) && col0 < p.N && m0 + q * 32 < p.M)
           asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
                        ::"l"(&map_c), "r"(s32(mine)), "r"(col0), "r"(m0 + q * 32) : "memory");
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kThreadsRes, 1) gemm_f32x3_tn_kernel(const __g
 #pragma unroll
         for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(v2[c]));
       }
-      if (ok && nkb > 0 && m < p.M) {
+      if (ok && status_clean(p.status) && nkb > 0 && m < p.M) {
         if (part < 2) {
           float* dst = p.C + (int64_t)m * p.ldc + n0 + part * 32;
 #pragma unroll
@@ -664,28 +664,28 @@ extern "C" int cueq_b200_gemm_f32x3(const cueq_gemm_f32x3_args* g, void* stream)
   const unsigned mtiles = (unsigned)((g->M + XM - 1) / XM);
   if (resident) {
     const size_t smem = 2 * kMaxKB * kBlkA + 4 * 2 * kBlkB + 8 * 4096 + 256 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static cueq::PerDeviceFlag configured;
+    if (!configured.get()) {
       CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
+      configured.set();
     }
     gemm_f32x3_kernel<<<dim3(mtiles), kThreadsRes, smem, st>>>(ma, mh, ml, mc, p);
   } else if (nt == 64) {
     using Cfg = StreamCfg<64>;
     const size_t smem = Cfg::kStages * Cfg::kStage + 4 * 2 * 4096 + 256 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static cueq::PerDeviceFlag configured;
+    if (!configured.get()) {
       CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
+      configured.set();
     }
     gemm_f32x3_stream_kernel<64><<<dim3(mtiles, (unsigned)((g->N + 63) / 64)), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
   } else {
     using Cfg = StreamCfg<128>;
     const size_t smem = Cfg::kStages * Cfg::kStage + 4 * 2 * 4096 + 256 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static cueq::PerDeviceFlag configured;
+    if (!configured.get()) {
       CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
+      configured.set();
     }
     gemm_f32x3_stream_kernel<128><<<dim3(mtiles, (unsigned)((g->N + 127) / 128)), kThreadsX, smem, st>>>(ma, mh, ml, mc, p);
   }
@@ -710,10 +710,10 @@ extern "C" int cueq_b200_gemm_f32x3_tn(const cueq_gemm_f32x3_tn_args* g, void* s
   p.ldc = g->ldc; p.M = (int)g->M; p.N = (int)g->N; p.K = (int)g->K;
   p.status = reinterpret_cast<int*>(g->status);
   const size_t smem = kTnOpStages * kTnOp + kTnRawStages * kTnRaw + 256 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_f32x3_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   const int64_t total_kb = (g->K + XKB - 1) / XKB;
   dim3 grid((unsigned)((g->M + XM - 1) / XM), (unsigned)((g->N + TN_N - 1) / TN_N), (unsigned)((total_kb + kTnBlocks - 1) / kTnBlocks));

@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kThreads) gemm_bf16_tn_kernel(const __grid_con
                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                    : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      if (ok && row < p.M) {
+      if (ok && status_clean(p.status) && row < p.M) {
         const int64_t roff = (int64_t)(row / p.rows_per_group) * p.group_stride + (int64_t)(row % p.rows_per_group) * p.ldc + n0 + half * 32;
         if (p.out_bf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + roff;
@@ -210,10 +210,10 @@ extern "C" int cueq_b200_gemm_bf16(const cueq_gemm_args* g, void* stream) {
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.accumulate = g->accumulate; p.out_bf16 = g->out_bf16;
   p.a_mn_major = g->a_mn_major; p.b_mn_major = g->b_mn_major; p.status = reinterpret_cast<int*>(g->status);
   const size_t smem = kStagesTc * kStageBytes + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
+  static cueq::PerDeviceFlag configured;
+  if (!configured.get()) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.set();
   }
   // split K when the tile grid alone cannot fill the GPU (partial sums then need a float32 C that
   // the caller zeroed or wants accumulated into)

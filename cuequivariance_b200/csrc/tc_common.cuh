@@ -35,8 +35,18 @@ __device__ __forceinline__ bool bar_wait(unsigned long long* b, unsigned parity,
   while (clock64() - t0 < kMaxWaitCycles) {
     if (bar_try(b, parity)) return true;
   }
-  if (status) atomicExch(status, 2);
+  if (status) {
+    atomicExch(status, 2);
+    __threadfence();  // visible to the epilogue threads before anything this thread signals next
+  }
   return false;
+}
+// True while no bounded wait has run out on this device since the host last cleared the word.
+// Every epilogue asks this after its own wait and before its first global store: a role of
+// the same CTA that gave up has stored 2 (and fenced) before it released the epilogue, so a
+// partial accumulator never reaches caller-owned memory; the host learns of it from the word.
+__device__ __forceinline__ bool status_clean(const int* status) {
+  return !status || *reinterpret_cast<const volatile int*>(status) == 0;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"

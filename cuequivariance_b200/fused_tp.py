@@ -109,14 +109,12 @@ class _TensorCoreUVW(torch.autograd.Function):
         import ctypes as C
 
         from . import _lib, profiling
-        from .executor import dtype_code
 
         a = owner._fctp_args(k, x1, x2, B)
         a.z = Z.data_ptr()
         a.z_dtype = _lib.BF16
         with profiling.kernel("fctp_build_z"):
             _lib.check(_lib.lib().cueq_b200_fctp_build_z(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
-        del dtype_code
 
     @staticmethod
     def _gemm(A, Bm, Cptr, M, N, K, lda, ldb, ldc, status, accumulate=0, out_bf16=0, a_mn=0, b_mn=0, rows_per_group=1, group_stride=0,

@@ -356,8 +356,6 @@ def test_linear_dense_route_against_oracle():
     x = torch.randn(B, m.irreps_in.dim, generator=gen)
     w = torch.randn(1, m.weight_numel, generator=gen)
     cot = torch.randn(B, m.irreps_out.dim, generator=gen)
-    t_in = cb.TransposeIrrepsLayout(s_in, source=cb.mul_ir, target=cb.ir_mul, device="cpu") if False else None
-    del t_in
 
     def grads(fn, xs, c):
         xs = [t.clone().requires_grad_(True) for t in xs]
@@ -386,3 +384,49 @@ def test_linear_dense_route_against_oracle():
     x_im = to_ir_mul(x.to(DEV)).cpu()
     ref = naive.segmented_polynomial(e.polynomial, [w, x_im])[0]
     _close(back(got[0]).cpu(), ref, 1e-5, 2e-6, "out vs oracle")
+
+
+def test_equivariant_tensor_product_wrapper_matches_oracle():
+    """`EquivariantTensorProduct` built from a descriptor: layout transposes of every operand around
+    the executor, gather of the second input and scatter of the output, against the oracle."""
+    e = D.channelwise_tensor_product("8x0e+8x1o+8x2e", "0e+1o+2e", ["0e", "1o", "2e"])
+    m = cb.EquivariantTensorProduct(e, layout=cb.mul_ir)
+    gen = torch.Generator().manual_seed(9)
+    E, N = 40, 6
+    w = torch.randn(E, e.inputs[0].dim, generator=gen)
+    x1 = torch.randn(N, e.inputs[1].dim, generator=gen)
+    x2 = torch.randn(E, e.inputs[2].dim, generator=gen)
+    snd, rcv = torch.randint(0, N, (E,), generator=gen), torch.randint(0, N, (E,), generator=gen)
+    cot = torch.randn(N, e.outputs[0].dim, generator=gen)
+    blocks = [[(mu, ir.dim) for mu, ir in r.irreps] for r in e.inputs + e.outputs]
+
+    def ref_fn(w_, a, b):
+        xs = [naive.transpose_layout(t, bl, True) for t, bl in zip((w_, a, b), blocks)]
+        (o,) = naive.segmented_polynomial(e.polynomial, xs, {1: snd}, {0: N}, {0: rcv})
+        return naive.transpose_layout(o, blocks[3], False)
+
+    ref = _derivatives(ref_fn, [w, x1, x2], cot)
+    got = _derivatives(lambda w_, a, b: m(w_, a, b, indices={1: snd.to(DEV)}, indices_out=rcv.to(DEV), size_out=N),
+                       [w.to(DEV), x1.to(DEV), x2.to(DEV)], cot.to(DEV))
+    _close(got[0], ref[0], 1e-5, 2e-6, "out")
+    for a, b in zip(got[1], ref[1]):
+        _close(a, b, 1e-4, 2e-5, "grad")
+    for a, b in zip(got[2], ref[2]):
+        _close(a, b, 1e-3, 2e-4, "gradgrad")
+
+
+def test_modules_survive_a_pickle_round_trip():
+    """`__reduce__` rebuilds the module from (polynomial, method, math_dtype, ...), like the reference
+    (cuequivariance_torch/primitives/segmented_polynomial.py:237-248): the copy must give the same bits."""
+    import pickle
+
+    e = D.channelwise_tensor_product("8x0e+8x1o", "0e+1o+2e", "0e+1o")
+    f = cb.SegmentedPolynomial(e.polynomial, method="uniform_1d", math_dtype="float32", name="pickled")
+    f2 = pickle.loads(pickle.dumps(f))
+    assert f2.method == f.method and f2.math_dtype == f.math_dtype and f2.name == "pickled" and repr(f2) == repr(f)
+    xs = [torch.randn(5, o.size, device=DEV) for o in e.polynomial.inputs]
+    assert torch.equal(f(xs)[0], f2(xs)[0])
+    tp = cb.ChannelWiseTensorProduct("8x0e+8x1o", "0e+1o", ["0e", "1o"], layout=cb.mul_ir, shared_weights=True, internal_weights=True, device=DEV)
+    tp2 = pickle.loads(pickle.dumps(tp))
+    a, b = torch.randn(5, tp.irreps_in1.dim, device=DEV), torch.randn(5, tp.irreps_in2.dim, device=DEV)
+    assert torch.equal(tp(a, b), tp2(a, b))

@@ -1,0 +1,56 @@
+"""The reference's own torch tests, unmodified, run against this library through the import
+boundary of the closed kernel package (``cuequivariance_ops_torch`` stand-in in
+``cuequivariance_b200/compat``): the reference front-end packs its argument lists, the
+registered op / the ``FusedTensorProductOp`` classes of the stand-in hand them to the CUDA
+kernels, and the tests compare with the reference's ``naive`` method themselves
+(cuequivariance_torch/tests/primitives/segmented_polynomial_test.py:208-265: every
+shared / indexed / batched combination, first derivatives and double backward;
+tests/operations/channel_wise_test.py:231-305: fused gather/scatter equals explicit gather,
+product and scatter_add, with double backward).
+
+The reference is staged under ``baseline/_ref`` by ``baseline/stage_reference.py`` (it is not
+part of this repository's history); the tests are skipped when it is missing.  They run in a
+child process so that the reference import does not leak into the other tests.  Left out:
+the export modes (TorchScript, torch.export, ONNX, TensorRT), which need the closed package's
+native operator registrations, the triangle / attention tests and ``indexed_linear``.
+"""
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BASELINE = os.path.join(ROOT, "baseline")
+TESTS = os.path.join(BASELINE, "_ref", "reference_tests")
+
+SELECTIONS = [
+    ("primitives/segmented_polynomial_test.py", "test_segmented_polynomial_indexing"),
+    ("primitives/segmented_polynomial_test.py", "test_segmented_polynomial_dytpes"),
+    ("operations/channel_wise_test.py", "test_channel_wise_fwd or test_channel_wise_bwd_bwd or test_channel_wise_indexing"),
+    ("operations/fully_connected_test.py", "test_fully_connected"),
+    ("operations/symmetric_contraction_test.py", "test_symmetric_contraction"),
+    ("operations/spherical_harmonics_test.py", "not export"),
+    ("primitives/transpose_test.py", "test_transpose"),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path,select", SELECTIONS, ids=[f"{p.split('/')[-1]}::{s.split(' ')[0]}" for p, s in SELECTIONS])
+def test_reference_tests_pass_on_this_library(path, select):
+    if not os.path.isdir(TESTS):
+        pytest.skip("the reference is not staged under baseline/_ref")
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([BASELINE, ROOT, env.get("PYTHONPATH", "")])
+    cmd = [sys.executable, "-m", "pytest", "-p", "ref_pytest_plugin", "-q", "-x", "--no-header", "-p", "no:cacheprovider",
+           "--rootdir", TESTS, os.path.join(TESTS, path), "-k", select]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env, cwd=TESTS)
+    tail = "\n".join((r.stdout + r.stderr).splitlines()[-40:])
+    assert r.returncode == 0, tail
+    m = re.search(r"(\d+) passed", r.stdout)
+    assert m and int(m.group(1)) > 0, "no reference test ran:\n" + tail
+    out_dir = os.environ.get("CUEQ_B200_REPORT_DIR")
+    if out_dir:
+        with open(os.path.join(out_dir, "reference_suite.txt"), "a") as f:
+            f.write(f"{path} -k '{select}': {r.stdout.strip().splitlines()[-1]}\n")
