@@ -55,7 +55,7 @@ class CwArgs(C.Structure):
         ("extent", C.c_int32), ("x1_offset", C.c_int32), ("num_paths", C.c_int32), ("num_terms", C.c_int32),
         ("w_offset", C.c_int32 * 8), ("out_offset", C.c_int32 * 8),
         ("x1_mul_ir", C.c_int32), ("out_mul_ir", C.c_int32), ("channels_per_lane", C.c_int32), ("staging", C.c_int32),
-        ("status", C.c_void_p), ("recv_mod", C.c_int32), ("reserved2", C.c_int32),
+        ("status", C.c_void_p), ("recv_mod", C.c_int32), ("variant", C.c_int32),
     ]
 
 

@@ -77,6 +77,16 @@ def emit_group(l1: int, paths) -> str:
     A(f"  static constexpr int SUMD3 = {out_off[-1]};")
     A(f"  static constexpr int MAXD3 = {max(d3s)};")
     A(f"  static constexpr int NX2 = {max(l2 for l2, _ in paths) ** 2 + 2 * max(l2 for l2, _ in paths) + 1};")
+    # two halves of the group with about the same number of multiply-adds: the forward kernel that
+    # gives a receiver to a pair of warps lets each warp compute the output blocks of one half
+    cost = [len(pt) + min(d1, dd) for pt, dd in zip(pats, d3s)]
+    best = min(range(1, 2 ** len(paths) - 1), key=lambda msk: (abs(sum(c for q, c in enumerate(cost) if msk >> q & 1) * 2 - sum(cost)), msk)) \
+        if len(paths) > 1 else 0
+    half = [best >> q & 1 for q in range(len(paths))]
+    slot = [sum(1 for r in range(q) if half[r] == half[q]) for q in range(len(paths))]
+    A("  __host__ __device__ static constexpr int half_of(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, half)))
+    A("  __host__ __device__ static constexpr int slot_of(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, slot)))
+    A(f"  static constexpr int HALF_PATHS = {max(half.count(0), half.count(1))};")
     A("  static constexpr const char* signature() { return \"%s\"; }" % group_signature(l1, paths))
     A("  __host__ __device__ static constexpr int d3(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, d3s)))
     A("  __host__ __device__ static constexpr int out_offset(int p) { constexpr int t[NPATH + 1] = {%s}; return t[p]; }" % ", ".join(map(str, out_off)))
@@ -93,23 +103,34 @@ def emit_group(l1: int, paths) -> str:
         q0 = pair_off[p]
         A(f"      float m[{len(pat)}];")
         A(f"      cw_load_m<{q0}, {len(pat)}>(M, m);")
-        # i-major emission: consecutive multiply-adds go to different accumulators t[k], so that
-        # the chains over i of the d3 outputs interleave instead of running one after the other
-        A(f"      float t[{d3}][C];")
-        seen_k = set()
         by_i2: dict[int, list] = {}
         for q, (i, k, _) in enumerate(pat):
             by_i2.setdefault(i, []).append((q, k))
-        for i in sorted(by_i2):
-            for q, k in by_i2[i]:
+        if d1 < d3:
+            # fewer input than output components: scale the inputs by the weight once (d1 multiplies)
+            # and add every product straight into its accumulator, instead of summing unweighted
+            # products in temporaries and scaling d3 of them at the end
+            A(f"      float xw[{d1}][C];")
+            for i in sorted(by_i2):
+                A(f"      CW_MULV4(xw[{i}], W, X[{i}]);")
+            for i in sorted(by_i2):
+                for q, k in by_i2[i]:
+                    A(f"      CW_FMA4(acc[{out_off[p] + k}], m[{q}], xw[{i}]);")
+        else:
+            # i-major emission: consecutive multiply-adds go to different accumulators t[k], so that
+            # the chains over i of the d3 outputs interleave instead of running one after the other
+            A(f"      float t[{d3}][C];")
+            seen_k = set()
+            for i in sorted(by_i2):
+                for q, k in by_i2[i]:
+                    if k in seen_k:
+                        A(f"      CW_FMA4(t[{k}], m[{q}], X[{i}]);")
+                    else:
+                        seen_k.add(k)
+                        A(f"      CW_MUL4(t[{k}], m[{q}], X[{i}]);")
+            for k in range(d3):
                 if k in seen_k:
-                    A(f"      CW_FMA4(t[{k}], m[{q}], X[{i}]);")
-                else:
-                    seen_k.add(k)
-                    A(f"      CW_MUL4(t[{k}], m[{q}], X[{i}]);")
-        for k in range(d3):
-            if k in seen_k:
-                A(f"      CW_FMAV4(acc[{out_off[p] + k}], W, t[{k}]);")
+                    A(f"      CW_FMAV4(acc[{out_off[p] + k}], W, t[{k}]);")
         A("    }")
     A("  }")
 
@@ -131,6 +152,14 @@ def emit_group(l1: int, paths) -> str:
         by_i: dict[int, list] = {}
         for q, (i, k, terms) in enumerate(pat):
             by_i.setdefault(i, []).append((q, k, terms))
+        # the x2 gradient needs sum_u w[u] x1[i,u] g[k,u]: the weight is folded into whichever of
+        # the two factors has fewer components (d1 or d3 multiplies per path)
+        scale_g = d3 < d1
+        if scale_g:
+            ks = sorted({k for lst in by_i.values() for _, k, _ in lst})
+            A(f"      float gs[{d3}][C];")
+            for k in ks:
+                A(f"      CW_MULV4(gs[{k}], W, G[{k}]);")
         t = term_cursor
         for i in range(d1):
             lst = by_i.get(i, [])
@@ -140,14 +169,20 @@ def emit_group(l1: int, paths) -> str:
             A("      {")
             A(f"        float m[{len(lst)}];")
             A(f"        cw_load_m<{q0 + qa}, {len(lst)}>(M, m);")
-            A("        float s[C], xw[C];")
-            A(f"        CW_MULV4(xw, W, X[{i}]);")
+            if scale_g:
+                A("        float s[C];")
+            else:
+                A("        float s[C], xw[C];")
+                A(f"        CW_MULV4(xw, W, X[{i}]);")
             for n, (q, k, terms) in enumerate(lst):
                 if n == 0:
                     A(f"        CW_MUL4(s, m[{q - qa}], G[{k}]);")
                 else:
                     A(f"        CW_FMA4(s, m[{q - qa}], G[{k}]);")
-                A(f"        {{ const float v = CW_DOT4(xw, G[{k}]);")
+                if scale_g:
+                    A(f"        {{ const float v = CW_DOT4(X[{i}], gs[{k}]);")
+                else:
+                    A(f"        {{ const float v = CW_DOT4(xw, G[{k}]);")
                 for j, _c in terms:
                     A(f"          r[{j_base + j}] = fmaf(coef.c[{t}], v, r[{j_base + j}]);")
                     t += 1
