@@ -16,7 +16,8 @@ ranks), `e2e` (same step fed from pinned host buffers through the public module 
 including the radial MLP and spherical harmonics that produce the per-edge operands),
 `roofline` (dominant kernel, timed live with CUDA events around its launches),
 `cpu_baseline` (the CPU oracle on a bounded slice, rank 0, N=1) and `clocks`.
-`--impl reference` times the CPU oracle port alone.
+`--impl reference` times the CPU arm alone: the unmodified reference's naive path when it is
+staged under `baseline/_ref` (kind "reference"), else the oracle port (kind "port"); same slice.
 """
 from __future__ import annotations
 
@@ -142,21 +143,84 @@ def cpu_oracle_rate(edges=CPU_SAMPLE_EDGES, nodes=CPU_SAMPLE_NODES, repeats=1, w
     return edges / (sum(times) / len(times)), cores, sum(times) / len(times)
 
 
+def cpu_reference_rate(edges=CPU_SAMPLE_EDGES, nodes=CPU_SAMPLE_NODES, repeats=1, warmup=0):
+    """The same slice through the unmodified reference (its `ChannelWiseTensorProduct` with
+    `method="naive"`, the only execution path it has without its closed kernel package), when
+    the reference is staged under `baseline/_ref`; returns None otherwise."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import refenv
+
+    if not refenv.available():
+        return None
+    import torch
+
+    cue, cuet = refenv.activate()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tp = cuet.ChannelWiseTensorProduct(cue.Irreps("O3", IRREPS1), cue.Irreps("O3", IRREPS2), [cue.O3(l, (-1) ** l) for l in range(4)],
+                                       layout=cue.mul_ir, shared_weights=False, internal_weights=False, method="naive")
+    sh = cuet.SphericalHarmonics([0, 1, 2, 3], normalize=True, method="naive")
+    gen = torch.Generator().manual_seed(30)
+    x1 = torch.randn(nodes, tp.irreps_in1.dim, generator=gen)
+    x2 = sh(torch.randn(edges, 3, generator=gen)).detach()
+    w = torch.randn(edges, tp.weight_numel, generator=gen)
+    snd = torch.randint(0, nodes, (edges,), generator=gen)
+    rcv = torch.sort(torch.randint(0, nodes, (edges,), generator=gen)).values
+    cot = torch.randn(nodes, tp.irreps_out.dim, generator=gen)
+
+    def step():
+        xs = [t.clone().requires_grad_(True) for t in (w, x1, x2)]
+        o = tp(xs[1], xs[2], xs[0], indices_1=snd, indices_out=rcv, size_out=nodes)
+        torch.autograd.grad((o * cot).sum(), xs)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    return edges / (sum(times) / len(times)), cores, sum(times) / len(times)
+
+
+def cpu_baseline(repeats=1, warmup=0):
+    """(rate, cores, seconds per step, kind): the reference itself when staged, else the port."""
+    try:
+        r = cpu_reference_rate(repeats=repeats, warmup=warmup)
+    except Exception as ex:  # a broken staging must not take the benchmark down: fall back to the port and say so
+        sys.stderr.write(f"reference arm: staged reference failed ({type(ex).__name__}: {ex}); timing the port\n")
+        r = None
+    if r is not None:
+        return r + ("reference",)
+    return cpu_oracle_rate(repeats=repeats, warmup=warmup) + ("port",)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rate, cores, sec = cpu_oracle_rate(repeats=args.steps, warmup=args.warmup)
+    rate, cores, sec, kind = cpu_baseline(repeats=args.steps, warmup=args.warmup)
     sample = f"{CPU_SAMPLE_EDGES} edges / {CPU_SAMPLE_NODES} nodes of the same irreps and channel count, fwd+bwd, per step"
     print(json.dumps({
         "impl": "reference", "metric": "edges/s channelwise TP fwd+bwd (1M edges,128ch,lmax3)", "value": rate, "unit": "edges/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config 3 shape, CPU slice: " + sample, "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": rate, "unit": "edges/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": rate, "unit": "edges/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": rate, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def kernel_source_digest() -> str:
+    """SHA-1 over the sources of the channelwise kernels (what a DRAM-traffic capture is valid for)."""
+    import hashlib
+
+    h = hashlib.sha1()
+    for name in ("cw_kernels.cu", "cw_macros.cuh", "gen_cw_groups.py"):
+        with open(os.path.join(ROOT, "cuequivariance_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
 
 
 # ----------------------------------------------------------------------------------------------
@@ -176,6 +240,68 @@ def group_bytes(plan, g, E, n_recv, n_nodes, backward: bool):
     if not backward:
         return b + n_recv * d3 * X           # + output blocks
     return b + n_recv * d3 * X + E * (npath * X + 16 * 4) + n_nodes * d1[l1] * X  # + gw, gx2, gx1
+
+
+def sharded_parity(tp, out, gx1, x1_l, x2, w, snd_l, rcv_l, cot, N, world, rank, dev):
+    """Correctness of the sharded step, checked outside the timed region on a fixed sub-graph against
+    single-GPU evaluations of the same module (which the test-suite pins on the CPU oracle):
+
+    * every rank: its first 256 output rows against the plain fused call on the full node table (all of
+      those receivers' edges are local to the rank, the node table is all-gathered once for the check);
+    * the node-feature gradient rows of nodes [0, 32) (owned by rank 0): edges that send from those nodes
+      live on every rank, so each rank contributes its matching edges (weights, harmonics, and the cotangent
+      row of each edge's receiver) by all-gather; rank 0 evaluates them unsharded and compares with the rows
+      it received from the reduce-scatter.
+    Returns the dict printed under "parity" (same on every rank)."""
+    import torch
+    import torch.distributed as dist
+
+    n_loc = x1_l.shape[0]
+    x1_all = torch.empty((N, x1_l.shape[1]), dtype=x1_l.dtype, device=dev)
+    dist.all_gather_into_tensor(x1_all, x1_l.detach().contiguous())
+    R = min(256, n_loc)
+    e_hi = int(torch.searchsorted(rcv_l, torch.tensor([R], device=dev, dtype=rcv_l.dtype))[0])
+    with torch.no_grad():
+        ref = tp(x1_all, x2[:e_hi].detach(), w[:e_hi].detach(), indices_1=snd_l[:e_hi], indices_out=rcv_l[:e_hi], size_out=R)
+    d_out = float((out[:R] - ref).abs().max())
+    s_out = float(ref.abs().max())
+    ok_out = d_out <= 1e-5 * s_out + 2e-6 * max(1.0, s_out)
+
+    S = 32
+    sel = torch.nonzero(snd_l < S).flatten()
+    P = (S * 32 * 3) // world + 64
+    cnt = torch.tensor([sel.numel()], device=dev, dtype=torch.int64)
+    if sel.numel() > P:
+        raise RuntimeError(f"parity check: {sel.numel()} edges from the sender window on rank {rank}, more than the {P} slots")
+
+    def pad(t):
+        buf = torch.zeros((P,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+        buf[: t.shape[0]] = t
+        return buf
+
+    parts = [pad(w[sel].detach()), pad(x2[sel].detach()), pad(cot[rcv_l[sel].long()]), pad(snd_l[sel])]
+    gathered = []
+    for t in parts + [cnt]:
+        g = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(g, t.contiguous())
+        gathered.append(g)
+    d_g, s_g, ok_g = 0.0, 0.0, True
+    if rank == 0:
+        counts = gathered[4].flatten().tolist()
+        w_g, x2_g, cot_g, snd_g = (torch.cat([g[r, : counts[r]] for r in range(world)]) for g in gathered[:4])
+        win = x1_l[:S].detach().clone().requires_grad_(True)
+        per_edge = tp(win, x2_g, w_g, indices_1=snd_g)
+        (ref_g,) = torch.autograd.grad((per_edge * cot_g).sum(), win)
+        d_g = float((gx1[:S] - ref_g).abs().max())
+        s_g = float(ref_g.abs().max())
+        ok_g = d_g <= 1e-4 * s_g + 2e-5 * max(1.0, s_g)
+    flags = torch.tensor([float(ok_out), float(ok_g), d_out, d_g, s_g], device=dev, dtype=torch.float64)
+    mins, maxs = flags.clone(), flags.clone()
+    dist.all_reduce(mins, op=dist.ReduceOp.MIN)
+    dist.all_reduce(maxs, op=dist.ReduceOp.MAX)
+    return {"checked": "first 256 output rows of every rank vs the unsharded fused call; node-feature gradient rows of nodes 0..31 vs an unsharded evaluation of all edges that send from them",
+            "out_rows_per_rank": R, "out_max_abs_diff": float(maxs[2]), "gx1_rows": S, "gx1_edges": int(sum(gathered[4].flatten().tolist())),
+            "gx1_max_abs_diff": float(maxs[3]), "gx1_scale": float(maxs[4]), "ok": bool(mins[0] > 0 and mins[1] > 0)}
 
 
 def main():
@@ -296,6 +422,7 @@ def main():
         ev1.record()
         barrier()
     launches = profiling.launch_count
+    cb.check_status()   # raises if any bounded wait inside a kernel ran out during the timed steps
     ms = ev0.elapsed_time(ev1) / args.steps
     t = torch.tensor([ms], device=dev)
     if world > 1:
@@ -329,17 +456,30 @@ def main():
                 kernels[name] = {"ms": tot / n, "bytes": bts, "gbs": bts / (tot / n * 1e-3) / 1e9}
     dom = max(kernels, key=lambda k: kernels[k]["ms"]) if kernels else None
     total_kernel_ms = sum(v["ms"] for v in kernels.values())
-    total_bytes = sum(v["bytes"] for v in kernels.values())
-    traffic = None
+    # algorithmic bytes of the step: every operand of the forward and of the backward call read or written
+    # once (x2, both indices and the x2 gradient once per call, not once per group launch)
+    w_sz, x1_sz, x2_sz, out_sz = plan.row_sizes
+    n_loc = n1 - n0
+    fwd_bytes = 4 * (El * (w_sz + x2_sz + 2) + N * x1_sz + n_loc * out_sz)
+    bwd_bytes = fwd_bytes + 4 * (El * (w_sz + x2_sz) + N * x1_sz)
+    total_bytes = fwd_bytes + bwd_bytes
+    # measured DRAM bytes per edge of each launch come from one ncu capture (profiles/traffic.json); they are
+    # only reported while the kernel sources are the ones that capture was taken on
+    traffic, traffic_note = None, "no capture on record"
     try:
-        per_edge = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))["per_edge_bytes"].get(dom)
-        traffic = per_edge * El if per_edge else None  # ncu capture of a smaller case, scaled by edges
-    except (OSError, ValueError):
+        rec = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+        if rec.get("source_digest") != kernel_source_digest():
+            traffic_note = "capture on record predates the current kernel sources"
+        else:
+            per_edge = rec["per_edge_bytes"].get(dom)
+            traffic = per_edge * El if per_edge else None
+            traffic_note = rec.get("source", "")
+    except (OSError, ValueError, KeyError):
         pass
     roofline = None
     if dom:
         roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": kernels[dom]["gbs"] / peak, "traffic": traffic, "peak_source": peak_src,
+                    "frac": kernels[dom]["gbs"] / peak, "traffic": traffic, "traffic_note": traffic_note, "peak_source": peak_src,
                     "all_kernels": {k: {"ms": round(v["ms"], 4), "gbs": round(v["gbs"], 1)} for k, v in kernels.items()},
                     "step_algorithmic_gbs": total_bytes / (total_kernel_ms * 1e-3) / 1e9 if total_kernel_ms else None,
                     "step_frac": (total_bytes / (ms * 1e-3) / 1e9) / peak}
@@ -396,15 +536,22 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         h2d = h_x1.numel() * 4 + h_vec.numel() * 4 + h_snd.numel() * 4 + h_rcv.numel() * 4
+        cb.check_status()
         e2e = {"value": E / (float(t[0]) * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+               "d2h": "scalar loss only (the output rows and the node-feature gradient stay on the device, as in a training step)",
                "ms_per_step": float(t[0]),
                "includes": "H2D of node features, edge vectors, indices; radial MLP (output layer: this library's 3xTF32 tcgen05 GEMM) and spherical harmonics on device; "
                            "TP fwd; backward to node features and MLP parameters; D2H of the scalar"}
 
+    parity = None
+    if world > 1:
+        out, _, gx1, _ = device_step()
+        parity = sharded_parity(tp, out.detach(), gx1, x1_l, x2, w, snd_l, rcv_l, cot, N, world, rank, dev)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        rate, cores, sec = cpu_oracle_rate()
-        cpu = {"value": rate, "unit": "edges/s", "cores": cores, "kind": "port",
+        rate, cores, sec, kind = cpu_baseline()
+        cpu = {"value": rate, "unit": "edges/s", "cores": cores, "kind": kind,
                "sample": f"{CPU_SAMPLE_EDGES} edges / {CPU_SAMPLE_NODES} nodes, same irreps and channels, fwd+bwd, {sec:.1f} s"}
 
     if rank == 0:
@@ -417,9 +564,12 @@ def main():
                        "sharding": f"edges by receiver range over {world} GPU(s); all-gather of node features, reduce-scatter of their gradient",
                        "l2": "inputs larger than L2 (per-edge weights alone are 12.3 GB); no explicit flush"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
+            "parity": parity,
         }))
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit("sharded result differs from the single-GPU evaluation: " + json.dumps(parity))
 
 
 if __name__ == "__main__":

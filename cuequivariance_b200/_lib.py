@@ -90,7 +90,7 @@ class FctpArgs(C.Structure):
         ("ld1", C.c_int64), ("ld2", C.c_int64), ("batch", C.c_int64),
         ("off1", C.c_int32), ("off2", C.c_int32),
         ("d1", C.c_int32), ("d2", C.c_int32), ("d3", C.c_int32), ("U", C.c_int32), ("V", C.c_int32),
-        ("x_dtype", C.c_int32), ("z_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("x_dtype", C.c_int32), ("z_dtype", C.c_int32), ("ldz", C.c_int32),
     ]
 
 
@@ -197,6 +197,7 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_signature.argtypes = [C.c_int]
     L.cueq_b200_cw_group_signature.restype = C.c_char_p
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
+    L.cueq_b200_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     L.cueq_b200_cw_forward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_backward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_forward_noalloc.argtypes = [C.c_int, C.POINTER(CwNoAllocArgs), C.c_void_p]

@@ -19,6 +19,16 @@ int fail(const char* fmt, ...) {
 }  // namespace cueq
 
 extern "C" int cueq_b200_abi_version(void) { return CUEQ_B200_ABI_VERSION; }
+
+// One asynchronous copy between device pointers on `stream`; either side may be another GPU's memory
+// mapped into this process.  The driver serves it with a copy engine, so no SM is taken from the kernels
+// that run meanwhile.
+extern "C" int cueq_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (bytes == 0) return 0;
+  if (!dst || !src) return cueq::fail("copy: null pointer");
+  CUEQ_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, reinterpret_cast<cudaStream_t>(stream)));
+  return 0;
+}
 extern "C" const char* cueq_b200_last_error(void) { return cueq::error_buffer(); }
 extern "C" int64_t cueq_b200_sizeof(int which) {
   switch (which) {

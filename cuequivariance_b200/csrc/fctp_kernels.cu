@@ -2,7 +2,9 @@
 //
 // For one path (l1, l2, l3) of ``uvw,iu,jv,kw+ijk`` (descriptor:
 // cuequivariance/group_theory/descriptors/irreps_tp.py:22-91) with coupling tensor C[i,j,k]:
-//   build   : Z[(z,k), (u,v)] = sum_ij C[i,j,k] x1[z,i,u] x2[z,j,v]         (bf16, GEMM operand)
+//   build   : Z[(z,k), (u,v)] = sum_ij C[i,j,k] x1[z,i,u] x2[z,j,v]         (GEMM operand: bf16 for the
+//             bf16 GEMM, float32 for the float32-accurate three-pass TF32 GEMM; rows may be column
+//             blocks of a wider matrix, so that the paths feeding one output irrep share one GEMM)
 //   GEMMs   : out[(z,k), w] += Z W;   gW = Z^T gout;   gZ = gout W^T          (gemm_tc.cu)
 //   consume : gx1[z,i,u] += sum_jkv C[i,j,k] gZ[(z,k),(u,v)] x2[z,j,v]
 //             gx2[z,j,v] += sum_iku C[i,j,k] gZ[(z,k),(u,v)] x1[z,i,u]
@@ -32,7 +34,8 @@ struct FctpParams {
   int64_t batch;
   int off1, off2;     // element offsets of the path's segments inside a row
   int d1, d2, d3, U, V;
-  int z_is_bf16;      // consume: element type of gZ
+  int z_is_bf16;      // element type of Z / gZ
+  int64_t ldz;        // row pitch of Z / gZ in elements (>= U*V)
   float cg[kMaxD * kMaxD * kMaxD];  // C[i][j][k], row-major, already scaled by the path normalisation
 };
 
@@ -69,14 +72,18 @@ __device__ __forceinline__ void contract_S(const FctpParams& p, const float* xs1
   }
 }
 
-template <typename TX>
+__device__ __forceinline__ void store_pair(__nv_bfloat16* dst, float a0, float a1) {
+  *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a0, a1);
+}
+__device__ __forceinline__ void store_pair(float* dst, float a0, float a1) { *reinterpret_cast<float2*>(dst) = make_float2(a0, a1); }
+
+template <typename TX, typename TZ>
 __global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_constant__ FctpParams p) {
   extern __shared__ float sm[];
   float* xs1 = sm;
   float* xs2 = xs1 + p.d1 * p.U;
   float* T = xs2 + p.d2 * p.V;
-  __nv_bfloat16* Z = reinterpret_cast<__nv_bfloat16*>(p.z);
-  const int UV = p.U * p.V;
+  TZ* Z = reinterpret_cast<TZ*>(p.z);
   for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
     __syncthreads();
     load_sample<TX>(p, z, xs1, xs2);
@@ -94,7 +101,7 @@ __global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_co
 #pragma unroll
         for (int i = 0; i < kMaxD; ++i)
           tt[i] = i < p.d1 ? *reinterpret_cast<const float2*>(T + (k * p.d1 + i) * p.V + 2 * vp) : make_float2(0.f, 0.f);
-        __nv_bfloat16* zrow = Z + (z * p.d3 + k) * (int64_t)UV + 2 * vp;
+        TZ* zrow = Z + (z * p.d3 + k) * p.ldz + 2 * vp;
         for (int u = ug; u < p.U; u += ugroups) {
           float a0 = 0.f, a1 = 0.f;
 #pragma unroll
@@ -105,7 +112,7 @@ __global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_co
               a1 = fmaf(tt[i].y, xi, a1);
             }
           }
-          *reinterpret_cast<__nv_bfloat162*>(zrow + u * p.V) = __floats2bfloat162_rn(a0, a1);
+          store_pair(zrow + u * p.V, a0, a1);
         }
       }
     }
@@ -121,7 +128,6 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid
   float* S = T + p.d3 * p.d1 * p.V;
   float* g2 = S + p.d3 * p.d2 * p.U;   // [d2*V] block-level accumulator of gx2
   const TZ* GZ = reinterpret_cast<const TZ*>(p.z);
-  const int UV = p.U * p.V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
     __syncthreads();
@@ -141,7 +147,7 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid
 #pragma unroll
         for (int j = 0; j < kMaxD; ++j) a2[j] = 0.f;
         for (int k = 0; k < p.d3; ++k) {
-          const float g = ldf<TZ>(GZ, (z * p.d3 + k) * (int64_t)UV + u * p.V + v);
+          const float g = ldf<TZ>(GZ, (z * p.d3 + k) * p.ldz + u * p.V + v);
 #pragma unroll
           for (int i = 0; i < kMaxD; ++i)
             if (i < p.d1) a1[i] = fmaf(g, T[(k * p.d1 + i) * p.V + v], a1[i]);
@@ -178,6 +184,8 @@ int fill(const cueq_fctp_args* a, FctpParams& p) {
   p.x1 = a->x1; p.x2 = a->x2; p.z = a->z; p.gx1 = (float*)a->gx1; p.gx2 = (float*)a->gx2;
   p.ld1 = a->ld1; p.ld2 = a->ld2; p.batch = a->batch; p.off1 = a->off1; p.off2 = a->off2;
   p.d1 = a->d1; p.d2 = a->d2; p.d3 = a->d3; p.U = a->U; p.V = a->V; p.z_is_bf16 = a->z_dtype == CUEQ_BF16;
+  p.ldz = a->ldz > 0 ? a->ldz : (int64_t)a->U * a->V;
+  if (p.ldz < (int64_t)a->U * a->V || (p.ldz & 1)) return cueq::fail("fctp: the row pitch of Z must be even and at least U*V");
   for (int t = 0; t < a->d1 * a->d2 * a->d3; ++t) p.cg[t] = a->cg[t];
   return 0;
 }
@@ -193,8 +201,12 @@ extern "C" int cueq_b200_fctp_build_z(const cueq_fctp_args* a, void* stream) {
   if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
   const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (a->x_dtype == CUEQ_F32) fctp_build_z_kernel<float><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
-  else fctp_build_z_kernel<__nv_bfloat16><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  if (a->z_dtype != CUEQ_F32 && a->z_dtype != CUEQ_BF16) return cueq::fail("fctp: Z must be float32 or bfloat16");
+  const bool xb = a->x_dtype == CUEQ_BF16, zb = a->z_dtype == CUEQ_BF16;
+  if (!xb && !zb) fctp_build_z_kernel<float, float><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  else if (!xb && zb) fctp_build_z_kernel<float, __nv_bfloat16><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  else if (xb && !zb) fctp_build_z_kernel<__nv_bfloat16, float><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
+  else fctp_build_z_kernel<__nv_bfloat16, __nv_bfloat16><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -19,9 +19,12 @@ Two routes:
     gradient of Z) and a kernel that folds the gradient of Z back onto x1 and x2.  First
     derivatives only.  ``Z`` makes a round trip through HBM; building its tiles directly in
     shared memory inside the GEMM is the remaining step.
-  - float32/float64 inputs: INTERIM composite of device-side torch ops with a library GEMM in
-    full precision (TF32 off), differentiable to any order; kept because bf16 operands cannot
-    meet the float32 tolerance (a split-precision tensor-core variant is not written yet).
+  - float32 inputs: the same decomposition in float32 accuracy.  ``Z`` is written in float32 (the
+    paths that feed one output irrep side by side, so one GEMM per output component contracts them
+    all) and contracted by this library's three-pass TF32 tcgen05 GEMMs (``dense.gemm_f32x3`` and
+    its row-reduction twin for the weight gradient); differentiable to any order, because every
+    derivative of a tri-linear map is again one of the same four contractions.
+  - float64 inputs and per-sample weights: the generic kernel on the fully flattened product.
 """
 from __future__ import annotations
 
@@ -247,15 +250,7 @@ class DenseUVW:
         self._cg = {}
         self.offsets = [op.offsets() for op in d.operands]
         self.out_size = d.operands[3].size
-        self._coef = {}
-
-    def _c(self, k, device, dtype):
-        key = (k, device, dtype)
-        t = self._coef.get(key)
-        if t is None:
-            t = torch.tensor(self.d.paths[k].coefficients, dtype=dtype, device=device)
-            self._coef[key] = t
-        return t
+        self._flat = {}
 
     # -- tensor-core route ---------------------------------------------------------------------
     def _tc_applicable(self, w, x1, x2) -> bool:
@@ -458,30 +453,251 @@ class DenseUVW:
             if x1.dtype != x2.dtype:
                 x2 = x2.to(x1.dtype)
             return [_TensorCoreUVW.apply(self, w, x1, x2)]
-        io = x1.dtype
-        md = self.math_dtype or (io if io in (torch.float32, torch.float64) else torch.float32)
+        if x1.dtype == torch.float32 and x2.dtype == torch.float32 and w.dtype == torch.float32 and w.shape[0] == 1 \
+                and self.math_dtype in (None, torch.float32) and self._f32_applicable():
+            B = max(x1.shape[0], x2.shape[0])
+            x1 = x1.expand(B, -1) if x1.shape[0] != B else x1
+            x2 = x2.expand(B, -1) if x2.shape[0] != B else x2
+            return [_DenseOut.apply(self, w, x1.contiguous(), x2.contiguous())]
+        return self._flattened(x1.dtype)(inputs)
+
+    # -- float32 route: float32-accurate tensor-core GEMMs on the coupled operand -----------------
+    def _f32_applicable(self) -> bool:
+        return all(self.d.operands[0].segments[p.indices[0]][1] % 2 == 0 and max(p.coefficients.shape) <= 7 for p in self.d.paths)
+
+    def _flattened(self, io_dtype):
+        """float64 operands, per-sample weights and shapes the dense kernels do not take run on the
+        generic kernel with every mode but the output's innermost one flattened into paths: correct
+        for any shape, slow for large multiplicities (hundreds of thousands of paths)."""
+        md = self.math_dtype or (io_dtype if io_dtype in (torch.float32, torch.float64) else torch.float32)
+        prog = self._flat.get(md)
+        if prog is None:
+            import warnings
+
+            from .executor import evaluate
+            from .polynomial import Operation
+
+            poly = Polynomial(list(self.d.operands[:3]), [self.d.operands[3]], [(Operation((0, 1, 2, 3)), self.d)])
+            n = flattened_path_count(poly)
+            if n > FLATTEN_LIMIT:
+                warnings.warn(f"fully connected product: this call (dtype {io_dtype}, math {md}) is outside the dense kernels and runs "
+                              f"on the generic kernel with {n} flattened paths")
+            fp = FusedTPProgram(poly, md, None, "fully_connected_flattened")
+            prog = lambda xs, fp=fp: evaluate(fp, list(xs), {}, {}, {}, None)  # noqa: E731
+            self._flat[md] = prog
+        return prog
+
+    def _by_output(self):
+        if not hasattr(self, "_by_out"):
+            by = {}
+            for k, p in enumerate(self.d.paths):
+                by.setdefault(p.indices[3], []).append(k)
+            self._by_out = by
+        return self._by_out
+
+    @staticmethod
+    def _pad32(n: int) -> int:
+        return (n + 31) // 32 * 32
+
+    def _build_f32(self, k, x1, x2, Z, ldz, col0):
+        """Z[:, col0 : col0 + U*V] (rows (z, k), pitch ldz) = coupled operand of path k, float32."""
+        import ctypes as C
+
+        from . import _lib, profiling
+
+        a = self._fctp_args(k, x1, x2, x1.shape[0])
+        a.z = Z.data_ptr() + 4 * col0
+        a.z_dtype, a.ldz = _lib.F32, ldz
+        with profiling.kernel("fctp_build_z"):
+            _lib.check(_lib.lib().cueq_b200_fctp_build_z(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def _chunk(self, B: int, row_floats: int) -> int:
+        """Samples per pass so that the coupled operand of a pass stays below about 4 GB."""
+        return max(128, min(B, int(1e9 // max(1, row_floats)) // 128 * 128))
+
+    def map_out(self, w, x1, x2):
+        """out = F(w, x1, x2): per output irrep one coupled operand [(z, k), sum of the paths' (u, v)] and one
+        GEMM per component k against the stacked weight blocks."""
+        from .dense import gemm_f32x3
+
         d, off = self.d, self.offsets
-        B = max(x1.shape[0], x2.shape[0], w.shape[0])
-        pieces = [None] * d.operands[3].num_segments
-        prev = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = False
-        try:
-            for k, p in enumerate(d.paths):
-                sw, s1, s2, so = p.indices
-                u, v, wd = d.operands[0].segments[sw]
-                d1, d2, d3 = p.coefficients.shape
-                a = x1[:, off[1][s1] : off[1][s1] + d1 * u].reshape(-1, d1, u).to(md)
-                b = x2[:, off[2][s2] : off[2][s2] + d2 * v].reshape(-1, d2, v).to(md)
-                z = torch.einsum("ijk,ziu,zjv->zkuv", self._c(k, x1.device, md), a, b)
-                wk = w[:, off[0][sw] : off[0][sw] + u * v * wd].to(md)
-                if wk.shape[0] == 1:
-                    r = (z.reshape(-1, u * v) @ wk.reshape(u * v, wd)).reshape(-1, d3 * wd)
-                else:
-                    r = torch.einsum("zkq,zqw->zkw", z.reshape(z.shape[0], d3, u * v), wk.reshape(-1, u * v, wd)).reshape(-1, d3 * wd)
-                pieces[so] = r if pieces[so] is None else pieces[so] + r
-        finally:
-            torch.backends.cuda.matmul.allow_tf32 = prev
-        cols = []
-        for s, seg in enumerate(d.operands[3].segments):
-            cols.append(pieces[s] if pieces[s] is not None else x1.new_zeros(B, int(np.prod(seg)), dtype=md))
-        return [torch.cat(cols, dim=1).to(io)]
+        B, dev = x1.shape[0], x1.device
+        out = torch.zeros((B, self.out_size), dtype=torch.float32, device=dev)
+        for so, ks in sorted(self._by_output().items()):
+            d3, Wd = d.operands[3].segments[so][0], d.operands[3].segments[so][1]
+            cols = [self._pad32(d.operands[0].segments[d.paths[k].indices[0]][0] * d.operands[0].segments[d.paths[k].indices[0]][1]) for k in ks]
+            K = sum(cols)
+            Wp = -(-Wd // 4) * 4
+            WT = torch.zeros((Wp, K), dtype=torch.float32, device=dev)      # stacked W_p^T, zero rows/columns as padding
+            c0 = 0
+            for k, ck in zip(ks, cols):
+                sw = d.paths[k].indices[0]
+                U, V, _ = d.operands[0].segments[sw]
+                WT[:Wd, c0 : c0 + U * V] = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd).t()
+                c0 += ck
+            step = self._chunk(B, d3 * K)
+            for b0 in range(0, B, step):
+                b1 = min(B, b0 + step)
+                padded = any(c != d.operands[0].segments[d.paths[k].indices[0]][0] * d.operands[0].segments[d.paths[k].indices[0]][1] for k, c in zip(ks, cols))
+                Z = (torch.zeros if padded else torch.empty)(((b1 - b0) * d3, K), dtype=torch.float32, device=dev)
+                c0 = 0
+                for k, ck in zip(ks, cols):
+                    self._build_f32(k, x1[b0:b1], x2[b0:b1], Z, K, c0)
+                    c0 += ck
+                Z3 = Z.view(b1 - b0, d3, K)
+                for kk in range(d3):
+                    o = off[3][so] + kk * Wd
+                    if Wp == Wd:
+                        gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward", out=out[b0:b1, o : o + Wd])
+                    else:
+                        out[b0:b1, o : o + Wd] = gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward")[:, :Wd]
+                del Z, Z3
+        return out
+
+    def map_w(self, x1, x2, g):
+        """dPhi/dw: per path  gW[(u,v), w] = sum_(z,k) Z[(z,k),(u,v)] g[z, k, w]  (reduction over rows)."""
+        from .dense import gemm_f32x3_tn
+
+        d, off = self.d, self.offsets
+        B, dev = x1.shape[0], x1.device
+        gw = torch.zeros((1, d.operands[0].size), dtype=torch.float32, device=dev)
+        for k, p in enumerate(d.paths):
+            sw, _, _, so = p.indices
+            U, V, Wd = d.operands[0].segments[sw]
+            d3 = p.coefficients.shape[2]
+            K = self._pad32(U * V)
+            Wp = -(-Wd // 4) * 4
+            acc = torch.zeros((K, Wp), dtype=torch.float32, device=dev)
+            step = self._chunk(B, d3 * K)
+            for b0 in range(0, B, step):
+                b1 = min(B, b0 + step)
+                Z = (torch.zeros if K != U * V else torch.empty)(((b1 - b0) * d3, K), dtype=torch.float32, device=dev)
+                self._build_f32(k, x1[b0:b1], x2[b0:b1], Z, K, 0)
+                Z3 = Z.view(b1 - b0, d3, K)
+                for kk in range(d3):
+                    o = off[3][so] + kk * Wd
+                    gk = g[b0:b1, o : o + Wd]
+                    if Wp != Wd:
+                        gk = torch.nn.functional.pad(gk, (0, Wp - Wd))
+                    gemm_f32x3_tn(Z3[:, kk, :], gk, name="fctp_f32_gw", out=acc)
+                del Z, Z3
+            gw[0, off[0][sw] : off[0][sw] + U * V * Wd] = acc[: U * V, :Wd].reshape(-1)
+        return gw
+
+    def map_x(self, w, x1, x2, g):
+        """(dPhi/dx1, dPhi/dx2): per path gZ = g W^T by one GEMM per component, folded against the other operand."""
+        import ctypes as C
+
+        from . import _lib, profiling
+        from .dense import gemm_f32x3
+
+        d, off = self.d, self.offsets
+        B, dev = x1.shape[0], x1.device
+        gx1 = torch.zeros(x1.shape, dtype=torch.float32, device=dev)
+        gx2 = torch.zeros(x2.shape, dtype=torch.float32, device=dev)
+        for k, p in enumerate(d.paths):
+            sw, _, _, so = p.indices
+            U, V, Wd = d.operands[0].segments[sw]
+            d3 = p.coefficients.shape[2]
+            N = -(-U * V // 4) * 4
+            Kw = self._pad32(Wd)
+            Wk = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd)
+            if Kw != Wd or N != U * V:
+                Wk = torch.nn.functional.pad(Wk, (0, Kw - Wd, 0, N - U * V))
+            Wk = Wk.contiguous()
+            step = self._chunk(B, d3 * N)
+            for b0 in range(0, B, step):
+                b1 = min(B, b0 + step)
+                gZ = torch.empty(((b1 - b0) * d3, N), dtype=torch.float32, device=dev)
+                gZ3 = gZ.view(b1 - b0, d3, N)
+                for kk in range(d3):
+                    o = off[3][so] + kk * Wd
+                    gk = g[b0:b1, o : o + Wd]
+                    if Kw != Wd:
+                        gk = torch.nn.functional.pad(gk, (0, Kw - Wd))
+                    gemm_f32x3(gk, Wk, name="fctp_f32_gx", out=gZ3[:, kk, :])
+                a = self._fctp_args(k, x1[b0:b1], x2[b0:b1], b1 - b0)
+                a.z, a.z_dtype, a.ldz = gZ.data_ptr(), _lib.F32, N
+                a.gx1, a.gx2 = gx1[b0:b1].data_ptr(), gx2[b0:b1].data_ptr()
+                with profiling.kernel("fctp_consume_gz"):
+                    _lib.check(_lib.lib().cueq_b200_fctp_consume_gz(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                del gZ, gZ3
+        return gx1, gx2
+
+
+# The fully connected product is linear in each of (w, x1, x2); with Phi(w, x1, x2, g) = <g, F(w, x1, x2)> every
+# derivative of every order is one of four contractions of Phi with three of its arguments: F itself and the
+# partial derivatives of Phi with respect to w, x1 and x2.  Each is a function below whose backward is made of
+# the others, so the float32 dense route is differentiable to any order on this library's kernels alone.
+class _DenseOut(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, owner, w, x1, x2):
+        ctx.owner = owner
+        ctx.save_for_backward(w, x1, x2)
+        return owner.map_out(w.detach(), x1.detach(), x2.detach())
+
+    @staticmethod
+    def backward(ctx, g):
+        w, x1, x2 = ctx.saved_tensors
+        g = g.contiguous()
+        gw = _DenseGw.apply(ctx.owner, x1, x2, g) if ctx.needs_input_grad[1] else None
+        gx1 = gx2 = None
+        if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+            gx1, gx2 = _DenseGx.apply(ctx.owner, w, x1, x2, g)
+        return None, gw, gx1 if ctx.needs_input_grad[2] else None, gx2 if ctx.needs_input_grad[3] else None
+
+
+class _DenseGw(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, owner, x1, x2, g):
+        ctx.owner = owner
+        ctx.save_for_backward(x1, x2, g)
+        return owner.map_w(x1.detach(), x2.detach(), g.detach())
+
+    @staticmethod
+    def backward(ctx, tw):
+        x1, x2, g = ctx.saved_tensors
+        tw = tw.contiguous()
+        gx1 = gx2 = gg = None
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            gx1, gx2 = _DenseGx.apply(ctx.owner, tw, x1, x2, g)
+        if ctx.needs_input_grad[3]:
+            gg = _DenseOut.apply(ctx.owner, tw, x1, x2)
+        return None, gx1 if ctx.needs_input_grad[1] else None, gx2 if ctx.needs_input_grad[2] else None, gg
+
+
+class _DenseGx(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, owner, w, x1, x2, g):
+        ctx.owner = owner
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(w, x1, x2, g)
+        return owner.map_x(w.detach(), x1.detach(), x2.detach(), g.detach())
+
+    @staticmethod
+    def backward(ctx, t1, t2):
+        w, x1, x2, g = ctx.saved_tensors
+        owner = ctx.owner
+        need_w, need_1, need_2, need_g = ctx.needs_input_grad[1:5]
+        gw = g1 = g2 = gg = None
+
+        def add(a, b):
+            return b if a is None else (a if b is None else a + b)
+
+        if t1 is not None:          # <t1, dPhi/dx1(w, x2, g)> = Phi(w, t1, x2, g)
+            t1 = t1.contiguous()
+            if need_w:
+                gw = add(gw, _DenseGw.apply(owner, t1, x2, g))
+            if need_2:
+                g2 = add(g2, _DenseGx.apply(owner, w, t1, x2, g)[1])
+            if need_g:
+                gg = add(gg, _DenseOut.apply(owner, w, t1, x2))
+        if t2 is not None:          # <t2, dPhi/dx2(w, x1, g)> = Phi(w, x1, t2, g)
+            t2 = t2.contiguous()
+            if need_w:
+                gw = add(gw, _DenseGw.apply(owner, x1, t2, g))
+            if need_1:
+                g1 = add(g1, _DenseGx.apply(owner, w, x1, t2, g)[0])
+            if need_g:
+                gg = add(gg, _DenseOut.apply(owner, w, x1, t2))
+        return None, gw, g1, g2, gg

@@ -71,6 +71,11 @@ typedef struct {
 } cueq_buffer;
 
 int cueq_b200_abi_version(void);
+/* One asynchronous device-to-device copy on `stream` (cudaMemcpyAsync); dst or src may be memory of
+ * another GPU of the node mapped into this process.  Used for the exchange of node features between
+ * the ranks of a receiver-sharded product, which then needs no SM.  The reference has no multi-GPU
+ * code; there is no counterpart. */
+int cueq_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 const char* cueq_b200_last_error(void);
 /* sizeof() of an argument block as this library was compiled, so that a binding can check its own
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
@@ -251,12 +256,13 @@ int cueq_b200_gemm_f32x3_tn(const cueq_gemm_f32x3_tn_args* args, void* stream);
  * cuequivariance/group_theory/descriptors/irreps_tp.py:22-91; module forward at
  * cuequivariance_torch/operations/tp_fully_connected.py:166-207) with coupling tensor cg[i][j][k]
  * (host array, d1*d2*d3 floats, normalisation included):
- *   build_z   : Z[(z,k), (u,v)] = sum_ij cg[i,j,k] x1[z, off1 + i*U + u] x2[z, off2 + j*V + v]   (bf16, [batch*d3, U*V])
+ *   build_z   : Z[(z,k), (u,v)] = sum_ij cg[i,j,k] x1[z, off1 + i*U + u] x2[z, off2 + j*V + v]   ([batch*d3, U*V], bf16 or float32)
  *   consume_gz: gx1[z, off1 + i*U + u] += sum_jkv cg[i,j,k] gZ[(z,k),(u,v)] x2[...]
  *               gx2[z, off2 + j*V + v] += sum_iku cg[i,j,k] gZ[(z,k),(u,v)] x1[...]
  * x1/x2 are float32 or bf16 (x_dtype), component-major (ir_mul) rows of pitch ld1/ld2; gx1/gx2
- * are float32 with the same pitches (either may be NULL); z is the bf16 output of build_z or the
- * gZ input (float32 or bf16, z_dtype) of consume_gz. */
+ * are float32 with the same pitches (either may be NULL); z is the output of build_z or the gZ
+ * input of consume_gz (float32 or bf16, z_dtype), rows `ldz` elements apart: a block of columns of a
+ * wider matrix when the paths that feed one output irrep are contracted by a single GEMM. */
 typedef struct {
   const void* x1;
   const void* x2;
@@ -268,7 +274,7 @@ typedef struct {
   int32_t off1, off2;
   int32_t d1, d2, d3, U, V;
   int32_t x_dtype, z_dtype;
-  int32_t reserved;
+  int32_t ldz;          /* row pitch of z in elements; 0 = U*V */
 } cueq_fctp_args;
 int cueq_b200_fctp_build_z(const cueq_fctp_args* args, void* stream);
 int cueq_b200_fctp_consume_gz(const cueq_fctp_args* args, void* stream);

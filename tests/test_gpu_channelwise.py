@@ -56,7 +56,7 @@ def _grads(fn, xs, cot, mask=(True, True, True)):
 @pytest.mark.parametrize("layout", [cb.mul_ir, cb.ir_mul])
 @pytest.mark.parametrize("mul,irreps1", [(4, "l2"), (32, "l3"), (128, "l3"), (256, "l2")])
 @pytest.mark.parametrize("sorted_receivers", [True, False])
-@pytest.mark.parametrize("cpl,staging,variant", [(2, 0, 1), (4, 0, 1), (2, 1, 1), (4, 1, 1), (0, 0, 2), (0, 0, 0)])  # variant: forward and backward
+@pytest.mark.parametrize("cpl,staging,variant", [(2, 0, 1), (4, 0, 1), (2, 1, 1), (4, 1, 1), (0, 0, 2), (0, 0, 3), (0, 0, 0)])  # variant: forward and backward
 def test_channelwise_kernels_match_oracle(layout, mul, irreps1, sorted_receivers, cpl, staging, variant, monkeypatch):
     from cuequivariance_b200 import channelwise
 

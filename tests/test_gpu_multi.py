@@ -1,6 +1,8 @@
-"""Two-GPU parity of the receiver-sharded channelwise product (pipelined all-gather /
-reduce-scatter path and the plain path) against the single-GPU call.  Skipped on boxes with
-fewer than two GPUs."""
+"""Two-GPU parity of the receiver-sharded channelwise product against the single-GPU call: the
+pipelined path with the rows moved by the copy engines over peer-mapped buffers, the same path
+with NCCL all-gather / reduce-scatter, and the plain path.  Every variant runs three steps in a
+row (the exchange buffers are reused from step to step).  Skipped on boxes with fewer than two
+GPUs."""
 import os
 import socket
 import sys
@@ -28,6 +30,7 @@ def _worker(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         import cuequivariance_b200 as cb
+        from cuequivariance_b200 import distributed
         from cuequivariance_b200.distributed import ReceiverShardedChannelWise, shard_bounds, shard_edges
 
         s1 = "32x0e+32x1o+32x2e+32x3o"
@@ -51,15 +54,20 @@ def _worker(rank, world, port, results):
         lo, hi = shard_bounds(N, world, rank)
         e0, e1 = shard_edges(rcv, N, world, rank)
         ok = True
-        for pipelined in (True, False):
+        for pipelined, exchange in ((True, "peer_copy"), (True, "nccl"), (False, "nccl")):
+            distributed.EXCHANGE = exchange
             op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD, pipelined=pipelined)
-            got = grads(lambda a, b, c: op(a, b, c, snd[e0:e1].contiguous(), (rcv[e0:e1] - lo).contiguous()),
-                        x1[lo:hi], x2[e0:e1], w[e0:e1], cot[lo:hi])
-            want = [ref[0][lo:hi], ref[1][lo:hi], ref[2][e0:e1], ref[3][e0:e1]]
-            for g_, w_ in zip(got, want):
-                scale = max(1.0, float(w_.abs().max()))
-                ok = ok and bool(((g_ - w_).abs() <= 1e-4 * w_.abs() + 2e-5 * scale).all())
-        results[rank] = ok
+            for step in range(3):
+                scale_in = 1.0 + step    # different data every step: a stale buffer would show
+                got = grads(lambda a, b, c: op(a, b, c, snd[e0:e1].contiguous(), (rcv[e0:e1] - lo).contiguous()),
+                            scale_in * x1[lo:hi], x2[e0:e1], w[e0:e1], cot[lo:hi])
+                want = [scale_in * ref[0][lo:hi], ref[1][lo:hi], scale_in * ref[2][e0:e1], scale_in * ref[3][e0:e1]]
+                for g_, w_ in zip(got, want):
+                    scale = max(1.0, float(w_.abs().max()))
+                    ok = ok and bool(((g_ - w_).abs() <= 1e-4 * w_.abs() + 2e-5 * scale).all())
+            if pipelined and exchange == "peer_copy":
+                ok = ok and any(bool(v) for v in distributed._EXCHANGES.values())   # the peer-copy exchange was really set up
+        results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
