@@ -317,7 +317,6 @@ def main():
     ap.add_argument("--nccl-ctas", type=int, default=0, help="N>1: upper bound on the thread blocks of a collective (0: NCCL's choice)")
     ap.add_argument("--sender-passes", type=int, default=None, help="backward: sender-range passes (1 = off)")
     ap.add_argument("--staging", type=int, default=None, help="forward staging: 0 = cp.async per lane, 1 = bulk copies")
-    ap.add_argument("--fwd-variant", type=int, default=None, help="forward kernels: 1 = one warp per receiver, 2 = a pair of warps per receiver")
     ap.add_argument("--bwd-variant", type=int, default=None, help="backward kernels: 1 = one warp per receiver, 2 = one thread block per receiver")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -359,10 +358,6 @@ def main():
         from cuequivariance_b200 import channelwise
 
         channelwise.BWD_VARIANT = args.bwd_variant
-    if args.fwd_variant is not None:
-        from cuequivariance_b200 import channelwise
-
-        channelwise.FWD_VARIANT = args.fwd_variant
     if args.bundles is not None:
         from cuequivariance_b200 import distributed
 

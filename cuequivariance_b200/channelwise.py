@@ -127,7 +127,6 @@ SENDER_PASSES = 1  # backward: visit the edges in this many sender-range passes 
 STAGING = 0  # forward kernels: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) signalled on an mbarrier
 CHANNELS_PER_LANE = 0  # 0: the library chooses; 2 or 4 force a variant (used by the tests)
 BWD_VARIANT = 0  # backward kernels: 0 = the library chooses, 1 = one warp per receiver, 2 = one thread block per receiver
-FWD_VARIANT = 0  # forward kernels: 0 = the library chooses, 1 = one warp per receiver, 2 = a pair of warps per receiver
 _IDENTITY_ROWPTR: dict = {}
 
 
@@ -355,7 +354,7 @@ class _ChannelwiseBase:
         # (config 3: forward 0.58 -> 0.46 ms, backward 1.15 -> 1.00 ms; every other group is slower with four)
         a.channels_per_lane = CHANNELS_PER_LANE or (4 if g.get("l1") == 0 and plan.extent % 128 == 0 else 0)
         a.staging = STAGING if which == "fwd_tab" else 0
-        a.variant = BWD_VARIANT if which == "bwd_tab" else FWD_VARIANT
+        a.variant = BWD_VARIANT if which == "bwd_tab" else 0
         if a.staging:
             a.status = _lib.status_word(tensors["w"].device).data_ptr()
         return a, tmpl[1]

@@ -585,10 +585,6 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
 // global memory anyway (x1 gradient).  A thread that owns four channels reads each broadcast
 // entry of the per-edge matrices, issues each copy and computes each address once for four
 // channels instead of two.
-// DIRECT_W: the weight segments do not pass through shared memory; the four weights a thread needs
-// for a path are loaded straight into registers while the previous path is being computed (and
-// those of the first path of the warp's next edge during the last path), which shrinks the edge
-// stages by almost half, so that a fourth block fits on an SM.
 template <class G, int C, int P, bool MUL_IR>
 struct StageGSplit {
   // the rows of the cotangent blocks are dealt round-robin to the warps of the block
@@ -606,53 +602,12 @@ struct StageGSplit {
   }
 };
 
-__device__ __forceinline__ void ldg_stream(float (&v)[4], const float* src, unsigned long long pol) {
-  asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;\n"
-               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(src), "l"(pol));
-}
-
-// x2 row and gathered x1 block of edge `pos` -> stage (no weights); returns the edge id
-template <class G, int C, bool X1_MUL_IR>
-__device__ __forceinline__ int issue_edge_x(const CwParams& p, float* st, int pos, int ch, int lane, bool active,
-                                            unsigned long long pol_stream, unsigned long long pol_keep) {
-  const int eid = p.order ? __ldg(p.order + pos) : pos;
-  if (lane < (G::NX2 + 3) / 4) cp_async_hint<16>(st + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane, pol_stream);
-  if (active) {
-    const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-    stage_block_hint<G::D1, C, X1_MUL_IR>(reinterpret_cast<Vec<C>*>(st + 16), p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, lane, pol_keep);
-  }
-  cp_async_commit();
-  return eid;
-}
-
-// like BwdPaths, with the weights of path P in registers and those of the following path on their way
-template <class G, int P, bool MUL_IR>
-struct BwdPathsW {
-  __device__ __forceinline__ static void run(const float (&X)[G::D1][4], float (&W)[4], const float* wrow, const float* wrow_next,
-                                             const float4* grow, int lane, const float* M, const CwCoef& coef, const CwParams& p,
-                                             float* gwrow, float (&gX)[G::D1][4], float (&r)[16], unsigned long long pol) {
-    float Wn[4] = {0.f, 0.f, 0.f, 0.f};
-    if constexpr (P + 1 < G::NPATH) ldg_stream(Wn, wrow + p.w_off[P + 1], pol);
-    else if (wrow_next) ldg_stream(Wn, wrow_next + p.w_off[0], pol);
-    float Gk[G::MAXD3][4];
-    unstage_block<G::d3(P), 4, MUL_IR>(grow + G::out_offset(P) * 32, lane, Gk);
-    float gw[4];
-    G::template bwd_path<P, 4>(X, W, M, Gk, coef, gX, gw, r);
-    if (p.need_gw) st_stream(gwrow + p.w_off[P], gw);
-    if constexpr (P + 1 < G::NPATH) BwdPathsW<G, P + 1, MUL_IR>::run(X, Wn, wrow, wrow_next, grow, lane, M, coef, p, gwrow, gX, r, pol);
-    // on the way out every level hands the array it received from below to its caller: after the last path it
-    // holds the weights of the first path of the warp's next edge
-#pragma unroll
-    for (int c = 0; c < 4; ++c) W[c] = Wn[c];
-  }
-};
-
-template <class G, bool MUL_IR, bool DIRECT_W>
-__global__ void __launch_bounds__(kWarps * 32, DIRECT_W ? 4 : 3) cw_bwd_block_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
+template <class G, bool MUL_IR>
+__global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
   constexpr int C = 4;
   extern __shared__ __align__(16) float smem[];
   using S = Smem<G, C>;
-  constexpr int kStage = DIRECT_W ? 16 + G::D1 * 32 * C : S::kPerStage;
+  constexpr int kStage = S::kPerStage;
   constexpr int kPerWarp = S::kM + 2 * kStage;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   Vec<C>* grow = reinterpret_cast<Vec<C>*>(smem);                 // shared by the block
@@ -674,27 +629,15 @@ __global__ void __launch_bounds__(kWarps * 32, DIRECT_W ? 4 : 3) cw_bwd_block_ke
     cp_async_commit();
     int pos = beg + warp;
     int eid = 0, eid_next = 0;
-    float Wcur[4] = {0.f, 0.f, 0.f, 0.f};
-    if (pos < end) {
-      if constexpr (DIRECT_W) {
-        eid_next = issue_edge_x<G, C, MUL_IR>(p, stages, pos, ch, lane, active, pol_stream, pol_keep);
-        if (active) ldg_stream(Wcur, p.w + (int64_t)eid_next * p.w_stride + ch + p.w_off[0], pol_stream);
-      } else {
-        eid_next = issue_edge<G, C, MUL_IR>(p, stages, pos, ch, lane, active, pol_stream, pol_keep);
-      }
-    } else {
-      cp_async_commit();
-    }
+    if (pos < end) eid_next = issue_edge<G, C, MUL_IR>(p, stages, pos, ch, lane, active, pol_stream, pol_keep);
+    else cp_async_commit();
     cp_async_wait<1>();                                            // this thread's share of the cotangent row has landed
     __syncthreads();                                               // ... and everybody else's
     for (int it = 0; pos < end; pos += kWarps, ++it) {
       float* st = stages + (it & 1) * kStage;
       eid = eid_next;
-      const bool more = pos + kWarps < end;
-      if (more) {
-        float* nst = stages + ((it + 1) & 1) * kStage;
-        if constexpr (DIRECT_W) eid_next = issue_edge_x<G, C, MUL_IR>(p, nst, pos + kWarps, ch, lane, active, pol_stream, pol_keep);
-        else eid_next = issue_edge<G, C, MUL_IR>(p, nst, pos + kWarps, ch, lane, active, pol_stream, pol_keep);
+      if (pos + kWarps < end) {
+        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, pos + kWarps, ch, lane, active, pol_stream, pol_keep);
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
@@ -713,14 +656,7 @@ __global__ void __launch_bounds__(kWarps * 32, DIRECT_W ? 4 : 3) cw_bwd_block_ke
         for (int i = 0; i < G::D1; ++i)
 #pragma unroll
           for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
-        float* gwrow = p.gw + (int64_t)eid * p.w_stride + ch;
-        if constexpr (DIRECT_W) {
-          const float* wrow = p.w + (int64_t)eid * p.w_stride + ch;
-          const float* wrow_next = more ? p.w + (int64_t)eid_next * p.w_stride + ch : nullptr;
-          BwdPathsW<G, 0, MUL_IR>::run(X, Wcur, wrow, wrow_next, grow, lane, Msm, coef, p, gwrow, gX, r, pol_stream);
-        } else {
-          BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, gwrow, gX, r);
-        }
+        BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
           const int snd = p.senders ? __ldg(p.senders + eid) : eid;
           emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
@@ -743,7 +679,7 @@ struct GroupEntry {
   int (*fwd)(const CwParams&, int, int, cudaStream_t);
   int (*bwd)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
   int (*fwd_bulk)(const CwParams&, int, int, cudaStream_t);
-  int (*bwd_block)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
+  int (*bwd_block)(const CwParams&, const CwCoef&, int, cudaStream_t);
 };
 
 int grid_x(int num_receivers) {
@@ -812,27 +748,25 @@ int launch_bwd(const CwParams& p, const CwCoef& coef, int mul_ir, int cpl, cudaS
   return mul_ir ? launch_bwd_t<G, 4, true>(p, coef, st) : launch_bwd_t<G, 4, false>(p, coef, st);
 }
 
-template <class G, bool A, bool DIRECT_W>
+template <class G, bool A>
 int launch_bwd_block_t(const CwParams& p, const CwCoef& coef, cudaStream_t st) {
   using S = Smem<G, 4>;
-  const size_t stage = DIRECT_W ? 16 + G::D1 * 128 : S::kPerStage;
-  const size_t smem = sizeof(float) * (S::kGrow + kWarps * (S::kM + 2 * stage));
+  const size_t smem = sizeof(float) * (S::kGrow + kWarps * S::kPerWarpFwd);
   static cueq::PerDeviceFlag configured;
   if (!configured.get()) {
-    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_block_kernel<G, A, DIRECT_W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_block_kernel<G, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured.set();
   }
   const int cap = 148 * 24;
   dim3 grid(p.num_receivers < cap ? p.num_receivers : cap, (p.extent + 127) / 128);
-  cw_bwd_block_kernel<G, A, DIRECT_W><<<grid, kWarps * 32, smem, st>>>(p, coef);
+  cw_bwd_block_kernel<G, A><<<grid, kWarps * 32, smem, st>>>(p, coef);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 template <class G>
-int launch_bwd_block(const CwParams& p, const CwCoef& coef, int mul_ir, int direct_w, cudaStream_t st) {
-  if (direct_w) return mul_ir ? launch_bwd_block_t<G, true, true>(p, coef, st) : launch_bwd_block_t<G, false, true>(p, coef, st);
-  return mul_ir ? launch_bwd_block_t<G, true, false>(p, coef, st) : launch_bwd_block_t<G, false, false>(p, coef, st);
+int launch_bwd_block(const CwParams& p, const CwCoef& coef, int mul_ir, cudaStream_t st) {
+  return mul_ir ? launch_bwd_block_t<G, true>(p, coef, st) : launch_bwd_block_t<G, false>(p, coef, st);
 }
 
 #define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, &launch_fwd<G>, &launch_bwd<G>, &launch_fwd_bulk<G>, &launch_bwd_block<G>},
@@ -898,7 +832,7 @@ extern "C" int cueq_b200_cw_forward(int g, const cueq_cw_args* a, void* stream) 
   if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise forward: null tensor");
   if (p.num_receivers == 0) return 0;
   p.status = reinterpret_cast<int*>(a->status);
-  if (a->variant < 0 || a->variant > 3) return cueq::fail("channelwise forward: variant must be 0 (automatic), 1, 2 or 3");
+  if (a->variant < 0 || a->variant > 2) return cueq::fail("channelwise: variant must be 0 (automatic), 1 or 2");
   if (a->staging == 1) return kGroups[g].fwd_bulk(p, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
   return kGroups[g].fwd(p, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
@@ -915,11 +849,11 @@ extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream)
   CwCoef coef;
   std::memset(&coef, 0, sizeof(coef));
   for (int t = 0; t < kGroups[g].nterm; ++t) coef.c[t] = a->bwd_coef[t];
-  if (a->variant < 0 || a->variant > 3) return cueq::fail("channelwise backward: variant must be 0 (automatic), 1, 2 or 3");
+  if (a->variant < 0 || a->variant > 2) return cueq::fail("channelwise backward: variant must be 0 (automatic), 1 or 2");
   // one thread block per receiver needs the four-channel layout (extent a multiple of 4 is given);
   // it is the default from 128 channels on, where a warp's 128 channels are all in use
-  const bool block_per_receiver = a->variant >= 2 || (a->variant == 0 && a->channels_per_lane != 2 && a->extent % 128 == 0);
-  if (block_per_receiver) return kGroups[g].bwd_block(p, coef, a->x1_mul_ir, a->variant == 3, reinterpret_cast<cudaStream_t>(stream));
+  const bool block_per_receiver = a->variant == 2 || (a->variant == 0 && a->channels_per_lane != 2 && a->extent % 128 == 0);
+  if (block_per_receiver) return kGroups[g].bwd_block(p, coef, a->x1_mul_ir, reinterpret_cast<cudaStream_t>(stream));
   return kGroups[g].bwd(p, coef, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -77,16 +77,6 @@ def emit_group(l1: int, paths) -> str:
     A(f"  static constexpr int SUMD3 = {out_off[-1]};")
     A(f"  static constexpr int MAXD3 = {max(d3s)};")
     A(f"  static constexpr int NX2 = {max(l2 for l2, _ in paths) ** 2 + 2 * max(l2 for l2, _ in paths) + 1};")
-    # two halves of the group with about the same number of multiply-adds: the forward kernel that
-    # gives a receiver to a pair of warps lets each warp compute the output blocks of one half
-    cost = [len(pt) + min(d1, dd) for pt, dd in zip(pats, d3s)]
-    best = min(range(1, 2 ** len(paths) - 1), key=lambda msk: (abs(sum(c for q, c in enumerate(cost) if msk >> q & 1) * 2 - sum(cost)), msk)) \
-        if len(paths) > 1 else 0
-    half = [best >> q & 1 for q in range(len(paths))]
-    slot = [sum(1 for r in range(q) if half[r] == half[q]) for q in range(len(paths))]
-    A("  __host__ __device__ static constexpr int half_of(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, half)))
-    A("  __host__ __device__ static constexpr int slot_of(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, slot)))
-    A(f"  static constexpr int HALF_PATHS = {max(half.count(0), half.count(1))};")
     A("  static constexpr const char* signature() { return \"%s\"; }" % group_signature(l1, paths))
     A("  __host__ __device__ static constexpr int d3(int p) { constexpr int t[NPATH] = {%s}; return t[p]; }" % ", ".join(map(str, d3s)))
     A("  __host__ __device__ static constexpr int out_offset(int p) { constexpr int t[NPATH + 1] = {%s}; return t[p]; }" % ", ".join(map(str, out_off)))

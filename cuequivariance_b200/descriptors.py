@@ -244,15 +244,47 @@ def spherical_harmonics(ir_vec, ls: Sequence[int], layout=ir_mul) -> Equivariant
 # ---------------------------------------------------------------------------------------
 # symmetric contraction (MACE): tables generated from the reference, see data/
 # ---------------------------------------------------------------------------------------
-def symmetric_contraction(irreps_in, irreps_out, degrees: Sequence[int]):
+def _symmetric_contraction_degree(irreps_in: Irreps, irreps_out: Irreps, degree: int, mul: int) -> Polynomial:
+    """One degree of the symmetric contraction built from this package's own symmetric-power basis:
+    ``w_a_b_.._i+ab..iw`` with one path per output irrep carrying ``U[a, b, .., i, w]``, normalised for the
+    output, coefficient modes flattened, and the channel mode ``u`` appended to every operand (the
+    construction of cuequivariance/group_theory/descriptors/symmetric_contractions.py:47-88)."""
+    from .stp import Path
+    from .symmetric_basis import symmetric_power_basis
+
+    blocks = [ir for _, ir in irreps_in]
+    letters = "abcdefgh"[:degree]
+    d = SegmentedTensorProduct.from_subscripts("w," + ",".join(letters) + ",i+" + letters + "iw")
+    for k in range(1, degree + 1):
+        d.add_segment(k, (irreps_in.set_mul(1).dim,))
+    for _, ir in irreps_out:
+        U = symmetric_power_basis(blocks, degree, ir)
+        if U.shape[-1] == 0:
+            d.add_segment(degree + 1, (ir.dim,))
+        else:
+            d.add_path(None, *(0,) * degree, None, c=U)
+    d = d.normalize_paths_for_operand(-1).flatten_coefficient_modes()
+    # every operand is now a list of scalar segments: give each the channel axis
+    operands = [Operand(1, ((mul,),) * op.num_segments) for op in d.operands]
+    du = SegmentedTensorProduct(("u",) * len(operands), "", operands, [Path(p.indices, p.coefficients) for p in d.paths])
+    return Polynomial([operands[0], operands[1]], [operands[-1]], [(Operation((0,) + (1,) * degree + (2,)), du)])
+
+
+def symmetric_contraction(irreps_in, irreps_out, degrees: Sequence[int], basis: str = "auto"):
     """``weights[u], input[u] (x degree) -> output[u]`` for each degree in ``degrees``
     (which must be ``1..n``).  Returns ``(EquivariantPolynomial, projection)`` like the
     reference's ``experimental.mace.symmetric_contraction``; ``projection`` maps original-MACE
     weights to this basis.
 
-    The change of basis to symmetric irreps is not unique, so the path tables are the
-    reference's own, stored under ``cuequivariance_b200/data`` for input irreps
-    ``0e[+1o[+2e[+3o]]]``, output ``0e[+1o[+2e]]`` and degree up to 3 (any multiplicity).
+    The basis of the symmetric powers is not unique (any invertible mixing of the weights gives another
+    valid one).  ``basis``:
+
+    * ``"reference"``: the reference's own path tables, shipped under ``cuequivariance_b200/data`` for
+      input irreps ``0e[+1o[+2e[+3o]]]``, output ``0e[+1o[+2e]]`` and degree up to 3 (any multiplicity), so
+      that weights trained with the reference keep their meaning;
+    * ``"constructed"``: this package's own basis (``symmetric_basis.symmetric_power_basis``), for any
+      O3/SO3 irreps and degree; the projection from original-MACE weights is not available (``None``);
+    * ``"auto"``: the table when there is one, else the constructed basis.
     """
     import os
 
@@ -265,14 +297,25 @@ def symmetric_contraction(irreps_in, irreps_out, degrees: Sequence[int]):
     if len(muls) != 1:
         raise ValueError("Input/Output irreps must have the same mul")
     (mul,) = muls
+    if basis not in ("auto", "reference", "constructed"):
+        raise ValueError("basis must be 'auto', 'reference' or 'constructed'")
     key_in = "_".join(repr(ir) for _, ir in irreps_in)
     key_out = "_".join(repr(ir) for _, ir in irreps_out)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", f"sc__{key_in}__{key_out}__deg{len(degrees)}.npz")
+    if basis == "constructed" or (basis == "auto" and not os.path.exists(path)):
+        polys = [_symmetric_contraction_degree(irreps_in, irreps_out, deg, mul) for deg in degrees]
+        poly = Polynomial.stack(polys, [True, False, False])
+        e = EquivariantPolynomial(
+            (IrrepsAndLayout(irreps_in.new_scalars(poly.inputs[0].size), ir_mul), IrrepsAndLayout(irreps_in, ir_mul)),
+            (IrrepsAndLayout(irreps_out, ir_mul),),
+            poly,
+        )
+        return e, None
     if not os.path.exists(path):
         raise NotImplementedError(
-            f"no symmetric-contraction table for {irreps_in} -> {irreps_out} degree {len(degrees)}; "
+            f"no reference table for {irreps_in} -> {irreps_out} degree {len(degrees)}; "
             "tables exist for inputs 0e[+1o[+2e[+3o]]], outputs 0e[+1o[+2e]], degree <= 3 "
-            "(data/make_symmetric_contraction_tables.py generates more from the reference)"
+            "(data/make_symmetric_contraction_tables.py generates more from the reference); basis='constructed' covers any shape"
         )
     t = np.load(path)
     nseg = [int(n) for n in t["num_segments"]]

@@ -72,6 +72,86 @@ class _DenseLinear(torch.autograd.Function):
         return None, gw, gx
 
 
+_BOUNDS: list = []   # small cache: (index tensor, version, classes) -> row ranges of the classes
+
+
+def class_bounds(indices: torch.Tensor, classes: int):
+    """Row ranges of the weight classes when ``indices`` is sorted ascending (``[classes + 1]`` python ints),
+    else None.  One device-to-host read, cached on the tensor's identity and version counter."""
+    for ref, ver, c, val in _BOUNDS:
+        if ref is indices and ver == indices._version and c == classes:
+            return val
+    idx = indices.contiguous()
+    edges = torch.searchsorted(idx, torch.arange(classes + 1, device=idx.device, dtype=idx.dtype))
+    ok = (idx[1:] >= idx[:-1]).all() if idx.numel() > 1 else torch.ones((), dtype=torch.bool, device=idx.device)
+    host = torch.cat([edges.to(torch.int64), ok.to(torch.int64).reshape(1)]).tolist()
+    val = host[:-1] if host[-1] else None
+    _BOUNDS.append((indices, indices._version, classes, val))
+    if len(_BOUNDS) > 8:
+        _BOUNDS.pop(0)
+    return val
+
+
+class _GroupedDenseLinear(torch.autograd.Function):
+    """Linear map with one weight set per class and rows sorted by class - the counterpart of the reference's
+    ``indexed_linear`` method (cuequivariance_torch/primitives/segmented_polynomial_indexed_linear.py:116-156,
+    247-339: sorted indices -> counts -> grouped GEMM): class ``c`` owns the contiguous rows
+    ``bounds[c] : bounds[c + 1]`` and gets its own GEMM against its own weight block.  Per irrep pair the ``d``
+    components of a row are folded into the row axis (``[Z, d, u] -> [Z * d, u]``), so one float32-accurate
+    tensor-core GEMM per (class, irrep pair) does the forward, one the input gradient and one (a reduction over
+    the class's rows) the weight gradient."""
+
+    @staticmethod
+    def forward(ctx, plan, bounds, weight, x):
+        from ..dense import gemm_f32x3
+
+        Z = x.shape[0]
+        out = torch.zeros((Z, plan["out_size"]), dtype=torch.float32, device=x.device)
+        for (wo, u, v, xo, oo, d, c) in plan["paths"]:
+            xp = x[:, xo : xo + d * u].reshape(Z * d, u)
+            wt = (weight[:, wo : wo + u * v].reshape(-1, u, v).transpose(1, 2) * c).contiguous()     # [class][N = v][K = u]
+            op = torch.zeros((Z * d, v), dtype=torch.float32, device=x.device)
+            for k in range(len(bounds) - 1):
+                r0, r1 = bounds[k] * d, bounds[k + 1] * d
+                if r1 > r0:
+                    gemm_f32x3(xp[r0:r1], wt[k], name="indexed_linear_f32x3", out=op[r0:r1])
+            out[:, oo : oo + d * v] += op.view(Z, d * v)
+        ctx.plan, ctx.bounds = plan, bounds
+        ctx.save_for_backward(weight, x)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gout):
+        from ..dense import gemm_f32x3, gemm_f32x3_tn
+
+        plan, bounds = ctx.plan, ctx.bounds
+        weight, x = ctx.saved_tensors
+        Z = x.shape[0]
+        gw = torch.zeros_like(weight) if ctx.needs_input_grad[2] else None
+        gx = torch.zeros_like(x) if ctx.needs_input_grad[3] else None
+        for (wo, u, v, xo, oo, d, c) in plan["paths"]:
+            gp = gout[:, oo : oo + d * v].reshape(Z * d, v)
+            if gx is not None:
+                wc = (weight[:, wo : wo + u * v].reshape(-1, u, v) * c).contiguous()                 # [class][N = u][K = v]
+                gxp = torch.zeros((Z * d, u), dtype=torch.float32, device=x.device)
+            if gw is not None:
+                xp = x[:, xo : xo + d * u].reshape(Z * d, u)
+            for k in range(len(bounds) - 1):
+                r0, r1 = bounds[k] * d, bounds[k + 1] * d
+                if r1 <= r0:
+                    continue
+                if gx is not None:
+                    gemm_f32x3(gp[r0:r1], wc[k], name="indexed_linear_f32x3_gx", out=gxp[r0:r1])
+                if gw is not None:
+                    acc = torch.zeros((u, v), dtype=torch.float32, device=x.device)
+                    gemm_f32x3_tn(xp[r0:r1], gp[r0:r1], out=acc, name="indexed_linear_f32x3_gw")
+                    gw[k, wo : wo + u * v] += (acc * c).reshape(-1)
+            if gx is not None:
+                gx[:, xo : xo + d * u] += gxp.view(Z, d * u)
+        return None, None, gw, gx
+
+
 class Linear(torch.nn.Module):
     """``forward(x, weight=None, weight_indices=None)``; ``x``: ``[batch, irreps_in.dim]``;
     ``weight``: ``[1 or weight_classes, weight_numel]`` when shared (the module's own parameter
@@ -119,8 +199,12 @@ class Linear(torch.nn.Module):
             self.weight = torch.nn.Parameter(torch.randn(weight_classes, self.weight_numel, device=device, dtype=dtype))
         else:
             self.weight = None
-        if method not in (None, "fused_tp"):
-            raise ValueError(f"method {method!r} is not available for Linear (only 'fused_tp')")
+        if method not in (None, "fused_tp", "indexed_linear"):
+            raise ValueError(f"method {method!r} is not available for Linear ('fused_tp' or 'indexed_linear')")
+        # "indexed_linear" (weight classes, rows sorted by class) insists on the grouped tensor-core GEMMs and
+        # raises where they do not apply; with the default the grouped route is taken when it applies and the
+        # generic kernel otherwise
+        self.require_grouped = method == "indexed_linear"
         self.method = "fused_tp"
         self.transpose_in = TransposeIrrepsLayout(irreps_in, source=IrrepsLayout.parse(layout_in or layout), target=e.inputs[1].layout, device=device)
         self.transpose_out = TransposeIrrepsLayout(irreps_out, source=e.outputs[0].layout, target=IrrepsLayout.parse(layout_out or layout), device=device)
@@ -166,6 +250,17 @@ class Linear(torch.nn.Module):
         if (self._dense_plan is not None and DENSE_ROUTE and not input_indices and weight.shape[0] == 1 and xin.is_cuda
                 and xin.dtype == torch.float32 and weight.dtype == torch.float32 and xin.shape[0] >= DENSE_MIN_ROWS):
             return self.transpose_out(_DenseLinear.apply(self._dense_plan, weight, xin.contiguous()))
+        if self._dense_plan is not None and DENSE_ROUTE and input_indices and xin.is_cuda and xin.dtype == torch.float32 \
+                and weight.dtype == torch.float32 and weight.shape[0] == self.weight_classes \
+                and (self.require_grouped or xin.shape[0] >= DENSE_MIN_ROWS):
+            bounds = class_bounds(weight_indices, self.weight_classes)
+            if bounds is not None:
+                return self.transpose_out(_GroupedDenseLinear.apply(self._dense_plan, bounds, weight, xin.contiguous()))
+            if self.require_grouped:
+                raise ValueError("Linear(method='indexed_linear') does not support non-sorted indices")
+        elif self.require_grouped:
+            raise ValueError("Linear(method='indexed_linear') needs float32 CUDA tensors, weight classes selected by sorted "
+                             "weight_indices and multiplicities that are multiples of 32")
         if self.f is None:
             raise ValueError("Linear: this shape runs only on the dense route (float32 CUDA tensors, one weight set, at least "
                              f"{DENSE_MIN_ROWS} rows); the generic kernel cannot take it: {self._generic_error}")

@@ -49,6 +49,9 @@ class SymmetricContraction(torch.nn.Module):
         self.contraction_degree = contraction_degree
         self.etp, p = descriptors.symmetric_contraction(irreps_in, irreps_out, tuple(range(1, contraction_degree + 1)))
         if original_mace:
+            if p is None:
+                raise NotImplementedError("original_mace=True needs the projection from original-MACE weights, which exists only "
+                                          "for the shapes with a reference table (inputs 0e[+1o[+2e[+3o]]], outputs 0e[+1o[+2e]], degree <= 3)")
             self.register_buffer("projection", torch.tensor(p, dtype=dtype, device=device))
             self.weight_shape = (p.shape[0], mul)
         else:

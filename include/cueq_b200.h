@@ -160,10 +160,9 @@ typedef struct {
   void* status;         /* nullable device int32: set to 1 if a bounded wait on a bulk copy ran out */
   int32_t recv_mod;     /* backward only: if > 0 the CSR has several rows per receiver (row r belongs to
                            receiver r % recv_mod), used to visit the edges in sender-range passes        */
-  int32_t variant;      /* 0 = the library chooses; 1 = one warp per receiver (2 or 4 channels per thread);
-                           2 = backward: one thread block per receiver (its warps share the staged cotangent
-                           row and split the receiver's edges), forward: a pair of warps per receiver (each
-                           accumulates half of the group's output blocks); four channels per thread          */
+  int32_t variant;      /* backward only: 0 = the library chooses; 1 = one warp per receiver (2 or 4 channels
+                           per thread); 2 = one thread block per receiver: its warps share the staged
+                           cotangent row and split the receiver's edges, four channels per thread          */
 } cueq_cw_args;
 
 int cueq_b200_cw_num_groups(void);

@@ -430,3 +430,45 @@ def test_modules_survive_a_pickle_round_trip():
     tp2 = pickle.loads(pickle.dumps(tp))
     a, b = torch.randn(5, tp.irreps_in1.dim, device=DEV), torch.randn(5, tp.irreps_in2.dim, device=DEV)
     assert torch.equal(tp(a, b), tp2(a, b))
+
+
+@pytest.mark.parametrize("method", [None, "indexed_linear"])
+def test_linear_weight_classes_on_grouped_gemms(method):
+    """`Linear` with one weight set per class and rows sorted by class (the reference's `indexed_linear`
+    situation, cuequivariance_torch/primitives/segmented_polynomial_indexed_linear.py:247-339): one float32-accurate
+    tensor-core GEMM per (class, irrep pair).  Output and first derivatives against the oracle with indexed
+    weights; unsorted indices take the generic kernel (default method) or raise (method="indexed_linear")."""
+    s_in, s_out = "64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"
+    classes, B = 5, 320
+    e = D.linear(s_in, s_out)
+    m = cb.Linear(s_in, s_out, layout=cb.ir_mul, internal_weights=False, shared_weights=True, weight_classes=classes, method=method)
+    gen = torch.Generator().manual_seed(78)
+    x = torch.randn(B, m.irreps_in.dim, generator=gen)
+    w = torch.randn(classes, m.weight_numel, generator=gen)
+    cot = torch.randn(B, m.irreps_out.dim, generator=gen)
+    idx = torch.sort(torch.randint(0, classes - 1, (B,), generator=gen)).values     # the last class owns no row
+
+    def grads(fn, xs, c):
+        xs = [t.clone().requires_grad_(True) for t in xs]
+        out = fn(*xs)
+        return [out.detach()] + list(torch.autograd.grad((out * c).sum(), xs))
+
+    ref = grads(lambda w_, x_: naive.segmented_polynomial(e.polynomial, [w_, x_], {0: idx})[0], [w, x], cot)
+    profiling.reset()
+    profiling.enable()
+    try:
+        got = grads(lambda w_, x_: m(x_, w_, weight_indices=idx.to(DEV)), [w.to(DEV), x.to(DEV)], cot.to(DEV))
+        names = set(profiling.summary())
+    finally:
+        profiling.enable(False)
+    assert {"indexed_linear_f32x3", "indexed_linear_f32x3_gx", "indexed_linear_f32x3_gw"} <= names, names
+    for name, a, b in zip(["out", "grad w", "grad x"], got, ref):
+        f = 1 if name == "out" else 10
+        _close(a, b, f * 1e-5, f * 2e-6, name)
+    shuffled = idx[torch.randperm(B, generator=gen)]
+    if method == "indexed_linear":
+        with pytest.raises(ValueError, match="non-sorted"):
+            m(x.to(DEV), w.to(DEV), weight_indices=shuffled.to(DEV))
+    else:
+        (ref2,) = naive.segmented_polynomial(e.polynomial, [w, x], {0: shuffled})
+        _close(m(x.to(DEV), w.to(DEV), weight_indices=shuffled.to(DEV)), ref2, 1e-5, 2e-6, "unsorted indices")
