@@ -313,6 +313,8 @@ def main():
     ap.add_argument("--edges", type=int, default=E_TOTAL, help="total edges (default: the named configuration)")
     ap.add_argument("--nodes", type=int, default=N_TOTAL)
     ap.add_argument("--cpl", type=int, default=0, help="force channels per lane (2 or 4) in the channelwise kernels; 0 = library default")
+    ap.add_argument("--exchange", default=None, choices=["peer_copy", "nccl"],
+                    help="N>1: how node rows travel between ranks (default: copy engines over peer-mapped buffers)")
     ap.add_argument("--bundles", type=int, default=None, help="N>1: exchanges per direction (0 = one per irrep, 1, 2)")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="N>1: upper bound on the thread blocks of a collective (0: NCCL's choice)")
     ap.add_argument("--sender-passes", type=int, default=None, help="backward: sender-range passes (1 = off)")
@@ -358,6 +360,10 @@ def main():
         from cuequivariance_b200 import channelwise
 
         channelwise.BWD_VARIANT = args.bwd_variant
+    if args.exchange is not None:
+        from cuequivariance_b200 import distributed
+
+        distributed.EXCHANGE = args.exchange
     if args.bundles is not None:
         from cuequivariance_b200 import distributed
 

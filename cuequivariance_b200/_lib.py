@@ -72,6 +72,14 @@ class CwNoAllocArgs(C.Structure):
     ]
 
 
+class ShArgs(C.Structure):
+    _fields_ = [
+        ("vec", C.c_void_p), ("y", C.c_void_p), ("gvec", C.c_void_p),
+        ("rows", C.c_int64), ("ld_vec", C.c_int64), ("ld_y", C.c_int64), ("ld_gvec", C.c_int64),
+        ("ls_mask", C.c_uint32), ("normalize", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 class GemmArgs(C.Structure):
     _fields_ = [
         ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p),
@@ -198,6 +206,10 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_signature.restype = C.c_char_p
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
     L.cueq_b200_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.cueq_b200_enable_peer_access.argtypes = [C.c_int]
+    L.cueq_b200_sh_width.argtypes = [C.c_uint32]
+    L.cueq_b200_sh_forward.argtypes = [C.POINTER(ShArgs), C.c_void_p]
+    L.cueq_b200_sh_backward.argtypes = [C.POINTER(ShArgs), C.c_void_p]
     L.cueq_b200_cw_forward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_backward.argtypes = [C.c_int, C.POINTER(CwArgs), C.c_void_p]
     L.cueq_b200_cw_forward_noalloc.argtypes = [C.c_int, C.POINTER(CwNoAllocArgs), C.c_void_p]

@@ -41,7 +41,7 @@ def generate() -> None:
     """Regenerates csrc/generated/*.cuh (no-op when the text is unchanged)."""
     import importlib.util
 
-    for name in ("gen_cw_groups", "gen_u1d_static"):
+    for name in ("gen_cw_groups", "gen_u1d_static", "gen_sh"):
         spec = importlib.util.spec_from_file_location(name, CSRC / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)

@@ -23,6 +23,23 @@ extern "C" int cueq_b200_abi_version(void) { return CUEQ_B200_ABI_VERSION; }
 // One asynchronous copy between device pointers on `stream`; either side may be another GPU's memory
 // mapped into this process.  The driver serves it with a copy engine, so no SM is taken from the kernels
 // that run meanwhile.
+// Lets copies and kernels of the current device reach memory of `peer_device` directly (over NVLink where the
+// GPUs are linked).  Without it a copy between two devices is staged through host memory.  Idempotent.
+extern "C" int cueq_b200_enable_peer_access(int peer_device) {
+  int dev = -1, can = 0;
+  CUEQ_CUDA_OK(cudaGetDevice(&dev));
+  if (dev == peer_device) return 0;
+  CUEQ_CUDA_OK(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can) return cueq::fail("device %d cannot access device %d directly", dev, peer_device);
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();   // clear the sticky-free error state
+    return 0;
+  }
+  if (e != cudaSuccess) return cueq::fail("cudaDeviceEnablePeerAccess(%d) failed: %s", peer_device, cudaGetErrorString(e));
+  return 0;
+}
+
 extern "C" int cueq_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
   if (bytes == 0) return 0;
   if (!dst || !src) return cueq::fail("copy: null pointer");
@@ -46,6 +63,7 @@ extern "C" int64_t cueq_b200_sizeof(int which) {
     case 11: return sizeof(cueq_fctp_fused_wunit);
     case 12: return sizeof(cueq_gemm_f32x3_args);
     case 13: return sizeof(cueq_gemm_f32x3_tn_args);
+    case 14: return sizeof(cueq_sh_args);
     default: return -1;
   }
 }

@@ -234,9 +234,17 @@ class PeerExchange:
         self.flat = torch.empty(self.offsets[-1], dtype=torch.float32, device=device)
         handles = [None] * self.world
         dist.all_gather_object(handles, reduce_tensor(self.flat), group=group)
+        from . import _lib
+
         self.peers = []
         for r, (fn, args) in enumerate(handles):
-            self.peers.append(self.flat if r == self.rank else fn(*args))
+            if r == self.rank:
+                self.peers.append(self.flat)
+                continue
+            t = fn(*args)                 # the peer's buffer, mapped into this process (a tensor on the peer's device)
+            with torch.cuda.device(device):
+                _lib.check(_lib.lib().cueq_b200_enable_peer_access(t.device.index))
+            self.peers.append(t)
         nb = len(self.widths)
         self.x = [self._view(self.flat, l, n_local, self.widths[l]) for l in range(nb)]
         self.g = [self._view(self.flat, nb + l, n_all, self.widths[l]) for l in range(nb)]

@@ -76,13 +76,16 @@ int cueq_b200_abi_version(void);
  * the ranks of a receiver-sharded product, which then needs no SM.  The reference has no multi-GPU
  * code; there is no counterpart. */
 int cueq_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+/* Enables direct access from the current device to `peer_device` (cudaDeviceEnablePeerAccess; already
+ * enabled counts as success), so that the copies above travel over NVLink instead of through the host. */
+int cueq_b200_enable_peer_access(int peer_device);
 const char* cueq_b200_last_error(void);
 /* sizeof() of an argument block as this library was compiled, so that a binding can check its own
    declaration before the first launch: 0 cueq_u1d_desc, 1 cueq_buffer, 2 cueq_cw_args,
    3 cueq_cw_noalloc_args, 4 cueq_gemm_args, 5 cueq_fctp_args, 6 cueq_fctp_fused_args,
    7 cueq_fctp_fused_task, 8 cueq_fctp_fused_gx_args, 9 cueq_fctp_fused_unit,
    10 cueq_fctp_fused_gw_args, 11 cueq_fctp_fused_wunit, 12 cueq_gemm_f32x3_args,
-   13 cueq_gemm_f32x3_tn_args; -1 for any other number. */
+   13 cueq_gemm_f32x3_tn_args, 14 cueq_sh_args; -1 for any other number. */
 int64_t cueq_b200_sizeof(int which);
 
 /* ---- generic uniform-1d executor (replaces torch.ops.cuequivariance.uniform_1d) ----------- */
@@ -112,6 +115,29 @@ int cueq_b200_segmented_transpose(const void* x, void* y, int64_t rows, int64_t 
                                   const int32_t* info_dev, int32_t num_blocks, int32_t dtype,
                                   void* stream);
 
+
+/* ---- spherical harmonics of 3-vectors, normalisation fused -----------------------------------
+ *
+ * Replaces, for degrees 0..4, what SphericalHarmonics.forward does in two steps
+ * (cuequivariance_torch/operations/spherical_harmonics.py:76-93: torch normalize, then the polynomial of
+ * cue.descriptors.spherical_harmonics, cuequivariance/group_theory/descriptors/spherical_harmonics_.py:23-52)
+ * and its first derivative.  `ls_mask` has bit l set for every requested degree; the output row holds the
+ * blocks of the requested degrees in ascending order (cueq_b200_sh_width elements).  forward: y = Y(vec or
+ * vec/|vec|); backward: `y` is the COTANGENT of the output and gvec[rows, 3] receives the gradient with
+ * respect to vec.  Row pitches in elements; float32 or float64. */
+typedef struct {
+  const void* vec;      /* [rows, ld_vec], 3 used columns                                          */
+  void* y;              /* forward: output [rows, ld_y]; backward: its cotangent (read only)       */
+  void* gvec;           /* backward: [rows, ld_gvec], 3 columns written; forward: unused           */
+  int64_t rows, ld_vec, ld_y, ld_gvec;
+  uint32_t ls_mask;
+  int32_t normalize;    /* 1: divide the vectors by max(|v|, 1e-12) first                          */
+  int32_t dtype;        /* CUEQ_F32 or CUEQ_F64                                                    */
+  int32_t reserved;
+} cueq_sh_args;
+int cueq_b200_sh_width(uint32_t ls_mask);
+int cueq_b200_sh_forward(const cueq_sh_args* args, void* stream);
+int cueq_b200_sh_backward(const cueq_sh_args* args, void* stream);
 
 /* ---- channelwise ("uvu") tensor product, specialised kernels --------------------------------
  *

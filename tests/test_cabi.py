@@ -116,7 +116,7 @@ def test_binding_struct_sizes_match_the_library():
     L = _lib.lib()
     structs = (_lib.U1dDesc, _lib.Buffer, _lib.CwArgs, _lib.CwNoAllocArgs, _lib.GemmArgs, _lib.FctpArgs, _lib.FctpFusedArgs,
                _lib.FctpFusedTask, _lib.FctpFusedGxArgs, _lib.FctpFusedUnit, _lib.FctpFusedGwArgs, _lib.FctpFusedWUnit,
-               _lib.GemmF32x3Args, _lib.GemmF32x3TnArgs)
+               _lib.GemmF32x3Args, _lib.GemmF32x3TnArgs, _lib.ShArgs)
     for which, st in enumerate(structs):
         assert L.cueq_b200_sizeof(which) == C.sizeof(st), st.__name__
     assert L.cueq_b200_sizeof(len(structs)) == -1

@@ -472,3 +472,34 @@ def test_linear_weight_classes_on_grouped_gemms(method):
     else:
         (ref2,) = naive.segmented_polynomial(e.polynomial, [w, x], {0: shuffled})
         _close(m(x.to(DEV), w.to(DEV), weight_indices=shuffled.to(DEV)), ref2, 1e-5, 2e-6, "unsorted indices")
+
+
+@pytest.mark.parametrize("tag", ["f64", "f32"])
+@pytest.mark.parametrize("ls,normalize", [([0, 1, 2, 3], True), ([1, 3], False), ([0, 2, 4], True)])
+def test_fused_spherical_harmonics_against_oracle(tag, ls, normalize):
+    """The fused kernels (normalisation + all degrees in one pass; first derivative) against the oracle on the
+    descriptor's polynomial; the second derivative (taken with create_graph) runs through the polynomial executor."""
+    dtype = DT[tag]
+    sh = cb.SphericalHarmonics(ls, normalize=normalize)
+    e = D.spherical_harmonics("1o", ls)
+    gen = torch.Generator().manual_seed(sum(ls))
+    vec = torch.randn(257, 3, generator=gen, dtype=torch.float64).to(dtype) * 2.0
+    cot = torch.randn(257, sum(2 * l + 1 for l in ls), generator=gen, dtype=torch.float64).to(dtype)
+
+    def ref_fn(v):
+        v = torch.nn.functional.normalize(v, dim=1) if normalize else v
+        return naive.segmented_polynomial(e.polynomial, [v])[0]
+
+    ref = _derivatives(ref_fn, [vec], cot)
+    profiling.reset()
+    profiling.enable()
+    try:
+        got = _derivatives(lambda v: sh(v), [vec.to(DEV)], cot.to(DEV))
+        names = set(profiling.summary())
+    finally:
+        profiling.enable(False)
+    assert {"sh_fused_forward", "sh_fused_backward"} <= names, names
+    rtol, atol = TOL[tag]
+    _close(got[0], ref[0], rtol, atol, "out")
+    _close(got[1][0], ref[1][0], 10 * rtol, 10 * atol, "grad")
+    _close(got[2][0], ref[2][0], 100 * rtol, 100 * atol, "gradgrad")
