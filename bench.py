@@ -398,7 +398,9 @@ def main():
         x2 = sh(vec).contiguous()
         w = mlp(bessel(length)).contiguous()
     cot = torch.randn(n1 - n0, tp.irreps_out.dim, generator=gen, device=dev)
-    op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD if world > 1 else None)
+    # every step runs its backward before the next forward, so the backward may read the gathered node features
+    # from the exchange's receive buffers instead of a copy
+    op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD if world > 1 else None, keep_gathered=False)
 
     def device_step():
         a, b, c = w.requires_grad_(True), x1_l.requires_grad_(True), x2.requires_grad_(True)

@@ -5,6 +5,7 @@ There is no fallback: if the library is missing or a call fails, an exception is
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libcueq_b200.so"
@@ -205,6 +206,7 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_signature.argtypes = [C.c_int]
     L.cueq_b200_cw_group_signature.restype = C.c_char_p
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
+    L.cueq_b200_check_index_range.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
     L.cueq_b200_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     L.cueq_b200_enable_peer_access.argtypes = [C.c_int]
     L.cueq_b200_sh_width.argtypes = [C.c_uint32]
@@ -266,15 +268,37 @@ def status_word(device):
     return t
 
 
+CHECK_INDICES = bool(os.environ.get("CUEQ_B200_CHECK_INDICES"))   # debug mode, see checked_index()
+
+
+def checked_index(index, rows: int):
+    """Debug mode (``CUEQ_B200_CHECK_INDICES=1`` or ``_lib.CHECK_INDICES = True``): a kernel flags every index
+    outside ``[0, rows)`` in the device's status word (code 3, reported by :func:`check_status`) and the
+    index handed to the product kernels is clamped into range, so that a bad index can neither fault nor
+    corrupt memory.  Off by default: index range is the caller's responsibility, as in the reference."""
+    if not CHECK_INDICES or index is None or not index.is_cuda or index.numel() == 0:
+        return index
+    import torch
+
+    with torch.cuda.device(index.device):
+        check(lib().cueq_b200_check_index_range(C.c_void_p(index.data_ptr()), index.numel(), int(rows), 1 if index.dtype == torch.int64 else 0,
+                                                C.c_void_p(status_word(index.device).data_ptr()),
+                                                C.c_void_p(torch.cuda.current_stream(index.device).cuda_stream)))
+    return index.clamp(0, max(int(rows) - 1, 0))
+
+
 def check_status(device=None) -> None:
     """Synchronises and raises :class:`CueqError` if any kernel since the last check reported a wait that
-    ran out (its results are then incomplete).  The word is cleared."""
+    ran out (its results are then incomplete) or, in index-checking mode, an index out of range.  The word is
+    cleared."""
     for dev, t in list(_status_words.items()):
         if device is not None and dev != __import__("torch").device(device):
             continue
         code = int(t.item())
         if code:
             t.zero_()
+            if code == 3:
+                raise CueqError(f"an index tensor on {dev} pointed outside its buffer (status 3); it was clamped into range, the results are wrong")
             raise CueqError(f"a kernel on {dev} gave up on a bounded wait (status {code}); its outputs are incomplete")
 
 

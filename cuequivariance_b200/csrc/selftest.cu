@@ -18,7 +18,29 @@ __global__ void bounded_wait_selftest_kernel(int* status, long long* waited_cycl
   }
 }
 
+// Debug aid standing in for a memory checker: flags gather / scatter indices that point outside their
+// buffer (status 3) instead of letting the launch that uses them read or write out of bounds.
+template <typename I>
+__global__ void index_range_kernel(const I* __restrict__ idx, int64_t n, int64_t rows, int* status) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t v = (int64_t)idx[i];
+    if (v < 0 || v >= rows) atomicExch(status, 3);
+  }
+}
+
 }  // namespace
+
+extern "C" int cueq_b200_check_index_range(const void* index, int64_t n, int64_t rows, int32_t index_is_64, void* status, void* stream) {
+  if (!status) return cueq::fail("index check: the status word is required");
+  if (n <= 0) return 0;
+  if (!index) return cueq::fail("index check: null index");
+  const unsigned grid = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (index_is_64) index_range_kernel<long long><<<grid, 256, 0, st>>>(reinterpret_cast<const long long*>(index), n, rows, reinterpret_cast<int*>(status));
+  else index_range_kernel<int><<<grid, 256, 0, st>>>(reinterpret_cast<const int*>(index), n, rows, reinterpret_cast<int*>(status));
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int cueq_b200_selftest_bounded_wait(void* status, void* waited_cycles, void* stream) {
   if (!status) return cueq::fail("selftest: the status word is required");

@@ -205,37 +205,39 @@ class PeerExchange:
     """Node-feature exchange between the ranks of one node without taking SMs from the kernels.
 
     The channelwise launches fill every SM, so a collective's thread blocks compete with them (and
-    wait for a free slot before a transfer can even start).  Here each rank keeps its contribution in
-    a buffer that the other ranks have mapped through CUDA IPC; a rank *pulls* what it needs with one
-    ``cudaMemcpyAsync`` per (peer, irrep block) on a copy stream of its own per peer, which the copy
-    engines serve over NVLink while the SMs compute.  Plain peer copies only: no multicast, no
-    batched-copy API.  What still needs a collective is the hand-shake "everybody's buffer is
-    written" before the pulls and "everybody has finished pulling" before a buffer is reused: a
-    one-element all-reduce on a high-priority stream (a few microseconds on one thread block).  A
-    rank that dies leaves the others in that collective, which the process-group time-out ends on
-    the host; nothing on the device waits on a flag.
+    wait for a free slot before a transfer can even start).  Here every rank owns a receive buffer
+    that the other ranks have mapped through CUDA IPC, and a rank *pushes* its contribution into
+    each peer's buffer with one ``cudaMemcpyAsync`` per (peer, irrep block) on a copy stream of its
+    own per peer; the copy engines move the rows over NVLink while the SMs compute.  (Measured on
+    two B200s: a copy that writes to the peer runs at 650 GB/s, the same copy issued as a read from
+    the peer at 24 GB/s, so the exchange only ever pushes.)  Plain peer copies only: no multicast,
+    no batched-copy API.  What still needs a collective is the hand-shake "everybody's rows have
+    landed" before a block is used and "everybody is done with the buffer" before it is written
+    again: a one-element all-reduce on a high-priority stream.  A rank that dies leaves the others
+    in that collective, which the process-group time-out ends on the host; nothing on the device
+    waits on a flag.
 
-    Buffers (float32): ``x[l]`` = this rank's rows of irrep block ``l`` of the node features
-    ``[n_local, width_l]``; ``g[l]`` = this rank's partial gradient of block ``l`` for ALL nodes
-    ``[n_local * world, width_l]``, which the group kernels reduce into directly.
+    Receive buffers (float32): ``full[l]`` = irrep block ``l`` of the node features of ALL ranks
+    ``[n_local * world, width_l]`` (forward); ``stage[l]`` = the other ranks' partial gradients of
+    this rank's rows ``[world, n_local, width_l]`` (backward; slot ``r`` is written by rank ``r``).
     """
 
     def __init__(self, group, n_local: int, widths, device):
         from torch.multiprocessing.reductions import reduce_tensor
 
+        from . import _lib
+
         self.group, self.n_local, self.widths = group, n_local, list(widths)
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.device = device
         n_all = n_local * self.world
-        sizes = [n_local * w for w in self.widths] + [n_all * w for w in self.widths]
+        sizes = [n_all * w for w in self.widths] + [n_all * w for w in self.widths]
         self.offsets = [0]
-        for s in sizes:
-            self.offsets.append(self.offsets[-1] + (s + 63) // 64 * 64)
+        for sz in sizes:
+            self.offsets.append(self.offsets[-1] + (sz + 63) // 64 * 64)
         self.flat = torch.empty(self.offsets[-1], dtype=torch.float32, device=device)
         handles = [None] * self.world
         dist.all_gather_object(handles, reduce_tensor(self.flat), group=group)
-        from . import _lib
-
         self.peers = []
         for r, (fn, args) in enumerate(handles):
             if r == self.rank:
@@ -246,53 +248,53 @@ class PeerExchange:
                 _lib.check(_lib.lib().cueq_b200_enable_peer_access(t.device.index))
             self.peers.append(t)
         nb = len(self.widths)
-        self.x = [self._view(self.flat, l, n_local, self.widths[l]) for l in range(nb)]
-        self.g = [self._view(self.flat, nb + l, n_all, self.widths[l]) for l in range(nb)]
+        self.full = [self._view(self.flat, l, n_all, self.widths[l]) for l in range(nb)]
+        self.stage = [self._view(self.flat, nb + l, n_all, self.widths[l]).view(self.world, n_local, self.widths[l]) for l in range(nb)]
+        self.x = [torch.empty((n_local, w), dtype=torch.float32, device=device) for w in self.widths]   # contiguous send copies
         self.copy_streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(max(1, self.world - 1))]
         self.exch = torch.cuda.Stream(device=device, priority=-1)
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
-        self.pending = []                  # events of pulls issued since the last hand-shake
-        self.x_free = self.g_free = None   # events: every rank has finished pulling from x / g
+        self.free = None                  # event: every rank is done with the receive buffers of the previous pass
 
     def _view(self, flat, slot, rows, width):
         return flat[self.offsets[slot] : self.offsets[slot] + rows * width].view(rows, width)
 
-    def peer_x(self, r, l):
-        return self._view(self.peers[r], l, self.n_local, self.widths[l])
-
-    def peer_g_rows(self, r, l):
-        """Rows of this rank's receiver range inside rank ``r``'s partial gradient of block ``l``."""
-        full = self._view(self.peers[r], len(self.widths) + l, self.n_local * self.world, self.widths[l])
+    def peer_full_rows(self, q, l):
+        """Where this rank's rows of block ``l`` go inside rank ``q``'s gathered block."""
+        full = self._view(self.peers[q], l, self.n_local * self.world, self.widths[l])
         return full[self.rank * self.n_local : (self.rank + 1) * self.n_local]
 
-    def handshake(self, after_event=None):
-        """All ranks have reached this point of their streams (and completed every pull they issued
-        before it).  Returns an event on the exchange stream."""
+    def peer_stage_slot(self, q, l):
+        """This rank's slot in rank ``q``'s staging area for block ``l``."""
+        st = self._view(self.peers[q], len(self.widths) + l, self.n_local * self.world, self.widths[l])
+        return st[self.rank * self.n_local : (self.rank + 1) * self.n_local]
+
+    def handshake(self, after_events=()):
+        """An event that completes once every rank has reached this point (each rank's collective
+        starts only after the events it was given)."""
         s = self.exch
-        if after_event is not None:
-            s.wait_event(after_event)
-        for ev in self.pending:
+        for ev in after_events:
             s.wait_event(ev)
-        self.pending = []
         with torch.cuda.stream(s):
             dist.all_reduce(self.flag, group=self.group)
         ev = torch.cuda.Event()
         ev.record(s)
         return ev
 
-    def pull(self, dst, src, peer_slot: int, after_event):
-        """``dst`` (local, contiguous) <- ``src`` (a peer's buffer, contiguous) on the copy stream of that peer."""
+    def push(self, dst, src, peer_slot: int, after_events):
+        """``dst`` (a peer's buffer, contiguous) <- ``src`` (local, contiguous) on the copy stream of that peer."""
         import ctypes as C
 
         from . import _lib
 
         s = self.copy_streams[peer_slot % len(self.copy_streams)]
-        s.wait_event(after_event)
+        for ev in after_events:
+            if ev is not None:
+                s.wait_event(ev)
         _lib.check(_lib.lib().cueq_b200_copy_async(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()),
-                                                   C.c_size_t(dst.numel() * dst.element_size()), C.c_void_p(s.cuda_stream)))
+                                                   C.c_size_t(src.numel() * src.element_size()), C.c_void_p(s.cuda_stream)))
         ev = torch.cuda.Event()
         ev.record(s)
-        self.pending.append(ev)
         return ev
 
 
@@ -321,13 +323,17 @@ def _exchange_for(group, n_local, widths, device):
 
 class _PeerCopyShardedChannelwise(torch.autograd.Function):
     """Same computation as `_PipelinedShardedChannelwise` with the rows moved by `PeerExchange`:
-    forward pulls the other ranks' node rows block by block (smallest irrep first) while the launches of
-    the blocks that have arrived run; backward lets every group launch reduce into this rank's shared
-    partial-gradient block, and as soon as a block is complete everywhere each rank pulls its own rows of
-    it from every peer and adds them up.  First-order only."""
+    forward pushes this rank's node rows into every peer's gathered blocks (smallest irrep first) and
+    launches a block's kernel once all ranks' rows of it have landed; backward lets every group launch
+    reduce into a local partial-gradient block and pushes each peer's rows of it into that peer's staging
+    slot as soon as the launch is done, the owner adds the slots up.  First-order only.
+
+    The gathered blocks live in the exchange's persistent receive buffers.  With ``keep`` they are cloned for
+    the backward pass; without, the backward pass reads the buffers themselves, which is valid as long as the
+    backward of a forward runs before the next forward of the same module (the usual training step)."""
 
     @staticmethod
-    def forward(ctx, handler, ex, x1_local, x2, weight, senders, receivers_local):
+    def forward(ctx, handler, ex, keep, x1_local, x2, weight, senders, receivers_local):
         from .channelwise import _CSR
 
         plan = handler.plan
@@ -338,30 +344,26 @@ class _PeerCopyShardedChannelwise(torch.autograd.Function):
         order, rowptr = _CSR.get(receivers_local, n_local)
         csr = (order, rowptr, n_local)
         groups = plan.groups
-        if ex.x_free is not None:
-            main.wait_event(ex.x_free)            # nobody is still reading the previous contents
         for l, g in enumerate(groups):
             ex.x[l].copy_(x1_local[:, g["x1_off"] : g["x1_off"] + g["x1_width"]])
         written = torch.cuda.Event()
         written.record(main)
-        ready = ex.handshake(written)
-        wide, arrived = [], []
-        for l, g in enumerate(groups):
-            full = torch.empty((n_local * world, g["x1_width"]), dtype=torch.float32, device=dev)
-            evs = []
-            for k in range(1, world):
-                r = (rank + k) % world
-                evs.append(ex.pull(full[r * n_local : (r + 1) * n_local], ex.peer_x(r, l), k - 1, ready))
-            wide.append(full)
-            arrived.append(evs)
-        ex.x_free = ex.handshake()                # runs once every rank's pulls are done; the next forward waits for it
+        ready = []
+        for l in range(len(groups)):
+            evs = [ex.push(ex.peer_full_rows((rank + k) % world, l), ex.x[l], k - 1, (written, ex.free)) for k in range(1, world)]
+            ready.append(ex.handshake(evs))
+        if ex.free is not None:
+            main.wait_event(ex.free)               # this rank's own rows also go into a buffer the last pass may still read
         out = torch.empty((n_local, plan.row_sizes[3]), dtype=torch.float32, device=dev)
         for l, g in enumerate(groups):
-            wide[l][rank * n_local : (rank + 1) * n_local].copy_(ex.x[l])
-            for ev in arrived[l]:
-                main.wait_event(ev)
-            handler.launch_forward_group(l, common, csr, True, weight, wide[l], x2, out)
-        ctx.handler, ctx.ex, ctx.common, ctx.csr = handler, ex, common, csr
+            ex.full[l][rank * n_local : (rank + 1) * n_local].copy_(ex.x[l])
+            main.wait_event(ready[l])
+            handler.launch_forward_group(l, common, csr, True, weight, ex.full[l], x2, out)
+        wide = [t.clone() for t in ex.full] if keep else list(ex.full)
+        done = torch.cuda.Event()
+        done.record(main)
+        ex.free = ex.handshake([done])             # superseded by the backward's own if one follows
+        ctx.handler, ctx.ex, ctx.common, ctx.csr, ctx.keep = handler, ex, common, csr, keep
         ctx.save_for_backward(weight, x2, *wide)
         return out
 
@@ -375,38 +377,33 @@ class _PeerCopyShardedChannelwise(torch.autograd.Function):
         dev = gout.device
         main = torch.cuda.current_stream(dev)
         gout = gout.contiguous()
-        need_x1, need_x2, need_w = ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.needs_input_grad[4]
+        need_x1, need_x2, need_w = ctx.needs_input_grad[3], ctx.needs_input_grad[4], ctx.needs_input_grad[5]
         gw = torch.empty_like(weight) if need_w else None
         gx2 = torch.zeros_like(x2) if need_x2 else None
         groups = plan.groups
-        stage, arrived = {}, {}
-        if need_x1:
-            if ex.g_free is not None:
-                main.wait_event(ex.g_free)        # the peers have finished pulling the previous partial gradients
-            for l in range(len(groups)):
-                ex.g[l].zero_()
+        partial, ready = {}, {}
         for l in reversed(range(len(groups))):    # largest blocks first: their transfers hide behind the later launches
-            handler.launch_backward_group(l, common, csr, True, weight, wide[l], x2, gout, gw, ex.g[l] if need_x1 else None, gx2)
+            gl = torch.zeros((n_local * world, groups[l]["x1_width"]), dtype=torch.float32, device=dev) if need_x1 else None
+            handler.launch_backward_group(l, common, csr, True, weight, wide[l], x2, gout, gw, gl, gx2)
             if need_x1:
                 done = torch.cuda.Event()
                 done.record(main)
-                ready = ex.handshake(done)        # block l is complete on every rank
-                st = torch.empty((world - 1, n_local, groups[l]["x1_width"]), dtype=torch.float32, device=dev)
                 evs = []
                 for k in range(1, world):
-                    r = (rank + k) % world
-                    evs.append(ex.pull(st[k - 1], ex.peer_g_rows(r, l), k - 1, ready))
-                stage[l], arrived[l] = st, evs
+                    q = (rank + k) % world
+                    evs.append(ex.push(ex.peer_stage_slot(q, l), gl[q * n_local : (q + 1) * n_local], k - 1, (done,)))
+                ex.stage[l][rank].copy_(gl[rank * n_local : (rank + 1) * n_local])      # this rank's own contribution
+                partial[l], ready[l] = gl, ex.handshake(evs)
         gx1 = None
         if need_x1:
-            ex.g_free = ex.handshake()
             gx1 = torch.empty((n_local, plan.row_sizes[1]), dtype=torch.float32, device=dev)
             for l, g in enumerate(groups):
-                for ev in arrived[l]:
-                    main.wait_event(ev)
-                mine = ex.g[l][rank * n_local : (rank + 1) * n_local]
-                torch.add(mine, stage[l].sum(0), out=gx1[:, g["x1_off"] : g["x1_off"] + g["x1_width"]])
-        return None, None, gx1, gx2, gw, None, None
+                main.wait_event(ready[l])
+                gx1[:, g["x1_off"] : g["x1_off"] + g["x1_width"]] = ex.stage[l].sum(0)
+        done = torch.cuda.Event()
+        done.record(main)
+        ex.free = ex.handshake([done])            # receive buffers (gathered blocks, staging slots) may be rewritten after this
+        return None, None, None, gx1, gx2, gw, None, None
 
 
 class ReceiverShardedChannelWise(torch.nn.Module):
@@ -418,11 +415,14 @@ class ReceiverShardedChannelWise(torch.nn.Module):
     rows of the output.  With ``group=None`` (one process) it is the plain fused call.
     """
 
-    def __init__(self, tp: torch.nn.Module, group=None, pipelined: bool = True):
+    def __init__(self, tp: torch.nn.Module, group=None, pipelined: bool = True, keep_gathered: bool = True):
         super().__init__()
         self.tp = tp
         self.group = group
         self.pipelined = pipelined
+        # False: the backward pass reads the gathered node features from the exchange's receive buffers instead of a
+        # copy; valid when every forward is followed by its backward before the next forward (a training step)
+        self.keep_gathered = keep_gathered
 
     def _handler(self, x1_local, x2, weight):
         """The specialised-kernel handler if the pipelined path applies (float32, mul_ir
@@ -450,8 +450,8 @@ class ReceiverShardedChannelWise(torch.nn.Module):
             if EXCHANGE == "peer_copy" and dist.get_world_size(self.group) > 1:
                 ex = _exchange_for(self.group, n_local, [g["x1_width"] for g in handler.plan.groups], x1_local.device)
                 if ex is not None:
-                    return _PeerCopyShardedChannelwise.apply(handler, ex, x1_local, x2.contiguous(), weight.contiguous(),
-                                                             senders, receivers_local)
+                    return _PeerCopyShardedChannelwise.apply(handler, ex, self.keep_gathered, x1_local, x2.contiguous(),
+                                                             weight.contiguous(), senders, receivers_local)
             return _PipelinedShardedChannelwise.apply(handler, self.group, x1_local, x2.contiguous(), weight.contiguous(),
                                                       senders, receivers_local)
         x1 = all_gather_rows(x1_local, self.group)

@@ -424,6 +424,10 @@ def evaluate(program: Uniform1dProgram, inputs, input_indices=None, output_shape
     inputs = list(inputs)
     if len(inputs) != program.num_inputs:
         raise ValueError("the number of inputs must match the number of inputs of the polynomial")
+    if _lib.CHECK_INDICES:
+        input_indices = {k: _lib.checked_index(v, inputs[k].shape[0]) for k, v in input_indices.items()}
+        output_indices = {k: _lib.checked_index(v, output_shapes[k] if isinstance(output_shapes[k], int) else output_shapes[k].shape[0])
+                          for k, v in output_indices.items()}
     cfg, expand = make_config(program, inputs, input_indices, output_shapes, output_indices)
     if layouts:
         nb = program.num_inputs + program.num_outputs

@@ -71,6 +71,11 @@ typedef struct {
 } cueq_buffer;
 
 int cueq_b200_abi_version(void);
+/* Debug aid (the reference documents index range as an unchecked precondition,
+ * cuequivariance_torch/primitives/segmented_polynomial.py:278-279): sets *status (device int32) to 3 if any of
+ * the n gather / scatter indices lies outside [0, rows).  Nothing traps; the host reads the word. */
+int cueq_b200_check_index_range(const void* index, int64_t n, int64_t rows, int32_t index_is_64, void* status,
+                                void* stream);
 /* One asynchronous device-to-device copy on `stream` (cudaMemcpyAsync); dst or src may be memory of
  * another GPU of the node mapped into this process.  Used for the exchange of node features between
  * the ranks of a receiver-sharded product, which then needs no SM.  The reference has no multi-GPU

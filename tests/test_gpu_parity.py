@@ -503,3 +503,28 @@ def test_fused_spherical_harmonics_against_oracle(tag, ls, normalize):
     _close(got[0], ref[0], rtol, atol, "out")
     _close(got[1][0], ref[1][0], 10 * rtol, 10 * atol, "grad")
     _close(got[2][0], ref[2][0], 100 * rtol, 100 * atol, "gradgrad")
+
+
+def test_index_range_debug_mode_flags_and_clamps(monkeypatch):
+    """With index checking on, an out-of-range scatter index is reported through the status word (code 3) and
+    clamped, so nothing faults; with valid indices the mode changes no result."""
+    from cuequivariance_b200 import _lib
+
+    monkeypatch.setattr(_lib, "CHECK_INDICES", True)
+    e = D.channelwise_tensor_product("8x0e+8x1o", "0e+1o", "0e+1o")
+    f = cb.SegmentedPolynomial(e.polynomial, method="uniform_1d")
+    p = e.polynomial
+    gen = torch.Generator().manual_seed(4)
+    E, N = 50, 6
+    xs = [torch.randn(E, p.inputs[0].size, generator=gen), torch.randn(N, p.inputs[1].size, generator=gen), torch.randn(E, p.inputs[2].size, generator=gen)]
+    snd, rcv = torch.randint(0, N, (E,), generator=gen), torch.randint(0, N, (E,), generator=gen)
+    (ref,) = naive.segmented_polynomial(p, xs, {1: snd}, {0: N}, {0: rcv})
+    (got,) = f([x.to(DEV) for x in xs], {1: snd.to(DEV)}, {0: torch.empty(N, 1, device=DEV)}, {0: rcv.to(DEV)})
+    _close(got, ref, 1e-5, 2e-6, "valid indices")
+    _lib.check_status()
+    bad = rcv.clone()
+    bad[7] = N + 3
+    f([x.to(DEV) for x in xs], {1: snd.to(DEV)}, {0: torch.empty(N, 1, device=DEV)}, {0: bad.to(DEV)})
+    with pytest.raises(_lib.CueqError, match="status 3"):
+        _lib.check_status()
+    _lib.check_status()   # the word was cleared
