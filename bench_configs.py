@@ -1,6 +1,10 @@
 """Throughput of the other benchmark configurations (the headline one is ``bench.py``).
 
-    python bench_configs.py [--config 0|1|2|2bf16|4|all] [--steps K]
+    python bench_configs.py [--config 0|1|2|2bf16|4|fma|all] [--steps K] [--batch B] [--edges E --nodes N]
+
+``--batch`` scales configs 1 and 2, ``--edges`` / ``--nodes`` configs 0 and 4 (the profiles under ``profiles/`` are
+captured on scaled-down cases with these flags); ``fma`` measures the float32 multiply-add peak that config 1 is
+rated against.
 
 Prints one JSON line per configuration: device-timed (CUDA events) steps on seeded
 synthetic inputs of the configuration's shapes, with the per-kernel breakdown of the native
@@ -49,12 +53,34 @@ def _time(step, steps, warmup=3):
     return ms, launches, kernels
 
 
-def config0(steps, dev):
+def fma_peak(steps, dev):
+    """float32 FMA peak: 148 x 32 blocks of 256 threads, 16 independent chains each."""
+    import ctypes as C
+
+    from cuequivariance_b200 import _lib
+
+    sink = torch.zeros(1, device=dev)
+    blocks, iters = 148 * 32, 20000
+    fn = lambda: _lib.check(_lib.lib().cueq_b200_selftest_fma_peak(C.c_void_p(sink.data_ptr()), blocks, iters,  # noqa: E731
+                                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    for _ in range(3):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"config": "fma", "what": "float32 multiply-add peak (register-resident chains)", "ms_per_step": ms,
+            "tflops": 2.0 * blocks * 256 * 16 * iters / ms / 1e9}
+
+
+def config0(steps, dev, E=65536, N=4096):
     tp = cb.ChannelWiseTensorProduct("128x0e+128x1o+128x2e", "0e+1o+2e+3o", FILTER, layout=cb.mul_ir,
                                      shared_weights=False, internal_weights=False)
     sh = cb.SphericalHarmonics([0, 1, 2, 3], normalize=True)
     g = torch.Generator(device=dev).manual_seed(0)
-    E, N = 65536, 4096
     x1 = torch.randn(N, tp.irreps_in1.dim, generator=g, device=dev)
     x2 = sh(torch.randn(E, 3, generator=g, device=dev))
     w = torch.randn(E, tp.weight_numel, generator=g, device=dev)
@@ -65,8 +91,7 @@ def config0(steps, dev):
             "gpu_launches": n, "kernels_ms": k}
 
 
-def config1(steps, dev):
-    B = 16384
+def config1(steps, dev, B=16384):
     m = cb.SymmetricContraction("128x0e+128x1o+128x2e+128x3o", "128x0e+128x1o", 3, 10, layout=cb.mul_ir, dtype=torch.float32, device=dev)
     g = torch.Generator(device=dev).manual_seed(10)
     x = torch.randn(B, m.irreps_in.dim, generator=g, device=dev, requires_grad=True)
@@ -79,13 +104,13 @@ def config1(steps, dev):
         torch.autograd.grad(out.sum(), [x, m.weight])
 
     ms, n, k = _time(step, steps)
-    return {"config": 1, "what": "symmetric contraction fwd+bwd", "ms_per_step": ms, "value": B / ms * 1e3, "unit": "atoms/s",
-            "gpu_launches": n, "kernels_ms": k}
+    flops = (299_648 + 1_031_296) * B   # multiply-adds counted as 2 flop on the merged (unsymmetrised) polynomials, per atom
+    return {"config": 1, "what": f"symmetric contraction fwd+bwd, {B} atoms", "ms_per_step": ms, "value": B / ms * 1e3, "unit": "atoms/s",
+            "tflops": flops / ms / 1e9, "gpu_launches": n, "kernels_ms": k}
 
 
-def config2(steps, dev, dtype=torch.float32):
+def config2(steps, dev, dtype=torch.float32, B=32768):
     s = "64x0e+64x1o+64x2e"
-    B = 32768
     m = cb.FullyConnectedTensorProduct(s, s, s, layout=cb.mul_ir, internal_weights=False, shared_weights=True)
     g = torch.Generator(device=dev).manual_seed(20)
     x1 = torch.randn(B, m.irreps_in1.dim, generator=g, device=dev).to(dtype).requires_grad_(True)
@@ -97,15 +122,23 @@ def config2(steps, dev, dtype=torch.float32):
         torch.autograd.grad(out.float().sum(), [x1, x2, w])
 
     ms, n, k = _time(step, steps)
-    route = "tensor-core route (TMA + tcgen05 GEMM, bf16 operands, float32 accumulation)" if dtype == torch.bfloat16 \
-        else "interim full-precision library-GEMM route"
+    route = "fused tcgen05 kernels (coupled operand built on chip, bf16 operands, float32 accumulation)" if dtype == torch.bfloat16 \
+        else "float32-accurate route (coupled operand in memory, three-pass TF32 tcgen05 GEMMs)"
     flops = 4 * 2 * 35 * 64 ** 3 * B
-    return {"config": 2, "what": f"fully connected fwd+bwd, {str(dtype).split('.')[-1]}, {route}", "ms_per_step": ms,
-            "value": B / ms * 1e3, "unit": "samples/s", "tflops": flops / ms / 1e9, "gpu_launches": n, "kernels_ms": k}
+    peak = _peaks().get("bf16_tflops_sustained")
+    return {"config": 2, "what": f"fully connected fwd+bwd, {str(dtype).split('.')[-1]}, {B} samples, {route}", "ms_per_step": ms,
+            "value": B / ms * 1e3, "unit": "samples/s", "tflops": flops / ms / 1e9,
+            "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
+                         "frac": (flops / ms / 1e9) / peak if peak else None,
+                         "note": "useful flop of the four contractions over the measured sustained bf16 peak; the float32 route spends three TF32 passes per product"},
+            "gpu_launches": n, "kernels_ms": k}
 
 
-def config2_bf16(steps, dev):
-    return config2(steps, dev, torch.bfloat16)
+def _peaks():
+    try:
+        return json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+    except OSError:
+        return {}
 
 
 def config4(steps, dev, E=65536, N=4096):
@@ -135,13 +168,18 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="all")
     ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--edges4", type=int, default=65536, help="config 4: number of edges (nodes = edges / 16 ... 32)")
-    ap.add_argument("--nodes4", type=int, default=4096)
+    ap.add_argument("--edges", type=int, default=65536, help="configs 0 and 4: number of edges")
+    ap.add_argument("--nodes", type=int, default=4096, help="configs 0 and 4: number of nodes")
+    ap.add_argument("--batch", type=int, default=None, help="configs 1 and 2: atoms / samples (default: the configuration's size)")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
-    fns = {"0": config0, "1": config1, "2": config2, "2bf16": config2_bf16,
-           "4": lambda steps, dev: config4(steps, dev, a.edges4, a.nodes4)}
-    for key in (fns if a.config == "all" else [a.config]):
+    fns = {"0": lambda steps, dev: config0(steps, dev, a.edges, a.nodes),
+           "1": lambda steps, dev: config1(steps, dev, a.batch or 16384),
+           "2": lambda steps, dev: config2(steps, dev, torch.float32, a.batch or 32768),
+           "2bf16": lambda steps, dev: config2(steps, dev, torch.bfloat16, a.batch or 32768),
+           "4": lambda steps, dev: config4(steps, dev, a.edges, a.nodes),
+           "fma": fma_peak}
+    for key in ([k for k in fns if k != "fma"] if a.config == "all" else [a.config]):
         print(json.dumps(fns[key](a.steps, dev)), flush=True)
 
 

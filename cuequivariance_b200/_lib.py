@@ -73,6 +73,10 @@ class CwNoAllocArgs(C.Structure):
     ]
 
 
+class PushArgs(C.Structure):
+    _fields_ = [("dst", C.c_void_p * 8), ("src", C.c_void_p * 8), ("bytes", C.c_int64 * 8), ("num_pieces", C.c_int32), ("blocks_per_piece", C.c_int32)]
+
+
 class ShArgs(C.Structure):
     _fields_ = [
         ("vec", C.c_void_p), ("y", C.c_void_p), ("gvec", C.c_void_p),
@@ -206,9 +210,14 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_signature.argtypes = [C.c_int]
     L.cueq_b200_cw_group_signature.restype = C.c_char_p
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
+    L.cueq_b200_selftest_fma_peak.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     L.cueq_b200_check_index_range.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
     L.cueq_b200_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     L.cueq_b200_enable_peer_access.argtypes = [C.c_int]
+    L.cueq_b200_push.argtypes = [C.POINTER(PushArgs), C.c_void_p]
+    L.cueq_b200_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    L.cueq_b200_ipc_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    L.cueq_b200_ipc_close.argtypes = [C.c_void_p]
     L.cueq_b200_sh_width.argtypes = [C.c_uint32]
     L.cueq_b200_sh_forward.argtypes = [C.POINTER(ShArgs), C.c_void_p]
     L.cueq_b200_sh_backward.argtypes = [C.POINTER(ShArgs), C.c_void_p]

@@ -28,7 +28,30 @@ __global__ void index_range_kernel(const I* __restrict__ idx, int64_t n, int64_t
   }
 }
 
+// Measures what the float32 multiply-add pipes deliver: every thread runs 16 independent chains of dependent
+// FMAs held in registers, no memory traffic.  The host times the launch; work = 2 * threads * 16 * iters flop.
+__global__ void __launch_bounds__(256) fma_peak_kernel(float* __restrict__ sink, int iters, float a, float b) {
+  float acc[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) acc[k] = (float)(threadIdx.x + k);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc[k] = fmaf(acc[k], a, b);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) s += acc[k];
+  if (s == 12345.678f) sink[0] = s;   // keeps the chains alive without a store in practice
+}
+
 }  // namespace
+
+extern "C" int cueq_b200_selftest_fma_peak(void* sink, int32_t blocks, int32_t iters, void* stream) {
+  if (!sink || blocks <= 0 || iters <= 0) return cueq::fail("fma peak: invalid arguments");
+  fma_peak_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<float*>(sink), iters, 0.999f, 0.001f);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int cueq_b200_check_index_range(const void* index, int64_t n, int64_t rows, int32_t index_is_64, void* status, void* stream) {
   if (!status) return cueq::fail("index check: the status word is required");

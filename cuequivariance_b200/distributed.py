@@ -198,6 +198,12 @@ class _PipelinedShardedChannelwise(torch.autograd.Function):
         return None, None, gx1, gx2, gw, None, None
 
 
+import os as _os
+
+_DIAG_SKIP_COPY = bool(_os.environ.get("CUEQ_DIAG_SKIP_COPY"))
+_DIAG_SKIP_HANDSHAKE = bool(_os.environ.get("CUEQ_DIAG_SKIP_HANDSHAKE"))
+PUSH_BLOCKS = int(_os.environ.get("CUEQ_PUSH_BLOCKS", "4"))      # thread blocks per (peer, irrep block) piece of the push kernel
+PUSH_MODE = _os.environ.get("CUEQ_PUSH_MODE", "kernel")   # "kernel": the push kernel; "memcpy": one cudaMemcpyAsync per piece
 EXCHANGE = "peer_copy"   # how the pipelined path moves node rows between ranks: "peer_copy" (copy engines) or "nccl"
 
 
@@ -207,11 +213,13 @@ class PeerExchange:
     The channelwise launches fill every SM, so a collective's thread blocks compete with them (and
     wait for a free slot before a transfer can even start).  Here every rank owns a receive buffer
     that the other ranks have mapped through CUDA IPC, and a rank *pushes* its contribution into
-    each peer's buffer with one ``cudaMemcpyAsync`` per (peer, irrep block) on a copy stream of its
-    own per peer; the copy engines move the rows over NVLink while the SMs compute.  (Measured on
-    two B200s: a copy that writes to the peer runs at 650 GB/s, the same copy issued as a read from
-    the peer at 24 GB/s, so the exchange only ever pushes.)  Plain peer copies only: no multicast,
-    no batched-copy API.  What still needs a collective is the hand-shake "everybody's rows have
+    each peer's buffer with this library's push kernel (``csrc/peer_copy.cu``: 16-byte stores over
+    NVLink, one launch per irrep block covering all peers, a few thread blocks per peer) on a
+    high-priority side stream.  Why a kernel and why pushing, measured on two B200s: a
+    ``cudaMemcpyAsync`` into IPC-mapped peer memory blocked the issuing host thread for the length
+    of the copy (1.3 ms per call, the host fell behind the device), and a transfer that reads from
+    the peer ran at 24 GB/s where the same transfer written to the peer ran at 650 GB/s.  Plain
+    stores only: no multicast, no TMA.  What still needs a collective is the hand-shake "everybody's rows have
     landed" before a block is used and "everybody is done with the buffer" before it is written
     again: a one-element all-reduce on a high-priority stream.  A rank that dies leaves the others
     in that collective, which the process-group time-out ends on the host; nothing on the device
@@ -223,7 +231,7 @@ class PeerExchange:
     """
 
     def __init__(self, group, n_local: int, widths, device):
-        from torch.multiprocessing.reductions import reduce_tensor
+        import ctypes as C
 
         from . import _lib
 
@@ -236,17 +244,22 @@ class PeerExchange:
         for sz in sizes:
             self.offsets.append(self.offsets[-1] + (sz + 63) // 64 * 64)
         self.flat = torch.empty(self.offsets[-1], dtype=torch.float32, device=device)
+        # every rank exports its buffer; every other rank maps it for ITS OWN device (see csrc/peer_copy.cu)
+        handle, offset = C.create_string_buffer(64), C.c_int64(0)
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().cueq_b200_ipc_export(C.c_void_p(self.flat.data_ptr()), handle, C.byref(offset)))
         handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.flat), group=group)
-        self.peers = []
-        for r, (fn, args) in enumerate(handles):
+        dist.all_gather_object(handles, (bytes(handle.raw), int(offset.value)), group=group)
+        self.peers, self._mapped = [], []
+        for r, (raw, off) in enumerate(handles):
             if r == self.rank:
                 self.peers.append(self.flat)
                 continue
-            t = fn(*args)                 # the peer's buffer, mapped into this process (a tensor on the peer's device)
+            base = C.c_void_p()
             with torch.cuda.device(device):
-                _lib.check(_lib.lib().cueq_b200_enable_peer_access(t.device.index))
-            self.peers.append(t)
+                _lib.check(_lib.lib().cueq_b200_ipc_open(C.create_string_buffer(raw, 64), C.byref(base)))
+            self._mapped.append(base)
+            self.peers.append(_as_tensor(base.value + off, self.flat.numel(), device))
         nb = len(self.widths)
         self.full = [self._view(self.flat, l, n_all, self.widths[l]) for l in range(nb)]
         self.stage = [self._view(self.flat, nb + l, n_all, self.widths[l]).view(self.world, n_local, self.widths[l]) for l in range(nb)]
@@ -275,27 +288,53 @@ class PeerExchange:
         s = self.exch
         for ev in after_events:
             s.wait_event(ev)
-        with torch.cuda.stream(s):
-            dist.all_reduce(self.flag, group=self.group)
+        if not _DIAG_SKIP_HANDSHAKE:
+            with torch.cuda.stream(s):
+                dist.all_reduce(self.flag, group=self.group)
         ev = torch.cuda.Event()
         ev.record(s)
         return ev
 
-    def push(self, dst, src, peer_slot: int, after_events):
-        """``dst`` (a peer's buffer, contiguous) <- ``src`` (local, contiguous) on the copy stream of that peer."""
+    def push(self, pieces, after_events):
+        """``pieces`` = [(dst, src)]: ``dst`` a peer's buffer, ``src`` local, both contiguous and of equal size.  One
+        launch of the push kernel per eight pieces on the exchange's copy stream; returns the completion event."""
         import ctypes as C
 
         from . import _lib
 
-        s = self.copy_streams[peer_slot % len(self.copy_streams)]
+        s = self.copy_streams[0]
         for ev in after_events:
             if ev is not None:
                 s.wait_event(ev)
-        _lib.check(_lib.lib().cueq_b200_copy_async(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()),
-                                                   C.c_size_t(src.numel() * src.element_size()), C.c_void_p(s.cuda_stream)))
+        if PUSH_MODE == "memcpy" and not _DIAG_SKIP_COPY:   # copy engines instead of the push kernel
+            with torch.cuda.device(self.device):
+                for dst, src in pieces:
+                    _lib.check(_lib.lib().cueq_b200_copy_async(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()),
+                                                               C.c_size_t(src.numel() * src.element_size()), C.c_void_p(s.cuda_stream)))
+            pieces = []
+        for i in range(0, len(pieces), 8):
+            a = _lib.PushArgs()
+            chunk = pieces[i : i + 8]
+            for k, (dst, src) in enumerate(chunk):
+                a.dst[k], a.src[k], a.bytes[k] = dst.data_ptr(), src.data_ptr(), src.numel() * src.element_size()
+            a.num_pieces, a.blocks_per_piece = len(chunk), PUSH_BLOCKS
+            if not _DIAG_SKIP_COPY:
+                with torch.cuda.device(self.device):
+                    _lib.check(_lib.lib().cueq_b200_push(C.byref(a), C.c_void_p(s.cuda_stream)))
         ev = torch.cuda.Event()
         ev.record(s)
         return ev
+
+
+class _RawDeviceArray:
+    """Exposes a raw device pointer through the CUDA array interface so that torch can wrap it without a copy."""
+
+    def __init__(self, ptr: int, numel: int):
+        self.__cuda_array_interface__ = {"shape": (numel,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def _as_tensor(ptr: int, numel: int, device) -> torch.Tensor:
+    return torch.as_tensor(_RawDeviceArray(ptr, numel), device=device)
 
 
 _EXCHANGES: dict = {}
@@ -350,8 +389,8 @@ class _PeerCopyShardedChannelwise(torch.autograd.Function):
         written.record(main)
         ready = []
         for l in range(len(groups)):
-            evs = [ex.push(ex.peer_full_rows((rank + k) % world, l), ex.x[l], k - 1, (written, ex.free)) for k in range(1, world)]
-            ready.append(ex.handshake(evs))
+            pieces = [(ex.peer_full_rows((rank + k) % world, l), ex.x[l]) for k in range(1, world)]
+            ready.append(ex.handshake([ex.push(pieces, (written, ex.free))]))
         if ex.free is not None:
             main.wait_event(ex.free)               # this rank's own rows also go into a buffer the last pass may still read
         out = torch.empty((n_local, plan.row_sizes[3]), dtype=torch.float32, device=dev)
@@ -388,12 +427,12 @@ class _PeerCopyShardedChannelwise(torch.autograd.Function):
             if need_x1:
                 done = torch.cuda.Event()
                 done.record(main)
-                evs = []
+                pieces = []
                 for k in range(1, world):
                     q = (rank + k) % world
-                    evs.append(ex.push(ex.peer_stage_slot(q, l), gl[q * n_local : (q + 1) * n_local], k - 1, (done,)))
+                    pieces.append((ex.peer_stage_slot(q, l), gl[q * n_local : (q + 1) * n_local]))
                 ex.stage[l][rank].copy_(gl[rank * n_local : (rank + 1) * n_local])      # this rank's own contribution
-                partial[l], ready[l] = gl, ex.handshake(evs)
+                partial[l], ready[l] = gl, ex.handshake([ex.push(pieces, (done,))])
         gx1 = None
         if need_x1:
             gx1 = torch.empty((n_local, plan.row_sizes[1]), dtype=torch.float32, device=dev)

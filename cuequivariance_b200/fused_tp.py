@@ -190,10 +190,9 @@ class _TensorCoreUVW(torch.autograd.Function):
                 gwf = owner._fused_gw(w, x1b, x2b, gout16, status)
                 need_w = False
             if need_x1:
-                gx1f = owner._fused_gx(1, w.reshape(-1, 64).to(torch.bfloat16).contiguous(), x2b, gout16, status)
+                gx1f = owner._fused_gx(1, owner._weights_bf16(w, False), x2b, gout16, status)
             if need_x2:
-                wt = w.reshape(-1, 64, 64, 64).transpose(1, 2).reshape(-1, 64).to(torch.bfloat16).contiguous()
-                gx2f = owner._fused_gx(2, wt, x1b, gout16, status)
+                gx2f = owner._fused_gx(2, owner._weights_bf16(w, True), x1b, gout16, status)
             need_x1 = need_x2 = False
         x1c, x2c = owner._as_kernel_input(x1), owner._as_kernel_input(x2)
         gw = torch.zeros((1, w.shape[1]), dtype=torch.float32, device=dev) if need_w else None
@@ -251,6 +250,22 @@ class DenseUVW:
         self.offsets = [op.offsets() for op in d.operands]
         self.out_size = d.operands[3].size
         self._flat = {}
+        self._wcache = {}
+
+    def _weights_bf16(self, w: torch.Tensor, transposed: bool) -> torch.Tensor:
+        """The shared weights as bf16 rows of 64, in ``[u][v][w]`` order or (``transposed``) ``[v][u][w]``.  The same
+        weight tensor is used by every call of a step and changes only when the optimizer updates it, so the
+        converted copies are kept until the tensor's version counter moves (or another tensor is passed)."""
+        key = (w.data_ptr(), w._version, tuple(w.shape), w.dtype, transposed)
+        hit = self._wcache.get(transposed)
+        if hit is not None and hit[0] == key:
+            return hit[1]
+        if transposed:
+            t = w.detach().reshape(-1, 64, 64, 64).transpose(1, 2).reshape(-1, 64).to(torch.bfloat16).contiguous()
+        else:
+            t = w.detach().reshape(-1, 64).to(torch.bfloat16).contiguous()
+        self._wcache[transposed] = (key, t)
+        return t
 
     # -- tensor-core route ---------------------------------------------------------------------
     def _tc_applicable(self, w, x1, x2) -> bool:
@@ -403,7 +418,7 @@ class DenseUVW:
         tasks = self._fused_tasks()
         B = x1.shape[0]
         x1c, x2c = x1.to(torch.bfloat16).contiguous(), x2.to(torch.bfloat16).contiguous()
-        w16 = w.reshape(-1, 64).to(torch.bfloat16).contiguous()
+        w16 = self._weights_bf16(w, False)
         out = torch.empty((B, self.out_size), dtype=torch.float32, device=x1.device)
         a = _lib.FctpFusedArgs()
         a.x1, a.x2, a.w, a.out = x1c.data_ptr(), x2c.data_ptr(), w16.data_ptr(), out.data_ptr()

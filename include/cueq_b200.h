@@ -71,6 +71,10 @@ typedef struct {
 } cueq_buffer;
 
 int cueq_b200_abi_version(void);
+/* Measurement aid, no reference counterpart: `blocks` x 256 threads each run 16 chains of `iters` dependent
+ * float32 multiply-adds in registers (2 * blocks * 256 * 16 * iters flop).  Timed by the caller with CUDA
+ * events, it gives the float32 FMA peak that the straight-line symmetric-contraction kernels are rated against. */
+int cueq_b200_selftest_fma_peak(void* sink, int32_t blocks, int32_t iters, void* stream);
 /* Debug aid (the reference documents index range as an unchecked precondition,
  * cuequivariance_torch/primitives/segmented_polynomial.py:278-279): sets *status (device int32) to 3 if any of
  * the n gather / scatter indices lies outside [0, rows).  Nothing traps; the host reads the word. */
@@ -81,6 +85,25 @@ int cueq_b200_check_index_range(const void* index, int64_t n, int64_t rows, int3
  * the ranks of a receiver-sharded product, which then needs no SM.  The reference has no multi-GPU
  * code; there is no counterpart. */
 int cueq_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+/* Pushes up to eight pieces of local device memory into other buffers - typically memory of peer GPUs mapped
+ * into this process - with one small kernel (16-byte stores over NVLink; `blocks_per_piece` thread blocks of
+ * 256 threads per piece, 0 = 4).  Asynchronous on `stream`, never blocks the host.  Pieces must be 16-byte
+ * aligned and a multiple of 16 bytes.  No counterpart in the reference (it has no multi-GPU code). */
+typedef struct {
+  void* dst[8];
+  const void* src[8];
+  int64_t bytes[8];
+  int32_t num_pieces;
+  int32_t blocks_per_piece;
+} cueq_push_args;
+int cueq_b200_push(const cueq_push_args* args, void* stream);
+/* Sharing a device buffer with the other processes of the node (CUDA IPC).  export: writes the 64-byte handle of
+ * the allocation containing `ptr` and the offset of `ptr` inside it.  open: maps that allocation for the CURRENT
+ * device (peer access to the exporting GPU is enabled as needed) and returns its base; the pointer is then
+ * base + offset.  close: unmaps.  No counterpart in the reference. */
+int cueq_b200_ipc_export(const void* ptr, void* handle64, int64_t* offset);
+int cueq_b200_ipc_open(const void* handle64, void** base);
+int cueq_b200_ipc_close(void* base);
 /* Enables direct access from the current device to `peer_device` (cudaDeviceEnablePeerAccess; already
  * enabled counts as success), so that the copies above travel over NVLink instead of through the host. */
 int cueq_b200_enable_peer_access(int peer_device);
