@@ -33,6 +33,26 @@ def pair_pattern(l1: int, l2: int, l3: int, major: str) -> List[Tuple[int, int, 
     return out
 
 
+def value_pattern(l1: int, l2: int, l3: int):
+    """The distinct values among the entries ``M[i, k] = sum_j C[i, j, k] x2[j]`` of a coupling, up to sign.
+
+    Many (i, k) pairs carry the same linear combination of x2 (or its negative): for l <= 3 there are 207
+    distinct ones among 311 pairs.  Returns ``(values, pairs)``: ``values[s]`` = the ``(j, coefficient)`` terms of
+    slot ``s`` (first coefficient positive), ``pairs`` = ``(i, k, slot, sign)`` in k-major order with
+    ``M[i, k] = sign * value[slot]``.  The forward kernels broadcast the values instead of the pairs."""
+    values, index, pairs = [], {}, []
+    for i, k, terms in pair_pattern(l1, l2, l3, "k"):
+        t = sorted(terms)
+        sign = 1.0 if t[0][1] > 0 else -1.0
+        key = tuple((j, round(sign * c, 12)) for j, c in t)
+        s = index.get(key)
+        if s is None:
+            s = index[key] = len(values)
+            values.append([(j, sign * c) for j, c in t])
+        pairs.append((i, k, s, sign))
+    return values, pairs
+
+
 SPLIT_GROUPS = False  # measured on B200: one launch per irrep beats two lighter launches
 
 
@@ -232,16 +252,32 @@ def match_channelwise(polynomial) -> Optional[ChannelwisePlan]:
         g = {"id": lib[sig], "x1_off": x1_off[s1], "w_off": [w_off[p[3]] for p in plist],
              "out_off": [out_off[p[4]] for p in plist], "npath": len(plist), "out_segs": [p[4] for p in plist],
              "x1_width": x1_op.segments[s1][0] * x1_op.segments[s1][1], "l1": l1}
-        for name, major in (("fwd_tab", "k"), ("bwd_tab", "i")):
-            start, tj, tc = [0], [], []
-            for l1_, l2, l3, _, _, c in plist:
-                for i, k, terms in pair_pattern(l1_, l2, l3, major):
-                    for j, _ref in terms:
-                        tj.append(x2_off[l2] + j)
-                        tc.append(float(c[i, j, k]))
-                    start.append(len(tj))
-            g[name] = (start, tj, tc)
+        # backward: one table entry per non-zero (i, k) pair, i-major
+        start, tj, tc = [0], [], []
+        for l1_, l2, l3, _, _, c in plist:
+            for i, k, terms in pair_pattern(l1_, l2, l3, "i"):
+                for j, _ref in terms:
+                    tj.append(x2_off[l2] + j)
+                    tc.append(float(c[i, j, k]))
+                start.append(len(tj))
+        g["bwd_tab"] = (start, tj, tc)
+        # forward: one entry per distinct value (see value_pattern); the descriptor's coefficient of a value is
+        # read off the first pair that carries it
+        start, tj, tc = [0], [], []
+        for l1_, l2, l3, _, _, c in plist:
+            values, pairs = value_pattern(l1_, l2, l3)
+            first = {}
+            for i, k, s, sign in pairs:
+                first.setdefault(s, (i, k, sign))
+            for s, terms in enumerate(values):
+                i, k, sign = first[s]
+                for j, _ref in terms:
+                    tj.append(x2_off[l2] + j)
+                    tc.append(sign * float(c[i, j, k]))
+                start.append(len(tj))
+        g["fwd_tab"] = (start, tj, tc)
         g["nterm"] = len(g["bwd_tab"][1])
+        g["nterm_fwd"] = len(g["fwd_tab"][1])
         groups.append(g)
     # every output segment must be produced by exactly one path (else rows would be incomplete)
     if len(seen_o) != out_op.num_segments:
@@ -318,7 +354,7 @@ class _ChannelwiseBase:
             t.extent = plan.extent
             t.x1_offset = g["x1_off"]
             t.num_paths = g["npath"]
-            t.num_terms = g["nterm"]
+            t.num_terms = g["nterm"] if which == "bwd_tab" else g["nterm_fwd"]
             for q in range(g["npath"]):
                 t.w_offset[q] = g["w_off"][q]
                 t.out_offset[q] = g["out_off"][q]

@@ -231,14 +231,17 @@ __device__ __forceinline__ void emit_block(float* base, int extent, int ch, cons
   }
 }
 
-// The channel-independent matrices M of one edge: M[q] = sum_t c[t] * x2[j[t]] for every
-// non-zero (i,k) pair q of the group.  Lane L owns the pairs L, L+32, ...; a pair has at most
-// two terms (true for every coupling with l <= 3), whose coefficients and x2 positions the
-// lane keeps in registers for the whole kernel, so the per-edge work is a handful of
-// shared-memory reads and FMAs without any loop or branch.
-template <class G>
+// The channel-independent matrices M of one edge: M[q] = sum_t c[t] * x2[j[t]] for every table
+// entry q of the group - one per non-zero (i,k) pair in the backward kernels (N = NPAIR), one per
+// distinct value among them in the forward kernels (N = NVAL: many pairs carry the same combination
+// of x2 up to sign, and every entry costs a broadcast read per warp and edge).  Lane L owns the
+// entries L, L+32, ...; an entry has at most two terms (true for every coupling with l <= 3), whose
+// coefficients and x2 positions the lane keeps in registers for the whole kernel, so the per-edge
+// work is a handful of shared-memory reads and FMAs without any loop or branch.
+template <int N>
 struct MTerms {
-  static constexpr int R = (G::NPAIR + 31) / 32;
+  static constexpr int R = (N + 31) / 32;
+  static constexpr int NPAD = (N + 3) / 4 * 4;
   float c[R][2];
   unsigned j[R];  // two 16-bit x2 positions per pair
 
@@ -248,7 +251,7 @@ struct MTerms {
       const int q = lane + 32 * r;
       c[r][0] = c[r][1] = 0.f;
       j[r] = 0;
-      if (q < G::NPAIR) {
+      if (q < N) {
         const int t0 = __ldg(p.tab_start + q), t1 = __ldg(p.tab_start + q + 1);
         if (t1 > t0) { c[r][0] = __ldg(p.tab_c + t0); j[r] = (unsigned)__ldg(p.tab_j + t0); }
         if (t1 > t0 + 1) { c[r][1] = __ldg(p.tab_c + t0 + 1); j[r] |= (unsigned)__ldg(p.tab_j + t0 + 1) << 16; }
@@ -259,7 +262,7 @@ struct MTerms {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const float m = fmaf(c[r][1], x2row[j[r] >> 16], c[r][0] * x2row[j[r] & 0xffffu]);
-      if (G::NPAIR % 32 == 0 || r + 1 < R || lane + 32 * r < G::NPAIR_PAD) M[lane + 32 * r] = m;
+      if (N % 32 == 0 || r + 1 < R || lane + 32 * r < NPAD) M[lane + 32 * r] = m;
     }
   }
 };
@@ -311,7 +314,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const
   float* mine = smem + warp * S::kPerWarpFwd;
   const int ch = blockIdx.y * (32 * C) + C * lane;   // first channel of this lane
   const bool active = ch < p.extent;
-  MTerms<G> mt;
+  MTerms<G::NVAL> mt;
   mt.load(p, lane);
   const unsigned long long pol_stream = policy_evict_first(), pol_keep = policy_evict_last();
 
@@ -415,7 +418,7 @@ __global__ void __launch_bounds__(kWarps * 32, C == 2 ? CW_MINBLOCKS : 2) cw_fwd
   const int ch = c0 + C * lane;
   const bool active = ch < p.extent;
   const int nch = min(S::NCH, p.extent - c0);
-  MTerms<G> mt;
+  MTerms<G::NVAL> mt;
   mt.load(p, lane);
   if (lane == 0) {
     mbar_init(bars + 0, 1);
@@ -523,7 +526,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
   Vec<C>* grow = reinterpret_cast<Vec<C>*>(mine + S::kPerWarpFwd);
   const int ch = blockIdx.y * (32 * C) + C * lane;
   const bool active = ch < p.extent;
-  MTerms<G> mt;
+  MTerms<G::NPAIR> mt;
   mt.load(p, lane);
   const unsigned long long pol_stream = policy_evict_first(), pol_keep = policy_evict_last();
 
@@ -616,7 +619,7 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
   float* stages = mine + S::kM;
   const int ch = blockIdx.y * (32 * C) + C * lane;
   const bool active = ch < p.extent;
-  MTerms<G> mt;
+  MTerms<G::NPAIR> mt;
   mt.load(p, lane);
   const unsigned long long pol_stream = policy_evict_first(), pol_keep = policy_evict_last();
 
@@ -675,7 +678,7 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
 // ---- registry -----------------------------------------------------------------------------------
 struct GroupEntry {
   const char* signature;
-  int d1, npath, npair, nterm, sumd3, nx2;
+  int d1, npath, npair, nterm, sumd3, nx2, nval, nterm_fwd;
   int (*fwd)(const CwParams&, int, int, cudaStream_t);
   int (*bwd)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
   int (*fwd_bulk)(const CwParams&, int, int, cudaStream_t);
@@ -769,7 +772,7 @@ int launch_bwd_block(const CwParams& p, const CwCoef& coef, int mul_ir, cudaStre
   return mul_ir ? launch_bwd_block_t<G, true>(p, coef, st) : launch_bwd_block_t<G, false>(p, coef, st);
 }
 
-#define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, &launch_fwd<G>, &launch_bwd<G>, &launch_fwd_bulk<G>, &launch_bwd_block<G>},
+#define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, G::NVAL, G::NTERM_FWD, &launch_fwd<G>, &launch_bwd<G>, &launch_fwd_bulk<G>, &launch_bwd_block<G>},
 const GroupEntry kGroups[] = {CW_FOR_EACH_GROUP(CW_ENTRY)};
 constexpr int kNumGroups = sizeof(kGroups) / sizeof(kGroups[0]);
 
@@ -778,7 +781,7 @@ int pick_cpl(const cueq_cw_args* a) {
   return a->extent >= 64 ? 2 : 4;
 }
 
-int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p) {
+int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p, int expected_terms) {
   if (!a) return cueq::fail("channelwise: null arguments");
   if (a->extent < 4 || a->extent % 4) return cueq::fail("channelwise: extent %d must be a positive multiple of 4", a->extent);
   if (a->x1_mul_ir != a->out_mul_ir) return cueq::fail("channelwise: x1 and out must use the same layout");
@@ -786,7 +789,7 @@ int fill_params(const cueq_cw_args* a, const GroupEntry& g, CwParams& p) {
   if (a->channels_per_lane != 0 && a->channels_per_lane != 2 && a->channels_per_lane != 4)
     return cueq::fail("channelwise: channels_per_lane must be 0 (auto), 2 or 4");
   if (a->num_paths != g.npath) return cueq::fail("channelwise: group has %d paths, got %d", g.npath, a->num_paths);
-  if (a->num_terms != g.nterm) return cueq::fail("channelwise: group has %d terms, got %d", g.nterm, a->num_terms);
+  if (a->num_terms != expected_terms) return cueq::fail("channelwise: this call's table has %d terms, got %d", expected_terms, a->num_terms);
   if (!a->rowptr || !a->tab_start || !a->tab_j || !a->tab_c) return cueq::fail("channelwise: null table or rowptr");
   if (a->num_receivers < 0) return cueq::fail("channelwise: negative receiver count");
   std::memset(&p, 0, sizeof(p));
@@ -828,7 +831,7 @@ extern "C" int cueq_b200_cw_group_info(int g, int32_t* d1, int32_t* npath, int32
 extern "C" int cueq_b200_cw_forward(int g, const cueq_cw_args* a, void* stream) {
   if (g < 0 || g >= kNumGroups) return cueq::fail("channelwise: group %d out of range", g);
   CwParams p;
-  if (int rc = fill_params(a, kGroups[g], p)) return rc;
+  if (int rc = fill_params(a, kGroups[g], p, kGroups[g].nterm_fwd)) return rc;
   if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise forward: null tensor");
   if (p.num_receivers == 0) return 0;
   p.status = reinterpret_cast<int*>(a->status);
@@ -840,7 +843,7 @@ extern "C" int cueq_b200_cw_forward(int g, const cueq_cw_args* a, void* stream) 
 extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream) {
   if (g < 0 || g >= kNumGroups) return cueq::fail("channelwise: group %d out of range", g);
   CwParams p;
-  if (int rc = fill_params(a, kGroups[g], p)) return rc;
+  if (int rc = fill_params(a, kGroups[g], p, kGroups[g].nterm)) return rc;
   if (!p.w || !p.x1 || !p.x2 || !p.gout) return cueq::fail("channelwise backward: null tensor");
   if (!a->bwd_coef) return cueq::fail("channelwise backward: null coefficient table");
   if (kGroups[g].nterm > kMaxTerms) return cueq::fail("channelwise backward: too many terms");
@@ -920,7 +923,7 @@ extern "C" int cueq_b200_cw_forward_noalloc(int g, const cueq_cw_noalloc_args* a
   if (a->num_receivers > kNoAllocMaxReceivers)
     return cueq::fail("channelwise (no-alloc): %lld receivers exceed the built-in scratch (max %d); use cueq_b200_cw_forward",
                       (long long)a->num_receivers, kNoAllocMaxReceivers);
-  if (ge.npair > kNoAllocMaxPairs || ge.nterm > kNoAllocMaxTerms)
+  if (ge.nval > kNoAllocMaxPairs || ge.nterm_fwd > kNoAllocMaxTerms)
     return cueq::fail("channelwise (no-alloc): group tables exceed the built-in scratch");
   if (a->num_edges < 0 || a->num_edges > 2147483647LL) return cueq::fail("channelwise (no-alloc): invalid edge count");
   if (!a->receivers && a->num_edges > 0) return cueq::fail("channelwise (no-alloc): null receivers");
@@ -951,18 +954,18 @@ extern "C" int cueq_b200_cw_forward_noalloc(int g, const cueq_cw_noalloc_args* a
   for (int q = 0; q < 8; ++q) { full.w_offset[q] = a->w_offset[q]; full.out_offset[q] = a->out_offset[q]; }
   full.x1_mul_ir = a->mul_ir; full.out_mul_ir = a->mul_ir; full.channels_per_lane = 0;
   CwParams p;
-  if (int rc = fill_params(&full, ge, p)) return rc;
+  if (int rc = fill_params(&full, ge, p, ge.nterm_fwd)) return rc;
   if (!p.w || !p.x1 || !p.x2 || !p.out) return cueq::fail("channelwise (no-alloc): null tensor");
   if (p.num_receivers == 0) return 0;
 
   NoAllocTables t;
   std::memset(&t, 0, sizeof(t));
-  for (int i = 0; i <= ge.npair; ++i) t.start[i] = a->tab_start_host[i];
-  for (int i = 0; i < ge.nterm; ++i) { t.j[i] = a->tab_j_host[i]; t.c[i] = a->tab_c_host[i]; }
+  for (int i = 0; i <= ge.nval; ++i) t.start[i] = a->tab_start_host[i];
+  for (int i = 0; i < ge.nterm_fwd; ++i) { t.j[i] = a->tab_j_host[i]; t.c[i] = a->tab_c_host[i]; }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int blocks = (int)((a->num_receivers + 1 + 255) / 256);
-  cw_noalloc_prepare<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(a->receivers, (int)a->num_edges, (int)a->num_receivers, rowptr, t, ge.npair,
-                                                              ge.nterm, tab_start, tab_j, tab_c);
+  cw_noalloc_prepare<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(a->receivers, (int)a->num_edges, (int)a->num_receivers, rowptr, t, ge.nval,
+                                                              ge.nterm_fwd, tab_start, tab_j, tab_c);
   CUEQ_CUDA_OK(cudaGetLastError());
   return ge.fwd(p, a->mul_ir, pick_cpl(&full), st);
 }

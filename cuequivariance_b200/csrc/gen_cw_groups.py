@@ -27,7 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 import numpy as np  # noqa: E402
 
-from cuequivariance_b200.channelwise import group_signature as _signature, pair_pattern, split_group  # noqa: E402
+from cuequivariance_b200.channelwise import group_signature as _signature, pair_pattern, split_group, value_pattern  # noqa: E402
 
 # Groups to build: (l1, [(l2, l3), ...]).  The list below is the family used by MACE-style
 # models: second operand 0e+1o+..+L2 (spherical harmonics), outputs filtered to natural
@@ -66,6 +66,9 @@ def emit_group(l1: int, paths) -> str:
     out_off = np.concatenate([[0], np.cumsum(d3s)]).tolist()
     ptot = pair_off[-1]
     ptot_pad = (ptot + 3) // 4 * 4
+    vals = [value_pattern(l1, l2, l3) for l2, l3 in paths]
+    val_off = np.concatenate([[0], np.cumsum([len(v) for v, _ in vals])]).tolist()
+    fwd_terms = sum(len(t) for v, _ in vals for t in v)
     L = []
     A = L.append
     A(f"struct {name} {{")
@@ -74,6 +77,8 @@ def emit_group(l1: int, paths) -> str:
     A(f"  static constexpr int NPATH = {len(paths)};")
     A(f"  static constexpr int NPAIR = {ptot};")
     A(f"  static constexpr int NPAIR_PAD = {ptot_pad};")
+    A(f"  static constexpr int NVAL = {val_off[-1]};      // distinct values among the M entries (forward table)")
+    A(f"  static constexpr int NTERM_FWD = {fwd_terms};")
     A(f"  static constexpr int SUMD3 = {out_off[-1]};")
     A(f"  static constexpr int MAXD3 = {max(d3s)};")
     A(f"  static constexpr int NX2 = {max(l2 for l2, _ in paths) ** 2 + 2 * max(l2 for l2, _ in paths) + 1};")
@@ -83,19 +88,19 @@ def emit_group(l1: int, paths) -> str:
     A("  __host__ __device__ static constexpr int pair_offset(int p) { constexpr int t[NPATH + 1] = {%s}; return t[p]; }" % ", ".join(map(str, pair_off)))
 
     # ---- forward ------------------------------------------------------------------------
-    A("  // acc[out_offset(p) + k][c] += W[p][c] * sum_i M[q(i,k)] * X[i][c]")
+    A("  // acc[out_offset(p) + k][c] += W[p][c] * sum_i (+-)V[slot(i,k)] * X[i][c];  V = the distinct values of M")
     A("  template <int P, int C>")
     A("  __device__ __forceinline__ static void fwd_path(const float (&X)[D1][C], const float (&W)[C], const float* __restrict__ M,")
     A("                                                  float (&acc)[SUMD3][C]) {")
     for p, (pat, d3) in enumerate(zip(pats, d3s)):
         A(f"    if constexpr (P == {p}) {{")
-        # load the M entries of this path as float4 where aligned
-        q0 = pair_off[p]
-        A(f"      float m[{len(pat)}];")
-        A(f"      cw_load_m<{q0}, {len(pat)}>(M, m);")
+        # load the distinct values of this path as float4 where aligned
+        values, vpairs = vals[p]
+        A(f"      float m[{len(values)}];")
+        A(f"      cw_load_m<{val_off[p]}, {len(values)}>(M, m);")
         by_i2: dict[int, list] = {}
-        for q, (i, k, _) in enumerate(pat):
-            by_i2.setdefault(i, []).append((q, k))
+        for (i, k, s, sign) in vpairs:
+            by_i2.setdefault(i, []).append((("-" if sign < 0 else "") + f"m[{s}]", k))
         if d1 < d3:
             # fewer input than output components: scale the inputs by the weight once (d1 multiplies)
             # and add every product straight into its accumulator, instead of summing unweighted
@@ -105,7 +110,7 @@ def emit_group(l1: int, paths) -> str:
                 A(f"      CW_MULV4(xw[{i}], W, X[{i}]);")
             for i in sorted(by_i2):
                 for q, k in by_i2[i]:
-                    A(f"      CW_FMA4(acc[{out_off[p] + k}], m[{q}], xw[{i}]);")
+                    A(f"      CW_FMA4(acc[{out_off[p] + k}], {q}, xw[{i}]);")
         else:
             # i-major emission: consecutive multiply-adds go to different accumulators t[k], so that
             # the chains over i of the d3 outputs interleave instead of running one after the other
@@ -114,10 +119,10 @@ def emit_group(l1: int, paths) -> str:
             for i in sorted(by_i2):
                 for q, k in by_i2[i]:
                     if k in seen_k:
-                        A(f"      CW_FMA4(t[{k}], m[{q}], X[{i}]);")
+                        A(f"      CW_FMA4(t[{k}], {q}, X[{i}]);")
                     else:
                         seen_k.add(k)
-                        A(f"      CW_MUL4(t[{k}], m[{q}], X[{i}]);")
+                        A(f"      CW_MUL4(t[{k}], {q}, X[{i}]);")
             for k in range(d3):
                 if k in seen_k:
                     A(f"      CW_FMAV4(acc[{out_off[p] + k}], W, t[{k}]);")

@@ -180,9 +180,11 @@ int cueq_b200_sh_backward(const cueq_sh_args* args, void* stream);
  * Edges are addressed through a CSR over receivers: rowptr[n]..rowptr[n+1] are the positions
  * of receiver n, order[pos] the edge id at a position (NULL: positions are edge ids, i.e. the
  * edge list is sorted by receiver), senders[edge] the x1 row (NULL: the edge id).
- * The tables describe M[i,k] = sum_j C[i,j,k] x2[j]: pair q owns terms tab_start[q]..tab_start[q+1],
- * each term a coefficient tab_c[t] and an x2 element tab_j[t]; pairs are ordered path by path,
- * k-major for the forward call and i-major for the backward call.  bwd_coef (host memory,
+ * The tables describe M[i,k] = sum_j C[i,j,k] x2[j]: entry q owns terms tab_start[q]..tab_start[q+1],
+ * each term a coefficient tab_c[t] and an x2 element tab_j[t].  Backward call: one entry per non-zero
+ * (i,k) pair, path by path, i-major.  Forward call: one entry per DISTINCT value among a path's pairs
+ * (pairs that carry the same combination of x2 up to sign share an entry; order of first appearance in
+ * k-major order, first coefficient positive - cuequivariance_b200/channelwise.py:value_pattern).  bwd_coef (host memory,
  * num_terms floats) lists the coefficients in the backward term order. */
 typedef struct {
   const void* w;        /* [E, w_stride]    per-edge weights                                  */
@@ -463,7 +465,7 @@ typedef struct {
   void* out;
   const int32_t* senders;        /* device, [num_edges]; NULL: x1 row = edge id                     */
   const int32_t* receivers;      /* device, [num_edges], sorted ascending, values in [0, num_receivers) */
-  const int32_t* tab_start_host; /* host, [num_pairs + 1] (k-major pair order, as for cw_forward)    */
+  const int32_t* tab_start_host; /* host, [entries + 1] (the forward table of cw_forward)             */
   const int32_t* tab_j_host;     /* host, [num_terms]                                                */
   const float* tab_c_host;       /* host, [num_terms]                                                */
   int64_t w_stride, x1_stride, x2_stride, out_stride;

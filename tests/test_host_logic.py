@@ -30,10 +30,14 @@ def test_channelwise_plan_for_the_headline_configuration():
     out_offs = sorted(o for g in plan.groups for o in g["out_off"])
     assert len(set(out_offs)) == 23 and out_offs[0] == 0
     assert sum(g["nterm"] for g in plan.groups) == 353
-    pairs = sum(len(g["fwd_tab"][0]) - 1 for g in plan.groups)
-    assert pairs == 311
-    for g in plan.groups:   # forward and backward tables hold the same terms in different orders
-        assert sorted(zip(g["fwd_tab"][1], np.round(g["fwd_tab"][2], 12))) == sorted(zip(g["bwd_tab"][1], np.round(g["bwd_tab"][2], 12)))
+    assert sum(len(g["bwd_tab"][0]) - 1 for g in plan.groups) == 311          # non-zero (i, k) pairs (backward table)
+    assert sum(len(g["fwd_tab"][0]) - 1 for g in plan.groups) == 207          # distinct values among them (forward table)
+    for g in plan.groups:   # every backward entry is plus or minus one forward entry
+        fwd = {tuple(sorted(zip(g["fwd_tab"][1][a:b], np.round(g["fwd_tab"][2][a:b], 12)))) for a, b in zip(g["fwd_tab"][0][:-1], g["fwd_tab"][0][1:])}
+        for a, b in zip(g["bwd_tab"][0][:-1], g["bwd_tab"][0][1:]):
+            terms = sorted(zip(g["bwd_tab"][1][a:b], np.round(g["bwd_tab"][2][a:b], 12)))
+            neg = sorted((j, -c) for j, c in terms)
+            assert tuple(terms) in fwd or tuple(neg) in fwd
     lib = cw._library_groups()
     assert all(0 <= g["id"] < _lib.lib().cueq_b200_cw_num_groups() for g in plan.groups) and len(lib) >= 4
 

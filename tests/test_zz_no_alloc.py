@@ -33,7 +33,7 @@ def _run_noalloc(plan, layout_mul_ir, w, x1, x2, senders, receivers, n_recv):
         a.tab_start_host, a.tab_j_host, a.tab_c_host = keep
         a.w_stride, a.x1_stride, a.x2_stride, a.out_stride = plan.row_sizes
         a.num_edges, a.num_receivers = receivers.numel(), n_recv
-        a.extent, a.x1_offset, a.num_paths, a.num_terms = plan.extent, g["x1_off"], g["npath"], g["nterm"]
+        a.extent, a.x1_offset, a.num_paths, a.num_terms = plan.extent, g["x1_off"], g["npath"], g["nterm_fwd"]
         for q in range(g["npath"]):
             a.w_offset[q], a.out_offset[q] = g["w_off"][q], g["out_off"][q]
         a.mul_ir = 1 if layout_mul_ir else 0
