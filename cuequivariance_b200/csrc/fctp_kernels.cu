@@ -127,47 +127,64 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid
   float* T = xs2 + p.d2 * p.V;
   float* S = T + p.d3 * p.d1 * p.V;
   float* g2 = S + p.d3 * p.d2 * p.U;   // [d2*V] block-level accumulator of gx2
+  float* g1 = g2 + p.d2 * p.V;         // [d1*U] block-level accumulator of gx1
   const TZ* GZ = reinterpret_cast<const TZ*>(p.z);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  // a thread owns one v for the whole sample and walks a share of the u range: its x2-gradient partials stay
+  // in registers over u (no shared atomics in the inner loop), the x1-gradient partials of a row u are summed
+  // over v with warp shuffles
+  const int vwarps = (p.V + 31) / 32;                          // warps that together cover the v axis
+  const int ugroups = nwarps / vwarps > 0 ? nwarps / vwarps : 1;
+  const int v = (warp % vwarps) * 32 + lane;
+  const int ug = warp / vwarps;
+  const bool v_ok = v < p.V && ug < ugroups;
   for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
     __syncthreads();
     load_sample<TX>(p, z, xs1, xs2);
     for (int t = threadIdx.x; t < p.d2 * p.V; t += blockDim.x) g2[t] = 0.f;
+    for (int t = threadIdx.x; t < p.d1 * p.U; t += blockDim.x) g1[t] = 0.f;
     __syncthreads();
     contract_T(p, xs2, T);
     contract_S(p, xs1, S);
     __syncthreads();
-    // a warp owns rows u = warp, warp + nwarps, ...; lanes run along v
-    for (int u = warp; u < p.U; u += nwarps) {
-      float a1[kMaxD];
+    float a2[kMaxD];
 #pragma unroll
-      for (int i = 0; i < kMaxD; ++i) a1[i] = 0.f;
-      for (int v = lane; v < p.V; v += 32) {
-        float a2[kMaxD];
+    for (int j = 0; j < kMaxD; ++j) a2[j] = 0.f;
+    if (ug < ugroups) {
+      for (int u = ug; u < p.U; u += ugroups) {
+        float a1[kMaxD];
 #pragma unroll
-        for (int j = 0; j < kMaxD; ++j) a2[j] = 0.f;
-        for (int k = 0; k < p.d3; ++k) {
-          const float g = ldf<TZ>(GZ, (z * p.d3 + k) * p.ldz + u * p.V + v);
+        for (int i = 0; i < kMaxD; ++i) a1[i] = 0.f;
+        if (v_ok) {
+          for (int k = 0; k < p.d3; ++k) {
+            const float g = ldf<TZ>(GZ, (z * p.d3 + k) * p.ldz + u * p.V + v);
 #pragma unroll
-          for (int i = 0; i < kMaxD; ++i)
-            if (i < p.d1) a1[i] = fmaf(g, T[(k * p.d1 + i) * p.V + v], a1[i]);
+            for (int i = 0; i < kMaxD; ++i)
+              if (i < p.d1) a1[i] = fmaf(g, T[(k * p.d1 + i) * p.V + v], a1[i]);
 #pragma unroll
-          for (int j = 0; j < kMaxD; ++j)
-            if (j < p.d2) a2[j] = fmaf(g, S[(k * p.d2 + j) * p.U + u], a2[j]);
+            for (int j = 0; j < kMaxD; ++j)
+              if (j < p.d2) a2[j] = fmaf(g, S[(k * p.d2 + j) * p.U + u], a2[j]);
+          }
         }
+#pragma unroll
+        for (int i = 0; i < kMaxD; ++i) {
+          if (i < p.d1) {
+            const float tot = cueq::warp_sum(a1[i]);
+            if (lane == 0) {
+              if (vwarps == 1) g1[i * p.U + u] = tot; else atomicAdd(g1 + i * p.U + u, tot);
+            }
+          }
+        }
+      }
+      if (v_ok) {
 #pragma unroll
         for (int j = 0; j < kMaxD; ++j)
           if (j < p.d2) atomicAdd(g2 + j * p.V + v, a2[j]);
       }
-#pragma unroll
-      for (int i = 0; i < kMaxD; ++i) {
-        if (i < p.d1) {
-          const float tot = cueq::warp_sum(a1[i]);
-          if (lane == 0 && p.gx1) p.gx1[z * p.ld1 + p.off1 + i * p.U + u] += tot;
-        }
-      }
     }
     __syncthreads();
+    if (p.gx1)
+      for (int t = threadIdx.x; t < p.d1 * p.U; t += blockDim.x) p.gx1[z * p.ld1 + p.off1 + t] += g1[t];
     if (p.gx2)
       for (int t = threadIdx.x; t < p.d2 * p.V; t += blockDim.x) p.gx2[z * p.ld2 + p.off2 + t] += g2[t];
   }
@@ -217,7 +234,7 @@ extern "C" int cueq_b200_fctp_consume_gz(const cueq_fctp_args* a, void* stream) 
   if (p.batch == 0) return 0;
   if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
   if (a->z_dtype != CUEQ_F32 && a->z_dtype != CUEQ_BF16) return cueq::fail("fctp: gZ must be float32 or bfloat16");
-  const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V + p.d3 * p.d2 * p.U + p.d2 * p.V);
+  const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V + p.d3 * p.d2 * p.U + p.d2 * p.V + p.d1 * p.U);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const unsigned grid = grid_for(p.batch);
   const bool xb = a->x_dtype == CUEQ_BF16, zb = a->z_dtype == CUEQ_BF16;
