@@ -203,8 +203,8 @@ import os as _os
 _DIAG_SKIP_COPY = bool(_os.environ.get("CUEQ_DIAG_SKIP_COPY"))
 _DIAG_SKIP_HANDSHAKE = bool(_os.environ.get("CUEQ_DIAG_SKIP_HANDSHAKE"))
 PUSH_BLOCKS = int(_os.environ.get("CUEQ_PUSH_BLOCKS", "4"))      # thread blocks per (peer, irrep block) piece of the push kernel
-PUSH_MODE = _os.environ.get("CUEQ_PUSH_MODE", "kernel")   # "kernel": the push kernel; "memcpy": one cudaMemcpyAsync per piece
-EXCHANGE = "peer_copy"   # how the pipelined path moves node rows between ranks: "peer_copy" (copy engines) or "nccl"
+PUSH_MODE = _os.environ.get("CUEQ_PUSH_MODE", "memcpy")   # "memcpy": one cudaMemcpyAsync per piece (copy engines); "kernel": the push kernel
+EXCHANGE = _os.environ.get("CUEQ_EXCHANGE", "nccl")       # how the pipelined path moves node rows between ranks: "nccl" or "peer_copy"
 
 
 class PeerExchange:

@@ -1,6 +1,6 @@
 """Two-GPU parity of the receiver-sharded channelwise product against the single-GPU call: the
-pipelined path with the rows moved by the copy engines over peer-mapped buffers, the same path
-with NCCL all-gather / reduce-scatter, and the plain path.  Every variant runs three steps in a
+pipelined path with the rows pushed into peer-mapped buffers (by the copy engines and by the push
+kernel), the same path with NCCL all-gather / reduce-scatter, and the plain path.  Every variant runs three steps in a
 row (the exchange buffers are reused from step to step).  Skipped on boxes with fewer than two
 GPUs."""
 import os
@@ -54,8 +54,8 @@ def _worker(rank, world, port, results):
         lo, hi = shard_bounds(N, world, rank)
         e0, e1 = shard_edges(rcv, N, world, rank)
         ok = True
-        for pipelined, exchange in ((True, "peer_copy"), (True, "nccl"), (False, "nccl")):
-            distributed.EXCHANGE = exchange
+        for pipelined, exchange, push in ((True, "peer_copy", "memcpy"), (True, "peer_copy", "kernel"), (True, "nccl", ""), (False, "nccl", "")):
+            distributed.EXCHANGE, distributed.PUSH_MODE = exchange, push or distributed.PUSH_MODE
             op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD, pipelined=pipelined)
             for step in range(3):
                 scale_in = 1.0 + step    # different data every step: a stale buffer would show
