@@ -479,10 +479,22 @@ def main():
             traffic_note = rec.get("source", "")
     except (OSError, ValueError, KeyError):
         pass
+    # the same launch counted in float32 arithmetic: issued multiply-adds and multiplies per edge (from the ncu
+    # capture on record) over the launch time, against the measured multiply-add peak of the CUDA cores
+    fp32 = None
+    try:
+        per_edge = rec["fp32_instr_per_edge"].get(dom) if rec.get("source_digest") == kernel_source_digest() else None
+        if per_edge:
+            flop = 32.0 * (2.0 * per_edge["ffma"] + per_edge["fmul"]) * El
+            tf = flop / (kernels[dom]["ms"] * 1e-3) / 1e12
+            fp32 = {"achieved": tf, "peak": rec["fp32_peak_tflops"], "unit": "TFLOP/s", "frac": tf / rec["fp32_peak_tflops"],
+                    "flop_per_edge": flop / El, "source": rec.get("fp32_source", ""), "peak_source": rec.get("fp32_peak_source", "")}
+    except (NameError, KeyError, TypeError):
+        pass
     roofline = None
     if dom:
         roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": kernels[dom]["gbs"] / peak, "traffic": traffic, "traffic_note": traffic_note, "peak_source": peak_src,
+                    "frac": kernels[dom]["gbs"] / peak, "traffic": traffic, "traffic_note": traffic_note, "peak_source": peak_src, "fp32": fp32,
                     "all_kernels": {k: {"ms": round(v["ms"], 4), "gbs": round(v["gbs"], 1)} for k, v in kernels.items()},
                     "step_algorithmic_gbs": total_bytes / (total_kernel_ms * 1e-3) / 1e9 if total_kernel_ms else None,
                     "step_frac": (total_bytes / (ms * 1e-3) / 1e9) / peak}

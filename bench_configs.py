@@ -53,16 +53,18 @@ def _time(step, steps, warmup=3):
     return ms, launches, kernels
 
 
-def fma_peak(steps, dev):
-    """float32 FMA peak: 148 x 32 blocks of 256 threads, 16 independent chains each."""
+def fma_peak(steps, dev, packed=False):
+    """float32 FMA peak: 148 x 32 blocks of 256 threads, 16 independent chains each (`packed`: the same
+    arithmetic issued as float32x2 instructions)."""
     import ctypes as C
 
     from cuequivariance_b200 import _lib
 
     sink = torch.zeros(1, device=dev)
     blocks, iters = 148 * 32, 20000
-    fn = lambda: _lib.check(_lib.lib().cueq_b200_selftest_fma_peak(C.c_void_p(sink.data_ptr()), blocks, iters,  # noqa: E731
-                                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    entry = _lib.lib().cueq_b200_selftest_fma2_peak if packed else _lib.lib().cueq_b200_selftest_fma_peak
+    fn = lambda: _lib.check(entry(C.c_void_p(sink.data_ptr()), blocks, iters,  # noqa: E731
+                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     for _ in range(3):
         fn()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -72,7 +74,8 @@ def fma_peak(steps, dev):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    return {"config": "fma", "what": "float32 multiply-add peak (register-resident chains)", "ms_per_step": ms,
+    return {"config": "fma2" if packed else "fma",
+            "what": "float32 multiply-add peak (register-resident chains" + (", packed float32x2 instructions)" if packed else ")"), "ms_per_step": ms,
             "tflops": 2.0 * blocks * 256 * 16 * iters / ms / 1e9}
 
 
@@ -178,8 +181,8 @@ def main():
            "2": lambda steps, dev: config2(steps, dev, torch.float32, a.batch or 32768),
            "2bf16": lambda steps, dev: config2(steps, dev, torch.bfloat16, a.batch or 32768),
            "4": lambda steps, dev: config4(steps, dev, a.edges, a.nodes),
-           "fma": fma_peak}
-    for key in ([k for k in fns if k != "fma"] if a.config == "all" else [a.config]):
+           "fma": fma_peak, "fma2": lambda steps, dev: fma_peak(steps, dev, packed=True)}
+    for key in ([k for k in fns if not k.startswith("fma")] if a.config == "all" else [a.config]):
         print(json.dumps(fns[key](a.steps, dev)), flush=True)
 
 

@@ -211,6 +211,7 @@ def lib() -> C.CDLL:
     L.cueq_b200_cw_group_signature.restype = C.c_char_p
     L.cueq_b200_cw_group_info.argtypes = [C.c_int] + [C.POINTER(C.c_int32)] * 4
     L.cueq_b200_selftest_fma_peak.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    L.cueq_b200_selftest_fma2_peak.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     L.cueq_b200_check_index_range.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
     L.cueq_b200_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     L.cueq_b200_enable_peer_access.argtypes = [C.c_int]

@@ -268,23 +268,31 @@ struct MTerms {
 };
 
 // asynchronous loads of everything edge `pos` needs into the stage at `st`; returns the edge id
+// The edge id (through the optional permutation) and the sender of the edge at position `pos`: two dependent
+// index loads.  The kernels request them one edge earlier than they issue that edge's copies, so that their
+// latency is hidden behind the arithmetic of an edge instead of being waited for in front of the copies.
+struct EdgeIds { int eid, snd; };
+__device__ __forceinline__ EdgeIds load_ids(const CwParams& p, int pos) {
+  EdgeIds e;
+  e.eid = p.order ? __ldg(p.order + pos) : pos;
+  e.snd = p.senders ? __ldg(p.senders + e.eid) : e.eid;
+  return e;
+}
+
 template <class G, int C, bool X1_MUL_IR>
-__device__ __forceinline__ int issue_edge(const CwParams& p, float* st, int pos, int ch, int lane, bool active,
-                                          unsigned long long pol_stream, unsigned long long pol_keep) {
-  const int eid = p.order ? __ldg(p.order + pos) : pos;
+__device__ __forceinline__ void issue_edge_ids(const CwParams& p, float* st, const EdgeIds ids, int ch, int lane, bool active,
+                                               unsigned long long pol_stream, unsigned long long pol_keep) {
   float* x2s = st;
   Vec<C>* stage = reinterpret_cast<Vec<C>*>(x2s + Smem<G, C>::kX2);
-  if (lane < (G::NX2 + 3) / 4) cp_async_hint<16>(x2s + 4 * lane, p.x2 + (int64_t)eid * p.x2_stride + 4 * lane, pol_stream);
+  if (lane < (G::NX2 + 3) / 4) cp_async_hint<16>(x2s + 4 * lane, p.x2 + (int64_t)ids.eid * p.x2_stride + 4 * lane, pol_stream);
   if (active) {
-    const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-    stage_block_hint<G::D1, C, X1_MUL_IR>(stage, p.x1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, lane, pol_keep);
-    const float* wrow = p.w + (int64_t)eid * p.w_stride + ch;
+    stage_block_hint<G::D1, C, X1_MUL_IR>(stage, p.x1 + (int64_t)ids.snd * p.x1_stride + p.x1_off, p.extent, ch, lane, pol_keep);
+    const float* wrow = p.w + (int64_t)ids.eid * p.w_stride + ch;
     Vec<C>* wst = stage + G::D1 * 32;
 #pragma unroll
     for (int q = 0; q < G::NPATH; ++q) cp_async_hint<4 * C>(wst + q * 32 + lane, wrow + p.w_off[q], pol_stream);
   }
   cp_async_commit();
-  return eid;
 }
 
 template <class G, int C, int P>
@@ -328,11 +336,14 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_fwd_kernel(const
       for (int c = 0; c < C; ++c) acc[a][c] = 0.f;
     float* Msm = mine;
     float* stages = mine + S::kM;
-    if (beg < end) issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active, pol_stream, pol_keep);
+    EdgeIds ahead = {0, 0};                                        // ids of the edge whose copies are issued next
+    if (beg < end) issue_edge_ids<G, C, MUL_IR>(p, stages, load_ids(p, beg), ch, lane, active, pol_stream, pol_keep);
+    if (beg + 1 < end) ahead = load_ids(p, beg + 1);
     for (int pos = beg; pos < end; ++pos) {
       float* st = stages + ((pos - beg) & 1) * S::kPerStage;
       if (pos + 1 < end) {
-        issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active, pol_stream, pol_keep);
+        issue_edge_ids<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, ahead, ch, lane, active, pol_stream, pol_keep);
+        if (pos + 2 < end) ahead = load_ids(p, pos + 2);           // used in the next trip
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
@@ -539,16 +550,21 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
     cp_async_commit();
     float* Msm = mine;
     float* stages = mine + S::kM;
-    int eid = 0, eid_next = issue_edge<G, C, MUL_IR>(p, stages, beg, ch, lane, active, pol_stream, pol_keep);
+    EdgeIds cur = {0, 0}, next = load_ids(p, beg), ahead = {0, 0};
+    issue_edge_ids<G, C, MUL_IR>(p, stages, next, ch, lane, active, pol_stream, pol_keep);
+    if (beg + 1 < end) ahead = load_ids(p, beg + 1);
     for (int pos = beg; pos < end; ++pos) {
       float* st = stages + ((pos - beg) & 1) * S::kPerStage;
-      eid = eid_next;
+      cur = next;
       if (pos + 1 < end) {
-        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, pos + 1, ch, lane, active, pol_stream, pol_keep);
+        next = ahead;
+        issue_edge_ids<G, C, MUL_IR>(p, stages + ((pos + 1 - beg) & 1) * S::kPerStage, next, ch, lane, active, pol_stream, pol_keep);
+        if (pos + 2 < end) ahead = load_ids(p, pos + 2);           // used in the next trip
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
       }
+      const int eid = cur.eid;
       __syncwarp();
       mt.compute(Msm, st, lane);
       __syncwarp();
@@ -565,8 +581,7 @@ __global__ void __launch_bounds__(kWarps * 32, CW_MINBLOCKS) cw_bwd_kernel(const
           for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
         BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
-          const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
+          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)cur.snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
         }
       }
       if (p.need_gx2) {
@@ -631,20 +646,28 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
     if (active) StageGSplit<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)nrow * p.out_stride, p, ch, lane, warp);
     cp_async_commit();
     int pos = beg + warp;
-    int eid = 0, eid_next = 0;
-    if (pos < end) eid_next = issue_edge<G, C, MUL_IR>(p, stages, pos, ch, lane, active, pol_stream, pol_keep);
-    else cp_async_commit();
+    EdgeIds cur = {0, 0}, next = {0, 0}, ahead = {0, 0};
+    if (pos < end) {
+      next = load_ids(p, pos);
+      issue_edge_ids<G, C, MUL_IR>(p, stages, next, ch, lane, active, pol_stream, pol_keep);
+    } else {
+      cp_async_commit();
+    }
+    if (pos + kWarps < end) ahead = load_ids(p, pos + kWarps);
     cp_async_wait<1>();                                            // this thread's share of the cotangent row has landed
     __syncthreads();                                               // ... and everybody else's
     for (int it = 0; pos < end; pos += kWarps, ++it) {
       float* st = stages + (it & 1) * kStage;
-      eid = eid_next;
+      cur = next;
       if (pos + kWarps < end) {
-        eid_next = issue_edge<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, pos + kWarps, ch, lane, active, pol_stream, pol_keep);
+        next = ahead;
+        issue_edge_ids<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, next, ch, lane, active, pol_stream, pol_keep);
+        if (pos + 2 * kWarps < end) ahead = load_ids(p, pos + 2 * kWarps);   // used in the next trip
         cp_async_wait<1>();
       } else {
         cp_async_wait<0>();
       }
+      const int eid = cur.eid;
       __syncwarp();
       mt.compute(Msm, st, lane);
       __syncwarp();
@@ -661,8 +684,7 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
           for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
         BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
         if (p.need_gx1) {
-          const int snd = p.senders ? __ldg(p.senders + eid) : eid;
-          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
+          emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)cur.snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
         }
       }
       if (p.need_gx2) {

@@ -15,6 +15,7 @@
 // to Z / gZ is a contiguous 128-byte row segment.
 #include <cuda_bf16.h>
 
+#include <cstdint>
 #include <cstring>
 
 #include "common.cuh"
@@ -190,6 +191,216 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid
   }
 }
 
+// ---- float32 operands, irrep dimensions known at compile time -------------------------------------
+//
+// The two kernels above keep every loop bound in a register: their inner loops carry predicated-off
+// multiply-adds for the unused part of the 7-wide unrolling, load one 4-byte element of Z / gZ per
+// thread at a time and spend as many instructions on index arithmetic as on the contraction.  For
+// the float32 route (x and Z both float32, V a power of two) the kernels below are instantiated per
+// (d1, d2, d3): a thread owns four consecutive v (one 16-byte access to Z / gZ per (k, u), all d3
+// rows of a u requested before the first is used), groups of V/4 threads share a u, and the sums
+// over v are taken by shuffles inside such a group.
+__host__ __device__ constexpr int pad4(int n) { return (n + 3) & ~3; }
+
+template <int D1, int D2, int D3>
+struct FastSmem {
+  // float offsets inside dynamic shared memory; every block starts on a 16-byte boundary
+  __host__ __device__ static int xs1(int, int) { return 0; }
+  __host__ __device__ static int xs2(int U, int) { return pad4(D1 * U); }
+  __host__ __device__ static int cg(int U, int V) { return xs2(U, V) + pad4(D2 * V); }
+  __host__ __device__ static int T(int U, int V) { return cg(U, V) + pad4(D1 * D2 * D3); }
+  __host__ __device__ static int S(int U, int V) { return T(U, V) + D3 * D1 * V; }          // V % 4 == 0
+  __host__ __device__ static int g2(int U, int V) { return S(U, V) + pad4(D3 * D2 * U); }
+  __host__ __device__ static int g1(int U, int V) { return g2(U, V) + D2 * V; }
+  __host__ __device__ static int build_floats(int U, int V) { return S(U, V); }
+  __host__ __device__ static int consume_floats(int U, int V) { return g1(U, V) + pad4(D1 * U); }
+};
+
+template <int D1, int D2, int D3>
+__device__ __forceinline__ void fast_prologue(const FctpParams& p, int64_t z, float* sm, int vshift, bool with_S) {
+  using L = FastSmem<D1, D2, D3>;
+  float* xs1 = sm + L::xs1(p.U, p.V);
+  float* xs2 = sm + L::xs2(p.U, p.V);
+  const float* cg = sm + L::cg(p.U, p.V);
+  load_sample<float>(p, z, xs1, xs2);
+  __syncthreads();
+  float* T = sm + L::T(p.U, p.V);
+  for (int t = threadIdx.x; t < D3 * D1 * p.V; t += blockDim.x) {
+    const int v = t & (p.V - 1), ki = t >> vshift, i = ki % D1, k = ki / D1;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < D2; ++j) acc = fmaf(cg[(i * D2 + j) * D3 + k], xs2[j * p.V + v], acc);
+    T[t] = acc;
+  }
+  if (with_S) {
+    float* S = sm + L::S(p.U, p.V);
+    for (int t = threadIdx.x; t < D3 * D2 * p.U; t += blockDim.x) {
+      const int u = t % p.U, kj = t / p.U, j = kj % D2, k = kj / D2;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < D1; ++i) acc = fmaf(cg[(i * D2 + j) * D3 + k], xs1[i * p.U + u], acc);
+      S[t] = acc;
+    }
+  }
+}
+
+template <int D1, int D2, int D3>
+__global__ void __launch_bounds__(kThreadsF) fctp_build_z_f32_kernel(const __grid_constant__ FctpParams p) {
+  using L = FastSmem<D1, D2, D3>;
+  extern __shared__ __align__(16) float sm[];
+  const int vshift = __ffs(p.V) - 1, gshift = vshift - 2;     // V = 1 << vshift; a u is shared by V/4 threads
+  const int vq = threadIdx.x & ((1 << gshift) - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsF >> gshift;
+  for (int t = threadIdx.x; t < D1 * D2 * D3; t += blockDim.x) sm[L::cg(p.U, p.V) + t] = p.cg[t];
+  const float* xs1 = sm + L::xs1(p.U, p.V);
+  const float* T = sm + L::T(p.U, p.V);
+  float* Z = reinterpret_cast<float*>(p.z);
+  for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
+    __syncthreads();
+    fast_prologue<D1, D2, D3>(p, z, sm, vshift, false);
+    __syncthreads();
+#pragma unroll 1
+    for (int k = 0; k < D3; ++k) {
+      float4 tt[D1];
+#pragma unroll
+      for (int i = 0; i < D1; ++i) tt[i] = *reinterpret_cast<const float4*>(T + (k * D1 + i) * p.V + 4 * vq);
+      float* zrow = Z + (z * D3 + k) * p.ldz + 4 * vq;
+      for (int u = ug; u < p.U; u += ugroups) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < D1; ++i) {
+          const float xi = xs1[i * p.U + u];
+          a.x = fmaf(tt[i].x, xi, a.x); a.y = fmaf(tt[i].y, xi, a.y);
+          a.z = fmaf(tt[i].z, xi, a.z); a.w = fmaf(tt[i].w, xi, a.w);
+        }
+        *reinterpret_cast<float4*>(zrow + (int64_t)u * p.V) = a;
+      }
+    }
+  }
+}
+
+template <int D1, int D2, int D3>
+__global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_f32_kernel(const __grid_constant__ FctpParams p) {
+  using L = FastSmem<D1, D2, D3>;
+  extern __shared__ __align__(16) float sm[];
+  const int vshift = __ffs(p.V) - 1, gshift = vshift - 2;
+  const int gsize = 1 << gshift;
+  const int vq = threadIdx.x & (gsize - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsF >> gshift;
+  for (int t = threadIdx.x; t < D1 * D2 * D3; t += blockDim.x) sm[L::cg(p.U, p.V) + t] = p.cg[t];
+  const float* T = sm + L::T(p.U, p.V);
+  const float* S = sm + L::S(p.U, p.V);
+  float* g2 = sm + L::g2(p.U, p.V);
+  float* g1 = sm + L::g1(p.U, p.V);
+  const float* GZ = reinterpret_cast<const float*>(p.z);
+  for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
+    __syncthreads();
+    for (int t = threadIdx.x; t < D2 * p.V; t += blockDim.x) g2[t] = 0.f;
+    fast_prologue<D1, D2, D3>(p, z, sm, vshift, true);
+    __syncthreads();
+    float a2[D2][4];
+#pragma unroll
+    for (int j = 0; j < D2; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a2[j][c] = 0.f;
+    // every thread makes the same number of trips, so the shuffles below always see the full warp
+    for (int u0 = 0; u0 < p.U; u0 += ugroups) {
+      const int u = u0 + ug;
+      const bool ok = u < p.U;
+      float4 g[D3];
+#pragma unroll
+      for (int k = 0; k < D3; ++k)
+        g[k] = ok ? __ldcs(reinterpret_cast<const float4*>(GZ + (z * D3 + k) * p.ldz + (int64_t)u * p.V + 4 * vq))
+                  : make_float4(0.f, 0.f, 0.f, 0.f);
+      float a1[D1];
+#pragma unroll
+      for (int i = 0; i < D1; ++i) a1[i] = 0.f;
+      const int us = ok ? u : 0;
+#pragma unroll
+      for (int k = 0; k < D3; ++k) {
+#pragma unroll
+        for (int i = 0; i < D1; ++i) {
+          const float4 t4 = *reinterpret_cast<const float4*>(T + (k * D1 + i) * p.V + 4 * vq);
+          a1[i] = fmaf(g[k].x, t4.x, fmaf(g[k].y, t4.y, fmaf(g[k].z, t4.z, fmaf(g[k].w, t4.w, a1[i]))));
+        }
+#pragma unroll
+        for (int j = 0; j < D2; ++j) {
+          const float s = S[(k * D2 + j) * p.U + us];
+          a2[j][0] = fmaf(g[k].x, s, a2[j][0]); a2[j][1] = fmaf(g[k].y, s, a2[j][1]);
+          a2[j][2] = fmaf(g[k].z, s, a2[j][2]); a2[j][3] = fmaf(g[k].w, s, a2[j][3]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < D1; ++i) {
+        float tot = a1[i];
+        for (int o = gsize >> 1; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        if (ok && vq == 0) g1[i * p.U + u] = tot;       // one group per u: a plain store
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < D2; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) atomicAdd(g2 + j * p.V + 4 * vq + c, a2[j][c]);
+    __syncthreads();
+    if (p.gx1)
+      for (int t = threadIdx.x; t < D1 * p.U; t += blockDim.x) p.gx1[z * p.ld1 + p.off1 + t] += g1[t];
+    if (p.gx2)
+      for (int t = threadIdx.x; t < D2 * p.V; t += blockDim.x) p.gx2[z * p.ld2 + p.off2 + t] += g2[t];
+  }
+}
+
+using FastKernel = void (*)(const FctpParams);
+
+template <int D1, int D2, int D3>
+void fast_pick(FastKernel& build, FastKernel& consume, int U, int V, size_t& smem_build, size_t& smem_consume) {
+  build = fctp_build_z_f32_kernel<D1, D2, D3>;
+  consume = fctp_consume_gz_f32_kernel<D1, D2, D3>;
+  smem_build = sizeof(float) * FastSmem<D1, D2, D3>::build_floats(U, V);
+  smem_consume = sizeof(float) * FastSmem<D1, D2, D3>::consume_floats(U, V);
+}
+
+template <int D1, int D2>
+bool fast_pick3(int d3, FastKernel& b, FastKernel& c, int U, int V, size_t& sb, size_t& sc) {
+  switch (d3) {
+    case 1: fast_pick<D1, D2, 1>(b, c, U, V, sb, sc); return true;
+    case 3: fast_pick<D1, D2, 3>(b, c, U, V, sb, sc); return true;
+    case 5: fast_pick<D1, D2, 5>(b, c, U, V, sb, sc); return true;
+    case 7: fast_pick<D1, D2, 7>(b, c, U, V, sb, sc); return true;
+  }
+  return false;
+}
+
+template <int D1>
+bool fast_pick2(int d2, int d3, FastKernel& b, FastKernel& c, int U, int V, size_t& sb, size_t& sc) {
+  switch (d2) {
+    case 1: return fast_pick3<D1, 1>(d3, b, c, U, V, sb, sc);
+    case 3: return fast_pick3<D1, 3>(d3, b, c, U, V, sb, sc);
+    case 5: return fast_pick3<D1, 5>(d3, b, c, U, V, sb, sc);
+    case 7: return fast_pick3<D1, 7>(d3, b, c, U, V, sb, sc);
+  }
+  return false;
+}
+
+// The compile-time kernels apply to float32 x and Z, odd irrep dimensions up to 7, V a power of two in
+// 16..128 and 16-byte aligned rows of Z; everything else takes the generic kernels.
+bool fast_lookup(const cueq_fctp_args* a, const FctpParams& p, FastKernel& b, FastKernel& c, size_t& sb, size_t& sc) {
+  if (a->x_dtype != CUEQ_F32 || a->z_dtype != CUEQ_F32) return false;
+  if (p.V < 16 || p.V > 128 || (p.V & (p.V - 1))) return false;
+  if ((p.ldz & 3) || (reinterpret_cast<uintptr_t>(p.z) & 15)) return false;
+  switch (p.d1) {
+    case 1: return fast_pick2<1>(p.d2, p.d3, b, c, p.U, p.V, sb, sc);
+    case 3: return fast_pick2<3>(p.d2, p.d3, b, c, p.U, p.V, sb, sc);
+    case 5: return fast_pick2<5>(p.d2, p.d3, b, c, p.U, p.V, sb, sc);
+    case 7: return fast_pick2<7>(p.d2, p.d3, b, c, p.U, p.V, sb, sc);
+  }
+  return false;
+}
+
+int launch_fast(FastKernel k, size_t smem, const FctpParams& p, cudaStream_t st) {
+  if (smem > 48 * 1024) CUEQ_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k<<<(unsigned)(p.batch < 148 * 16 ? p.batch : 148 * 16), kThreadsF, smem, st>>>(p);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 int fill(const cueq_fctp_args* a, FctpParams& p) {
   if (!a) return cueq::fail("fctp: null arguments");
   if (a->d1 < 1 || a->d1 > kMaxD || a->d2 < 1 || a->d2 > kMaxD || a->d3 < 1 || a->d3 > kMaxD)
@@ -218,6 +429,11 @@ extern "C" int cueq_b200_fctp_build_z(const cueq_fctp_args* a, void* stream) {
   if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
   const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    FastKernel fb, fc;
+    size_t sb, sc;
+    if (fast_lookup(a, p, fb, fc, sb, sc)) return launch_fast(fb, sb, p, st);
+  }
   if (a->z_dtype != CUEQ_F32 && a->z_dtype != CUEQ_BF16) return cueq::fail("fctp: Z must be float32 or bfloat16");
   const bool xb = a->x_dtype == CUEQ_BF16, zb = a->z_dtype == CUEQ_BF16;
   if (!xb && !zb) fctp_build_z_kernel<float, float><<<grid_for(p.batch), kThreadsF, smem, st>>>(p);
@@ -236,6 +452,11 @@ extern "C" int cueq_b200_fctp_consume_gz(const cueq_fctp_args* a, void* stream) 
   if (a->z_dtype != CUEQ_F32 && a->z_dtype != CUEQ_BF16) return cueq::fail("fctp: gZ must be float32 or bfloat16");
   const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V + p.d3 * p.d2 * p.U + p.d2 * p.V + p.d1 * p.U);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    FastKernel fb, fc;
+    size_t sb, sc;
+    if (fast_lookup(a, p, fb, fc, sb, sc)) return launch_fast(fc, sc, p, st);
+  }
   const unsigned grid = grid_for(p.batch);
   const bool xb = a->x_dtype == CUEQ_BF16, zb = a->z_dtype == CUEQ_BF16;
   if (!xb && !zb) fctp_consume_gz_kernel<float, float><<<grid, kThreadsF, smem, st>>>(p);

@@ -44,7 +44,31 @@ __global__ void __launch_bounds__(256) fma_peak_kernel(float* __restrict__ sink,
   if (s == 12345.678f) sink[0] = s;   // keeps the chains alive without a store in practice
 }
 
+// The same measurement with the packed instruction of sm_100 (fma.rn.f32x2: two float32 multiply-adds per
+// thread and instruction): eight chains of float2 per thread, work = 2 * threads * 16 * iters flop as above.
+__global__ void __launch_bounds__(256) fma2_peak_kernel(float* __restrict__ sink, int iters, float a, float b) {
+  float2 acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = make_float2((float)(threadIdx.x + k), (float)k);
+  const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = __ffma2_rn(acc[k], a2, b2);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += acc[k].x + acc[k].y;
+  if (s == 12345.678f) sink[0] = s;
+}
+
 }  // namespace
+
+extern "C" int cueq_b200_selftest_fma2_peak(void* sink, int32_t blocks, int32_t iters, void* stream) {
+  if (!sink || blocks <= 0 || iters <= 0) return cueq::fail("fma peak: invalid arguments");
+  fma2_peak_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<float*>(sink), iters, 0.999f, 0.001f);
+  CUEQ_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int cueq_b200_selftest_fma_peak(void* sink, int32_t blocks, int32_t iters, void* stream) {
   if (!sink || blocks <= 0 || iters <= 0) return cueq::fail("fma peak: invalid arguments");

@@ -75,6 +75,8 @@ int cueq_b200_abi_version(void);
  * float32 multiply-adds in registers (2 * blocks * 256 * 16 * iters flop).  Timed by the caller with CUDA
  * events, it gives the float32 FMA peak that the straight-line symmetric-contraction kernels are rated against. */
 int cueq_b200_selftest_fma_peak(void* sink, int32_t blocks, int32_t iters, void* stream);
+/* The same with the packed float32x2 multiply-add of sm_100 (two multiply-adds per thread and instruction). */
+int cueq_b200_selftest_fma2_peak(void* sink, int32_t blocks, int32_t iters, void* stream);
 /* Debug aid (the reference documents index range as an unchecked precondition,
  * cuequivariance_torch/primitives/segmented_polynomial.py:278-279): sets *status (device int32) to 3 if any of
  * the n gather / scatter indices lies outside [0, rows).  Nothing traps; the host reads the word. */

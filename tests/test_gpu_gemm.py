@@ -158,3 +158,68 @@ def test_bounded_wait_times_out_and_reports():
 
     y = gemm_f32x3(a, a[:64])
     assert torch.isfinite(y).all()
+
+
+# ---- CUDA-core kernels around the dense float32 route: coupled operand and its consumer -----------------------
+@pytest.mark.parametrize("d1,d2,d3,U,V,pitch_extra,z_dtype", [
+    (1, 1, 1, 64, 64, 0, "f32"),       # compile-time kernels, groups of 16 threads per u
+    (3, 5, 3, 64, 64, 32, "f32"),      # Z as a column block of a wider matrix
+    (5, 5, 5, 24, 32, 0, "f32"),       # fewer u than thread groups
+    (7, 3, 5, 40, 128, 0, "f32"),      # a full warp per u
+    (3, 3, 1, 17, 16, 4, "f32"),       # four threads per u, odd U
+    (5, 7, 7, 8, 16, 0, "f32"),
+    (3, 3, 3, 12, 8, 0, "f32"),        # V below 16: generic kernels
+    (3, 5, 3, 32, 32, 0, "bf16"),      # bf16 Z: generic kernels
+])
+def test_fctp_build_and_consume_against_float64(d1, d2, d3, U, V, pitch_extra, z_dtype):
+    """Z[(z,k),(u,v)] = sum_ij C[i,j,k] x1[z,i,u] x2[z,j,v]; gx1 / gx2 = its two contractions with gZ
+    (the operand kernels of the dense route, csrc/fctp_kernels.cu), float32 against float64 einsum."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(d1 * 100 + d2 * 10 + d3 + U + V)
+    B = 301
+    off1, off2, ld1, ld2 = 5, 3, d1 * U + 9, d2 * V + 4
+    x1 = torch.randn(B, ld1, generator=g, device=dev)
+    x2 = torch.randn(B, ld2, generator=g, device=dev)
+    cg = torch.randn(d1, d2, d3, generator=g, device=dev)
+    cg[torch.rand(d1, d2, d3, generator=g, device=dev) < 0.4] = 0.0
+    zt = torch.float32 if z_dtype == "f32" else torch.bfloat16
+    ldz = U * V + pitch_extra
+    Z = torch.full((B * d3, ldz), 7.0, dtype=zt, device=dev)
+    cg_host = (C.c_float * (d1 * d2 * d3))(*cg.flatten().tolist())
+
+    def args(zbuf):
+        a = _lib.FctpArgs()
+        a.x1, a.x2, a.z = x1.data_ptr(), x2.data_ptr(), zbuf.data_ptr()
+        a.cg = C.cast(cg_host, C.POINTER(C.c_float))
+        a.ld1, a.ld2, a.batch, a.off1, a.off2 = ld1, ld2, B, off1, off2
+        a.d1, a.d2, a.d3, a.U, a.V = d1, d2, d3, U, V
+        a.x_dtype, a.z_dtype, a.ldz = _lib.F32, (_lib.F32 if z_dtype == "f32" else _lib.BF16), ldz
+        return a
+
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(_lib.lib().cueq_b200_fctp_build_z(C.byref(args(Z)), st))
+    X1 = x1[:, off1 : off1 + d1 * U].double().view(B, d1, U)
+    X2 = x2[:, off2 : off2 + d2 * V].double().view(B, d2, V)
+    want = torch.einsum("ijk,ziu,zjv->zkuv", cg.double(), X1, X2).reshape(B * d3, U * V)
+    tol = 2e-5 if z_dtype == "f32" else 2e-2
+    got = Z[:, : U * V].double()
+    assert (got - want).abs().max() <= tol * want.abs().max()
+    if pitch_extra:
+        assert (Z[:, U * V :] == 7.0).all()                      # nothing written beside the block
+
+    gZ = torch.randn(B * d3, ldz, generator=g, device=dev).to(zt)
+    gx1 = torch.ones(B, ld1, device=dev)
+    gx2 = torch.ones(B, ld2, device=dev)
+    a = args(gZ)
+    a.gx1, a.gx2 = gx1.data_ptr(), gx2.data_ptr()
+    _lib.check(_lib.lib().cueq_b200_fctp_consume_gz(C.byref(a), st))
+    G = gZ[:, : U * V].double().view(B, d3, U, V)
+    w1 = torch.einsum("ijk,zkuv,zjv->ziu", cg.double(), G, X2).reshape(B, d1 * U)
+    w2 = torch.einsum("ijk,zkuv,ziu->zjv", cg.double(), G, X1).reshape(B, d2 * V)
+    e1 = (gx1[:, off1 : off1 + d1 * U].double() - 1.0 - w1).abs().max()
+    e2 = (gx2[:, off2 : off2 + d2 * V].double() - 1.0 - w2).abs().max()
+    assert e1 <= 2e-5 * max(1.0, float(w1.abs().max())), e1
+    assert e2 <= 2e-5 * max(1.0, float(w2.abs().max())), e2
+    keep1 = torch.ones(ld1, dtype=torch.bool, device=dev)
+    keep1[off1 : off1 + d1 * U] = False
+    assert (gx1[:, keep1] == 1.0).all() and (gx2[:, : off2] == 1.0).all()   # the neighbouring segments are untouched
