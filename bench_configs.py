@@ -1,17 +1,18 @@
 """Throughput of the other benchmark configurations (the headline one is ``bench.py``).
 
-    python bench_configs.py [--config 0|1|2|2bf16|4|fma|all] [--steps K] [--batch B] [--edges E --nodes N]
+    python bench_configs.py [--config 0|1|2|2bf16|4|linear|fma|fma2|all] [--steps K] [--batch B] [--edges E --nodes N]
 
-``--batch`` scales configs 1 and 2, ``--edges`` / ``--nodes`` configs 0 and 4 (the profiles under ``profiles/`` are
-captured on scaled-down cases with these flags); ``fma`` measures the float32 multiply-add peak that config 1 is
-rated against.
+``--batch`` scales configs 1, 2 and ``linear``, ``--edges`` / ``--nodes`` configs 0 and 4 (the profiles under
+``profiles/`` are captured on scaled-down cases with these flags); ``fma`` / ``fma2`` measure the float32
+multiply-add peak (scalar / packed instructions) that the CUDA-core kernels are rated against; ``linear`` is the
+radial output layer of config 3 on its own (float32-accurate tensor-core GEMMs).
 
 Prints one JSON line per configuration: device-timed (CUDA events) steps on seeded
 synthetic inputs of the configuration's shapes, with the per-kernel breakdown of the native
 launches.  Config 0: channelwise forward, 65,536 edges / 4,096 nodes / 128x(0e+1o+2e).
 Config 1: symmetric contraction 128x(0e+1o+2e+3o) -> 128x(0e+1o), degree 3, 16,384 atoms, 10
 species, forward + backward.  Config 2: fully connected 64x(0e+1o+2e)^3, batch 32,768, forward +
-backward (interim library-GEMM route).  Config 4: config-3 graph at 65,536 edges, energy =
+backward (float32: coupled operand in memory + three-pass TF32 GEMMs; ``2bf16``: fused kernels).  Config 4: config-3 graph at 65,536 edges, energy =
 sum of the 0e outputs, first derivatives w.r.t. node features / harmonics / weights, then the
 second derivative of their squared norm w.r.t. the same inputs (force-training pattern).
 """
@@ -137,6 +138,25 @@ def config2(steps, dev, dtype=torch.float32, B=32768):
             "gpu_launches": n, "kernels_ms": k}
 
 
+def dense_layer(steps, dev, rows=1048576):
+    """The radial output layer of config 3 on its own: ``linear_f32x3`` rows x 64 -> 2,944 forward + backward."""
+    from cuequivariance_b200.dense import linear_f32x3
+
+    g = torch.Generator(device=dev).manual_seed(50)
+    x = torch.randn(rows, 64, generator=g, device=dev, requires_grad=True)
+    w = (torch.randn(2944, 64, generator=g, device=dev) / 8.0).requires_grad_(True)
+    b = torch.zeros(2944, device=dev, requires_grad=True)
+    cot = torch.randn(rows, 2944, generator=g, device=dev)
+
+    def step():
+        torch.autograd.grad(linear_f32x3(x, w, b), [x, w, b], cot)
+
+    ms, n, k = _time(step, steps)
+    flops = 3 * 2 * rows * 64 * 2944
+    return {"config": "linear", "what": f"float32-accurate dense layer {rows} x 64 -> 2944, fwd+bwd", "ms_per_step": ms,
+            "tflops": flops / ms / 1e9, "gpu_launches": n, "kernels_ms": k}
+
+
 def _peaks():
     try:
         return json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
@@ -181,8 +201,9 @@ def main():
            "2": lambda steps, dev: config2(steps, dev, torch.float32, a.batch or 32768),
            "2bf16": lambda steps, dev: config2(steps, dev, torch.bfloat16, a.batch or 32768),
            "4": lambda steps, dev: config4(steps, dev, a.edges, a.nodes),
+           "linear": lambda steps, dev: dense_layer(steps, dev, a.batch or 1048576),
            "fma": fma_peak, "fma2": lambda steps, dev: fma_peak(steps, dev, packed=True)}
-    for key in ([k for k in fns if not k.startswith("fma")] if a.config == "all" else [a.config]):
+    for key in ([k for k in fns if not k.startswith("fma") and k != "linear"] if a.config == "all" else [a.config]):
         print(json.dumps(fns[key](a.steps, dev)), flush=True)
 
 

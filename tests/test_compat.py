@@ -97,6 +97,59 @@ def test_segmented_transpose_stand_in(golden):
     assert torch.equal(y.cpu(), torch.from_numpy(g["y"]))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("subscripts", [("uv", "u", "v"), ("uv", "v", "u"), ("u", "uv", "v"), ("u", "vu", "v"),
+                                        ("u", "v", "uv"), ("u", "v", "vu")])
+def test_indexed_linear_stand_in(subscripts, dtype):
+    """The six argument patterns the reference front-end uses
+    (cuequivariance_torch/primitives/segmented_polynomial_indexed_linear.py:345-398) against float64 einsum over
+    rows expanded by class, with first derivatives and one second derivative."""
+    compat.install()
+    from cuequivariance_ops_torch import indexed_linear
+
+    dev = "cuda:0"
+    gen = torch.Generator().manual_seed(7)
+    u, v, C = 12, 20, 4
+    counts = torch.tensor([5, 0, 9, 3], dtype=torch.int32)
+    Z = int(counts.sum())
+    cls = torch.repeat_interleave(torch.arange(C), counts.long())
+    dim = {"u": u, "v": v}
+    sa, sb, so = subscripts
+
+    def make(sub):
+        return torch.randn(*([C] if len(sub) == 2 else [Z]), *[dim[ch] for ch in sub], generator=gen, dtype=torch.float64)
+
+    a, b = make(sa), make(sb)
+    cot = make(so)
+
+    def expand(t, sub):
+        return t[cls] if len(sub) == 2 else t
+
+    def ref(a_, b_):
+        if len(so) == 2:
+            rows = torch.einsum(f"z{sa},z{sb}->z{so}", a_, b_)
+            return 0.7 * torch.zeros(C, dim[so[0]], dim[so[1]], dtype=a_.dtype).index_add_(0, cls, rows)
+        return 0.7 * torch.einsum(f"z{sa},z{sb}->z{so}", expand(a_, sa), expand(b_, sb))
+
+    def got(a_, b_):
+        return indexed_linear(a_, b_, counts.to(dev), u, v, C, Z, subscripts, torch.tensor(0.7))
+
+    def derivatives(fn, xs, c):
+        xs = [x.clone().requires_grad_(True) for x in xs]
+        out = fn(*xs)
+        g = torch.autograd.grad((out * c).sum(), xs, create_graph=True)
+        gg = torch.autograd.grad((g[0] ** 2).sum(), xs[1])      # through the gradient of the first argument
+        return [out.detach(), g[0].detach(), g[1].detach(), gg[0]]
+
+    want = derivatives(ref, [a, b], cot)
+    have = derivatives(got, [a.to(dev).to(dtype), b.to(dev).to(dtype)], cot.to(dev).to(dtype))
+    tol = 1e-11 if dtype == torch.float64 else 2e-4
+    for w_, h_ in zip(want, have):
+        assert h_.shape == w_.shape
+        assert (h_.cpu().double() - w_).abs().max() <= tol * max(1.0, float(w_.abs().max()))
+
+
 @pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not present")
 def test_unmodified_reference_frontend_dispatches_to_the_stand_in():
     """Runs in a subprocess so that the reference import does not leak into other tests."""

@@ -12,7 +12,7 @@ The reference is staged under ``baseline/_ref`` by ``baseline/stage_reference.py
 part of this repository's history); the tests are skipped when it is missing.  They run in a
 child process so that the reference import does not leak into the other tests.  Left out:
 the export modes (TorchScript, torch.export, ONNX, TensorRT), which need the closed package's
-native operator registrations, the triangle / attention tests and ``indexed_linear``.
+native operator registrations, and the triangle / attention tests.
 """
 import os
 import re
@@ -31,7 +31,8 @@ SELECTIONS = [
     ("primitives/segmented_polynomial_test.py", "test_segmented_polynomial_dytpes and not device1"),
     ("operations/channel_wise_test.py", "test_channel_wise_fwd or test_channel_wise_bwd_bwd or test_channel_wise_indexing"),
     ("operations/fully_connected_test.py", "test_fully_connected"),
-    ("operations/linear_test.py", "(test_linear_fwd or test_linear_bwd_bwd or test_linear_copy) and not indexed_linear"),
+    ("primitives/segmented_polynomial_test.py", "test_segmented_polynomial_indexed_linear"),
+    ("operations/linear_test.py", "test_linear_fwd or test_linear_bwd_bwd or test_linear_copy"),
     ("operations/rotation_test.py", "test_rotation or test_inversion"),   # test_vector_to_euler_angles uses CPU tensors
     ("operations/spherical_harmonics_test.py", "not export"),
     ("primitives/transpose_test.py", "test_transpose"),
