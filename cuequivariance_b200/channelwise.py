@@ -146,7 +146,7 @@ _CSR = _CsrCache()
 SENDER_PASSES = 1  # backward: visit the edges in this many sender-range passes when the node table exceeds 64 MB
 STAGING = 0  # forward kernels: 0 = per-lane cp.async staging, 1 = bulk copies (TMA) signalled on an mbarrier
 CHANNELS_PER_LANE = 0  # 0: the library chooses; 2 or 4 force a variant (used by the tests)
-BWD_VARIANT = 0  # backward kernels: 0 = the library chooses, 1 = one warp per receiver, 2 = one thread block per receiver
+BWD_VARIANT = 0  # backward kernels: 0 = the library chooses, 1 = one warp per receiver, 2 = one thread block per receiver, 3 = 2 with bulk reductions of the x1 gradient
 _IDENTITY_ROWPTR: dict = {}
 
 

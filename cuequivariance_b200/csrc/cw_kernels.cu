@@ -24,6 +24,7 @@
 //     of the gathered operand goes out as vectorised reductions (red.global.add.v4.f32) keyed
 //     by sender, the weight gradient is streamed out, the gradient of x2 is reduced over the
 //     channels with warp shuffles.
+#include <cstdint>
 #include <cstring>
 
 #include "common.cuh"
@@ -143,6 +144,16 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
                ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// One bulk reduction (float32 add) of `bytes` contiguous bytes from shared to global memory, issued by one thread
+// and tracked by that thread's bulk async-group; both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_reduce_add(float* gmem_dst, const void* smem_src, unsigned bytes, unsigned long long pol) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.L2::cache_hint.add.f32 [%0], [%1], %2, %3;\n"
+               ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes), "l"(pol) : "memory");
+  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+// the issuing thread waits until its bulk reductions have read their shared-memory source / have completed
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
 __device__ __forceinline__ void red_add(float* addr, const float (&v)[4]) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
@@ -486,7 +497,7 @@ __global__ void __launch_bounds__(kWarps * 32, C == 2 ? CW_MINBLOCKS : 2) cw_fwd
 }
 
 // ---- backward ---------------------------------------------------------------------------------
-template <class G, int C, int P, bool MUL_IR>
+template <class G, int C, int P, bool MUL_IR, bool NEED_R = true>
 struct BwdPaths {
   __device__ __forceinline__ static void run(const float (&X)[G::D1][C], const Vec<C>* wst, const Vec<C>* grow, int lane,
                                              const float* M, const CwCoef& coef, const CwParams& p, float* gwrow,
@@ -496,9 +507,9 @@ struct BwdPaths {
     float Gk[G::MAXD3][C];
     unstage_block<G::d3(P), C, MUL_IR>(grow + G::out_offset(P) * 32, lane, Gk);
     float gw[C];
-    G::template bwd_path<P, C>(X, W, M, Gk, coef, gX, gw, r);
+    G::template bwd_path<P, C, NEED_R>(X, W, M, Gk, coef, gX, gw, r);
     if (p.need_gw) st_stream(gwrow + p.w_off[P], gw);
-    if constexpr (P + 1 < G::NPATH) BwdPaths<G, C, P + 1, MUL_IR>::run(X, wst, grow, lane, M, coef, p, gwrow, gX, r);
+    if constexpr (P + 1 < G::NPATH) BwdPaths<G, C, P + 1, MUL_IR, NEED_R>::run(X, wst, grow, lane, M, coef, p, gwrow, gX, r);
   }
 };
 
@@ -620,9 +631,14 @@ struct StageGSplit {
   }
 };
 
-template <class G, bool MUL_IR>
+template <class G, bool MUL_IR, bool BULK_RED, bool NEED_GX2>
 __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __grid_constant__ CwParams p, const __grid_constant__ CwCoef coef) {
   constexpr int C = 4;
+  // BULK_RED (mul_ir rows only): the x1 gradient of an edge - the 32 lanes' C*D1 values are one contiguous run of
+  // the sender's row - leaves as ONE bulk reduction per warp and edge instead of D1 vector reductions per lane.
+  // Its shared-memory source is the slot the edge's x1 block was staged in (free once X is in registers); the
+  // slot is refilled two trips later, after the issuing lane has waited for the reduction to have read it.
+  constexpr bool kBulk = BULK_RED && MUL_IR;
   extern __shared__ __align__(16) float smem[];
   using S = Smem<G, C>;
   constexpr int kStage = S::kPerStage;
@@ -642,6 +658,10 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
     const int beg = __ldg(p.rowptr + n), end = __ldg(p.rowptr + n + 1);
     if (beg >= end) continue;                                      // same decision in every thread of the block
     const int nrow = p.recv_mod ? n % p.recv_mod : n;
+    if (kBulk) {                                                   // the last reduction of the previous receiver has left its slot
+      if (lane == 0) bulk_wait_read();
+      __syncwarp();
+    }
     __syncthreads();                                               // everybody is done with the previous cotangent row
     if (active) StageGSplit<G, C, 0, MUL_IR>::run(grow, p.gout + (int64_t)nrow * p.out_stride, p, ch, lane, warp);
     cp_async_commit();
@@ -659,18 +679,33 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
     for (int it = 0; pos < end; pos += kWarps, ++it) {
       float* st = stages + (it & 1) * kStage;
       cur = next;
-      if (pos + kWarps < end) {
-        next = ahead;
-        issue_edge_ids<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, next, ch, lane, active, pol_stream, pol_keep);
-        if (pos + 2 * kWarps < end) ahead = load_ids(p, pos + 2 * kWarps);   // used in the next trip
-        cp_async_wait<1>();
+      if (!kBulk) {
+        if (pos + kWarps < end) {
+          next = ahead;
+          issue_edge_ids<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, next, ch, lane, active, pol_stream, pol_keep);
+          if (pos + 2 * kWarps < end) ahead = load_ids(p, pos + 2 * kWarps);   // used in the next trip
+          cp_async_wait<1>();
+        } else {
+          cp_async_wait<0>();
+        }
       } else {
-        cp_async_wait<0>();
+        cp_async_wait<0>();                                          // the copies of this edge are the only ones in flight
       }
       const int eid = cur.eid;
       __syncwarp();
       mt.compute(Msm, st, lane);
       __syncwarp();
+      if (kBulk) {
+        // the other slot is the source of the previous edge's reduction: refill it only after that has been read
+        // (the matrices above were computed in the meantime)
+        if (lane == 0) bulk_wait_read();
+        __syncwarp();
+        if (pos + kWarps < end) {
+          next = ahead;
+          issue_edge_ids<G, C, MUL_IR>(p, stages + ((it + 1) & 1) * kStage, next, ch, lane, active, pol_stream, pol_keep);
+          if (pos + 2 * kWarps < end) ahead = load_ids(p, pos + 2 * kWarps);
+        }
+      }
       float r[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) r[j] = 0.f;
@@ -682,12 +717,29 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
         for (int i = 0; i < G::D1; ++i)
 #pragma unroll
           for (int c = 0; c < C; ++c) gX[i][c] = 0.f;
-        BwdPaths<G, C, 0, MUL_IR>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
-        if (p.need_gx1) {
+        BwdPaths<G, C, 0, MUL_IR, NEED_GX2>::run(X, stage + G::D1 * 32, grow, lane, Msm, coef, p, p.gw + (int64_t)eid * p.w_stride + ch, gX, r);
+        if (p.need_gx1 && !kBulk) {
           emit_block<G::D1, C, MUL_IR, true>(p.gx1 + (int64_t)cur.snd * p.x1_stride + p.x1_off, p.extent, ch, gX, 0, pol_keep);
         }
+        if (p.need_gx1 && kBulk) {
+          // the lane's C*D1 values in the order of the global row (channel-major), lane after lane
+          float f[G::D1 * C];
+#pragma unroll
+          for (int i = 0; i < G::D1; ++i)
+#pragma unroll
+            for (int c = 0; c < C; ++c) f[c * G::D1 + i] = gX[i][c];
+          __syncwarp();                                              // every lane has taken its X out of the slot
+          float4* slot = reinterpret_cast<float4*>(st + S::kX2);
+#pragma unroll
+          for (int t = 0; t < G::D1; ++t) slot[lane * G::D1 + t] = make_float4(f[4 * t], f[4 * t + 1], f[4 * t + 2], f[4 * t + 3]);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0)
+            bulk_reduce_add(p.gx1 + (int64_t)cur.snd * p.x1_stride + p.x1_off + (int64_t)(blockIdx.y * 32 * C) * G::D1, slot,
+                            (unsigned)(G::D1 * 32 * C * sizeof(float)), pol_keep);
+        }
       }
-      if (p.need_gx2) {
+      if (NEED_GX2) {
         const float tot = reduce16(r, lane);
         // a reduction without return value: the warp does not wait for it (a load-add-store would stall on the load)
         if (!(lane & 1) && (lane >> 1) < G::NX2) atomicAdd(p.gx2 + (int64_t)eid * p.x2_stride + (lane >> 1), tot);
@@ -695,6 +747,7 @@ __global__ void __launch_bounds__(kWarps * 32, 3) cw_bwd_block_kernel(const __gr
       __syncwarp();
     }
   }
+  if (kBulk && lane == 0) bulk_wait_all();                           // shared memory stays allocated until the last reduction is done
 }
 
 // ---- registry -----------------------------------------------------------------------------------
@@ -704,7 +757,7 @@ struct GroupEntry {
   int (*fwd)(const CwParams&, int, int, cudaStream_t);
   int (*bwd)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
   int (*fwd_bulk)(const CwParams&, int, int, cudaStream_t);
-  int (*bwd_block)(const CwParams&, const CwCoef&, int, cudaStream_t);
+  int (*bwd_block)(const CwParams&, const CwCoef&, int, int, cudaStream_t);
 };
 
 int grid_x(int num_receivers) {
@@ -773,25 +826,32 @@ int launch_bwd(const CwParams& p, const CwCoef& coef, int mul_ir, int cpl, cudaS
   return mul_ir ? launch_bwd_t<G, 4, true>(p, coef, st) : launch_bwd_t<G, 4, false>(p, coef, st);
 }
 
-template <class G, bool A>
+template <class G, bool A, bool BULK, bool GX2>
 int launch_bwd_block_t(const CwParams& p, const CwCoef& coef, cudaStream_t st) {
   using S = Smem<G, 4>;
   const size_t smem = sizeof(float) * (S::kGrow + kWarps * S::kPerWarpFwd);
   static cueq::PerDeviceFlag configured;
   if (!configured.get()) {
-    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_block_kernel<G, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_block_kernel<G, A, BULK, GX2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured.set();
   }
   const int cap = 148 * 24;
   dim3 grid(p.num_receivers < cap ? p.num_receivers : cap, (p.extent + 127) / 128);
-  cw_bwd_block_kernel<G, A><<<grid, kWarps * 32, smem, st>>>(p, coef);
+  cw_bwd_block_kernel<G, A, BULK, GX2><<<grid, kWarps * 32, smem, st>>>(p, coef);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
+// bulk: the x1 gradient leaves as one bulk reduction per warp and edge; needs mul_ir rows whose blocks start on
+// 16-byte boundaries (checked here: a misaligned bulk operation is an illegal instruction, not an error code)
 template <class G>
-int launch_bwd_block(const CwParams& p, const CwCoef& coef, int mul_ir, cudaStream_t st) {
-  return mul_ir ? launch_bwd_block_t<G, true>(p, coef, st) : launch_bwd_block_t<G, false>(p, coef, st);
+int launch_bwd_block(const CwParams& p, const CwCoef& coef, int mul_ir, int bulk, cudaStream_t st) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.gx1) % 16 == 0) && (p.x1_stride % 4 == 0) && (p.x1_off % 4 == 0) && (p.extent % 128 == 0);
+  // the x2-gradient partials are a third of the arithmetic: a launch that does not need them runs without
+  if (bulk && mul_ir && p.need_gx1 && aligned)
+    return p.need_gx2 ? launch_bwd_block_t<G, true, true, true>(p, coef, st) : launch_bwd_block_t<G, true, true, false>(p, coef, st);
+  if (mul_ir) return p.need_gx2 ? launch_bwd_block_t<G, true, false, true>(p, coef, st) : launch_bwd_block_t<G, true, false, false>(p, coef, st);
+  return p.need_gx2 ? launch_bwd_block_t<G, false, false, true>(p, coef, st) : launch_bwd_block_t<G, false, false, false>(p, coef, st);
 }
 
 #define CW_ENTRY(G) {G::signature(), G::D1, G::NPATH, G::NPAIR, G::NTERM, G::SUMD3, G::NX2, G::NVAL, G::NTERM_FWD, &launch_fwd<G>, &launch_bwd<G>, &launch_fwd_bulk<G>, &launch_bwd_block<G>},
@@ -874,11 +934,16 @@ extern "C" int cueq_b200_cw_backward(int g, const cueq_cw_args* a, void* stream)
   CwCoef coef;
   std::memset(&coef, 0, sizeof(coef));
   for (int t = 0; t < kGroups[g].nterm; ++t) coef.c[t] = a->bwd_coef[t];
-  if (a->variant < 0 || a->variant > 2) return cueq::fail("channelwise backward: variant must be 0 (automatic), 1 or 2");
+  if (a->variant < 0 || a->variant > 3) return cueq::fail("channelwise backward: variant must be 0 (automatic), 1, 2 or 3");
   // one thread block per receiver needs the four-channel layout (extent a multiple of 4 is given);
   // it is the default from 128 channels on, where a warp's 128 channels are all in use
-  const bool block_per_receiver = a->variant == 2 || (a->variant == 0 && a->channels_per_lane != 2 && a->extent % 128 == 0);
-  if (block_per_receiver) return kGroups[g].bwd_block(p, coef, a->x1_mul_ir, reinterpret_cast<cudaStream_t>(stream));
+  const bool block_per_receiver = a->variant >= 2 || (a->variant == 0 && a->channels_per_lane != 2 && a->extent % 128 == 0);
+  if (a->variant == 3 && a->extent % 128) return cueq::fail("channelwise backward: variant 3 needs a multiple of 128 channels");
+  // bulk reductions pay from three components per channel on (one 1.5 KB operation instead of three vector
+  // reductions per lane); for the scalar block (512 bytes per edge) the vector reductions are faster
+  const bool bulk = a->variant == 3 || (a->variant == 0 && kGroups[g].d1 >= 3);
+  if (block_per_receiver)
+    return kGroups[g].bwd_block(p, coef, a->x1_mul_ir, bulk, reinterpret_cast<cudaStream_t>(stream));
   return kGroups[g].bwd(p, coef, a->x1_mul_ir, pick_cpl(a), reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -132,7 +132,8 @@ def emit_group(l1: int, paths) -> str:
     # ---- backward -----------------------------------------------------------------------
     A("  // per path, pairs ordered by i: S[i] = sum_k M[q] G[k];  gX[i] += W*S[i];  gw = sum_i S[i] X[i];")
     A("  //           r[j] += c * dot4(W*X[i], G[k]) over the non-zero (i, j, k)")
-    A("  template <int P, int C, class Coef>")
+    A("  // NEED_R = false leaves the x2-gradient partials (and the products that only feed them) out")
+    A("  template <int P, int C, bool NEED_R, class Coef>")
     A("  __device__ __forceinline__ static void bwd_path(const float (&X)[D1][C], const float (&W)[C], const float* __restrict__ M,")
     A("                                                  const float (&G)[MAXD3][C], const Coef& coef,")
     A("                                                  float (&gX)[D1][C], float (&gw)[C], float (&r)[16]) {")
@@ -175,9 +176,9 @@ def emit_group(l1: int, paths) -> str:
                 else:
                     A(f"        CW_FMA4(s, m[{q - qa}], G[{k}]);")
                 if scale_g:
-                    A(f"        {{ const float v = CW_DOT4(X[{i}], gs[{k}]);")
+                    A(f"        if constexpr (NEED_R) {{ const float v = CW_DOT4(X[{i}], gs[{k}]);")
                 else:
-                    A(f"        {{ const float v = CW_DOT4(xw, G[{k}]);")
+                    A(f"        if constexpr (NEED_R) {{ const float v = CW_DOT4(xw, G[{k}]);")
                 for j, _c in terms:
                     A(f"          r[{j_base + j}] = fmaf(coef.c[{t}], v, r[{j_base + j}]);")
                     t += 1

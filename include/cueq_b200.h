@@ -218,9 +218,13 @@ typedef struct {
   void* status;         /* nullable device int32: set to 1 if a bounded wait on a bulk copy ran out */
   int32_t recv_mod;     /* backward only: if > 0 the CSR has several rows per receiver (row r belongs to
                            receiver r % recv_mod), used to visit the edges in sender-range passes        */
-  int32_t variant;      /* backward only: 0 = the library chooses; 1 = one warp per receiver (2 or 4 channels
+  int32_t variant;      /* backward only: 0 = the library chooses (3 from 128 channels on for x1 degrees >= 1,
+                           2 for the scalar block, 1 otherwise); 1 = one warp per receiver (2 or 4 channels
                            per thread); 2 = one thread block per receiver: its warps share the staged
-                           cotangent row and split the receiver's edges, four channels per thread          */
+                           cotangent row and split the receiver's edges, four channels per thread;
+                           3 = as 2, with the x1 gradient of an edge leaving as one bulk reduction
+                           (cp.reduce.async.bulk) per warp instead of vector reductions per lane (mul_ir
+                           rows, 128 | extent; falls back to 2 where the rows are not 16-byte aligned)        */
 } cueq_cw_args;
 
 int cueq_b200_cw_num_groups(void);

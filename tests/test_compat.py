@@ -133,7 +133,7 @@ def test_indexed_linear_stand_in(subscripts, dtype):
         return 0.7 * torch.einsum(f"z{sa},z{sb}->z{so}", expand(a_, sa), expand(b_, sb))
 
     def got(a_, b_):
-        return indexed_linear(a_, b_, counts.to(dev), u, v, C, Z, subscripts, torch.tensor(0.7))
+        return indexed_linear(a_, b_, counts.to(dev), u, v, C, Z, subscripts, torch.tensor(0.7, dtype=torch.float64))
 
     def derivatives(fn, xs, c):
         xs = [x.clone().requires_grad_(True) for x in xs]
