@@ -204,6 +204,8 @@ _DIAG_SKIP_COPY = bool(_os.environ.get("CUEQ_DIAG_SKIP_COPY"))
 _DIAG_SKIP_HANDSHAKE = bool(_os.environ.get("CUEQ_DIAG_SKIP_HANDSHAKE"))
 PUSH_BLOCKS = int(_os.environ.get("CUEQ_PUSH_BLOCKS", "4"))      # thread blocks per (peer, irrep block) piece of the push kernel
 PUSH_MODE = _os.environ.get("CUEQ_PUSH_MODE", "memcpy")   # "memcpy": one cudaMemcpyAsync per piece (copy engines); "kernel": the push kernel
+HANDSHAKE = _os.environ.get("CUEQ_HANDSHAKE", "events")   # peer exchange: "events" (interprocess CUDA events, no kernel) or "nccl" (one-element all-reduce)
+HANDSHAKE_TIMEOUT_S = 60.0
 EXCHANGE = _os.environ.get("CUEQ_EXCHANGE", "nccl")       # how the pipelined path moves node rows between ranks: "nccl" or "peer_copy"
 
 
@@ -268,6 +270,74 @@ class PeerExchange:
         self.exch = torch.cuda.Stream(device=device, priority=-1)
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
         self.free = None                  # event: every rank is done with the receive buffers of the previous pass
+        self.handshake_mode = HANDSHAKE
+        if self.handshake_mode == "events":
+            self._setup_event_handshake()
+
+    # -- hand-shake without a kernel -----------------------------------------------------------------
+    #
+    # A collective needs thread blocks, and while a channelwise launch holds every register of every SM its
+    # blocks are not scheduled before that launch drains - the hand-shake then costs as long as the kernel
+    # it was meant to overlap.  Interprocess CUDA events need no SM: rank r records event E[r][k % S] on its
+    # exchange stream and the others make their exchange streams wait for it.  A stream wait captures the
+    # event's latest record *at the time of the call*, so a waiter must not call before the record has been
+    # issued: every rank publishes the number of records it has issued in a page of host shared memory and a
+    # waiter polls that counter (on the host, bounded) first.  An event slot is recorded again S hand-shakes
+    # later; by then every rank has issued its waits for the earlier record, because nobody starts hand-shake
+    # k + 1 before everybody has published hand-shake k.
+    _SLOTS = 8
+
+    def _setup_event_handshake(self):
+        import os
+        import tempfile
+
+        import numpy as np
+
+        dev = self.device
+        with torch.cuda.device(dev):
+            self._ev_local = [torch.cuda.Event(enable_timing=False, interprocess=True) for _ in range(self._SLOTS)]
+            for ev in self._ev_local:
+                ev.record(self.exch)               # an event must have been recorded before its handle is exported
+            handles = [ev.ipc_handle() for ev in self._ev_local]
+        # the counter page: a small file in shared memory that every rank maps; rank 0 removes the name again as
+        # soon as everybody has it open (the mappings stay valid), so nothing is left behind whatever happens later
+        path = [None]
+        if self.rank == 0:
+            fd, path[0] = tempfile.mkstemp(prefix="cueq_b200_handshake_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            os.write(fd, bytes(8 * self.world))
+            os.close(fd)
+        dist.broadcast_object_list(path, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        self._issued = np.memmap(path[0], dtype=np.int64, mode="r+", shape=(self.world,))
+        dist.barrier(group=self.group)
+        if self.rank == 0:
+            os.unlink(path[0])
+        all_handles = [None] * self.world
+        dist.all_gather_object(all_handles, handles, group=self.group)
+        self._ev_peer = []
+        for r, hs in enumerate(all_handles):
+            if r == self.rank:
+                self._ev_peer.append(self._ev_local)
+            else:
+                self._ev_peer.append([torch.cuda.Event.from_ipc_handle(dev, h) for h in hs])
+        self._count = 0
+        dist.barrier(group=self.group)             # nobody polls a counter page that does not exist yet
+
+    def _event_handshake(self, s):
+        import time
+
+        k = self._count
+        slot = k % self._SLOTS
+        self._ev_local[slot].record(s)
+        self._issued[self.rank] = k + 1
+        deadline = time.monotonic() + HANDSHAKE_TIMEOUT_S
+        for q in range(self.world):
+            if q == self.rank:
+                continue
+            while self._issued[q] < k + 1:
+                if time.monotonic() > deadline:
+                    raise RuntimeError(f"peer exchange: rank {q} did not reach hand-shake {k} within {HANDSHAKE_TIMEOUT_S} s")
+            s.wait_event(self._ev_peer[q][slot])
+        self._count = k + 1
 
     def _view(self, flat, slot, rows, width):
         return flat[self.offsets[slot] : self.offsets[slot] + rows * width].view(rows, width)
@@ -288,7 +358,9 @@ class PeerExchange:
         s = self.exch
         for ev in after_events:
             s.wait_event(ev)
-        if not _DIAG_SKIP_HANDSHAKE:
+        if self.handshake_mode == "events":
+            self._event_handshake(s)
+        elif not _DIAG_SKIP_HANDSHAKE:
             with torch.cuda.stream(s):
                 dist.all_reduce(self.flag, group=self.group)
         ev = torch.cuda.Event()

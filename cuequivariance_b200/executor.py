@@ -303,6 +303,9 @@ class StaticKernel:
         return None  # the derivative program is matched by its own digest
 
 
+SPLIT_STATIC_GRADIENTS = True   # one launch per gradient where each has a build-time kernel (see PolynomialFunction.backward)
+
+
 def attach_static(program: "Uniform1dProgram") -> None:
     """Gives ``program`` the build-time kernel of its polynomial if the library has one."""
     from .static_poly import digest
@@ -402,11 +405,24 @@ class PolynomialFunction(torch.autograd.Function):
         grads: List[Optional[torch.Tensor]] = [None] * len(inputs)
         if any(needs) and any(has):
             dprog = program.derivative(needs, has)
-            dcfg = derivative_config(cfg, needs, has)
             cots = []
             for j, g in enumerate(grad_outputs):
                 if g is not None:
                     cots.append(g.contiguous())
+            # A build-time straight-line kernel that produces several gradients at once can need more registers
+            # than a thread has (the symmetric contraction's weight + input gradient spills 0.8 KB per thread);
+            # where every single gradient has a straight-line kernel of its own, one launch per gradient is faster.
+            if SPLIT_STATIC_GRADIENTS and sum(needs) > 1 and isinstance(dprog._special, StaticKernel):
+                singles = []
+                for i, n in enumerate(needs):
+                    if n:
+                        one = tuple(k == i for k in range(len(needs)))
+                        singles.append((i, one, program.derivative(one, has)))
+                if all(isinstance(dp._special, StaticKernel) for _, _, dp in singles):
+                    for i, one, dp in singles:
+                        (grads[i],) = PolynomialFunction.apply(dp, derivative_config(cfg, one, has), *inputs, *cots)
+                    return (None, None, *grads)
+            dcfg = derivative_config(cfg, needs, has)
             res = PolynomialFunction.apply(dprog, dcfg, *inputs, *cots)
             it = iter(res)
             for i, n in enumerate(needs):

@@ -75,4 +75,5 @@ def registered_polynomials() -> List[Tuple[str, Polynomial]]:
     out.append(("sc_l3_l1_d3_fwd", fwd))
     out.append(("sc_l3_l1_d3_bwd_wx", fwd.backward([True, True], [True])))
     out.append(("sc_l3_l1_d3_bwd_x", fwd.backward([False, True], [True])))
+    out.append(("sc_l3_l1_d3_bwd_w", fwd.backward([True, False], [True])))
     return out

@@ -54,8 +54,12 @@ def _worker(rank, world, port, results):
         lo, hi = shard_bounds(N, world, rank)
         e0, e1 = shard_edges(rcv, N, world, rank)
         ok = True
-        for pipelined, exchange, push in ((True, "peer_copy", "memcpy"), (True, "peer_copy", "kernel"), (True, "nccl", ""), (False, "nccl", "")):
+        for pipelined, exchange, push, shake in ((True, "peer_copy", "memcpy", "events"), (True, "peer_copy", "kernel", "events"),
+                                                 (True, "peer_copy", "memcpy", "nccl"), (True, "nccl", "", ""), (False, "nccl", "", "")):
             distributed.EXCHANGE, distributed.PUSH_MODE = exchange, push or distributed.PUSH_MODE
+            if shake:
+                distributed.HANDSHAKE = shake
+                distributed._EXCHANGES.clear()      # the hand-shake kind is fixed when an exchange is set up
             op = ReceiverShardedChannelWise(tp, group=dist.group.WORLD, pipelined=pipelined)
             for step in range(3):
                 scale_in = 1.0 + step    # different data every step: a stale buffer would show
