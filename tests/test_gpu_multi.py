@@ -85,3 +85,53 @@ def test_receiver_sharded_channelwise_two_gpus():
     results = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert len(results) == world and all(results.values())
+
+
+def _one_process_two_devices(results):
+    """Child process: the same kernels on cuda:0 and then on cuda:1 of ONE process.  Every launcher raises the
+    dynamic shared-memory limit of its kernel once per device; a process-wide flag would leave the second device
+    at 48 KB and its launch would fail."""
+    sys.path.insert(0, ROOT)
+    import cuequivariance_b200 as cb
+    from cuequivariance_b200 import _lib
+    from cuequivariance_b200.dense import linear_f32x3
+
+    s1 = "+".join(f"128x{ir}" for ir in ("0e", "1o", "2e", "3o"))
+    filt = ["0e", "1o", "2e", "3o"]
+    tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", filt, layout=cb.mul_ir, shared_weights=False, internal_weights=False)
+    gen = torch.Generator().manual_seed(5)
+    E, N = 600, 40
+    x1, x2, w = torch.randn(N, tp.irreps_in1.dim, generator=gen), torch.randn(E, 16, generator=gen), torch.randn(E, tp.weight_numel, generator=gen)
+    snd = torch.randint(0, N, (E,), generator=gen, dtype=torch.int32)
+    rcv = torch.sort(torch.randint(0, N, (E,), generator=gen, dtype=torch.int32)).values
+    cot = torch.randn(N, tp.irreps_out.dim, generator=gen)
+    xa, wa = torch.randn(512, 64, generator=gen), torch.randn(256, 64, generator=gen)
+    outs = []
+    for d in ("cuda:0", "cuda:1"):
+        a, b, c = (t.to(d).requires_grad_(True) for t in (x1, x2, w))
+        out = tp(a, b, c, indices_1=snd.to(d), indices_out=rcv.to(d), size_out=N)      # backward of the l >= 2 groups: > 48 KB
+        g = torch.autograd.grad((out * cot.to(d)).sum(), (a, b, c))
+        xl, wl = xa.to(d).requires_grad_(True), wa.to(d).requires_grad_(True)
+        y = linear_f32x3(xl, wl)                                                       # tcgen05 kernels: > 100 KB
+        gy = torch.autograd.grad(y.sum(), (xl, wl))
+        torch.cuda.synchronize(d)
+        _lib.check_status()
+        outs.append([t.detach().cpu() for t in (out, *g, y, *gy)])
+    ok = True
+    for p, q in zip(*outs):
+        ok = ok and bool((p - q).abs().max() <= 1e-4 * max(1.0, float(p.abs().max())))   # reduction order differs from run to run
+    results["ok"] = ok
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices():
+    import torch.multiprocessing as mp
+
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_one_process_two_devices_entry, args=(results,), nprocs=1, join=True)
+    assert results.get("ok") is True
+
+
+def _one_process_two_devices_entry(_index, results):
+    _one_process_two_devices(results)

@@ -41,9 +41,10 @@ def _run_noalloc(plan, layout_mul_ir, w, x1, x2, senders, receivers, n_recv):
     return out
 
 
-def test_noalloc_forward_matches_regular_entry_point_twice():
+@pytest.mark.parametrize("mul_ir", [True, False])
+def test_noalloc_forward_matches_regular_entry_point_twice(mul_ir):
     s1 = "64x0e+64x1o+64x2e+64x3o"
-    tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", ["0e", "1o", "2e", "3o"], layout=cb.mul_ir,
+    tp = cb.ChannelWiseTensorProduct(s1, "0e+1o+2e+3o", ["0e", "1o", "2e", "3o"], layout=cb.mul_ir if mul_ir else cb.ir_mul,
                                      shared_weights=False, internal_weights=False)
     plan = tp.f._program(torch.float32)._special.plan
     gen = torch.Generator(device=DEV).manual_seed(7)
@@ -54,7 +55,7 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
         snd = torch.randint(0, N, (E,), generator=gen, device=DEV, dtype=torch.int32)
         rcv = torch.sort(torch.randint(0, N - 3, (E,), generator=gen, device=DEV, dtype=torch.int32)).values
         ref = tp(x1, x2, w, indices_1=snd, indices_out=rcv, size_out=N)
-        got = _run_noalloc(plan, True, w, x1, x2, snd, rcv, N)
+        got = _run_noalloc(plan, mul_ir, w, x1, x2, snd, rcv, N)
         torch.cuda.synchronize()
         assert not torch.isnan(got).any(), "some output rows were not written"
         scale = max(1.0, float(ref.abs().max()))
