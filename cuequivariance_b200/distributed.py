@@ -209,6 +209,44 @@ HANDSHAKE_TIMEOUT_S = 60.0
 EXCHANGE = _os.environ.get("CUEQ_EXCHANGE", "nccl")       # how the pipelined path moves node rows between ranks: "nccl" or "peer_copy"
 
 
+class HandshakeBoard:
+    """One counter per rank in a page of host memory shared by the ranks of one node.
+
+    ``publish(k)`` sets this rank's counter; ``wait_for(q, k)`` polls rank ``q``'s counter on the host until it
+    has reached ``k`` (bounded: raises after ``timeout`` seconds, e.g. when rank ``q`` has died).  The page is a
+    small file in shared memory that every rank maps; rank 0 removes its name as soon as everybody has it open
+    (the mappings stay valid), so nothing is left behind whatever happens later.  Needs no GPU."""
+
+    def __init__(self, group=None):
+        import os
+        import tempfile
+
+        import numpy as np
+
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        path = [None]
+        if self.rank == 0:
+            fd, path[0] = tempfile.mkstemp(prefix="cueq_b200_handshake_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            os.write(fd, bytes(8 * self.world))
+            os.close(fd)
+        dist.broadcast_object_list(path, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self.counters = np.memmap(path[0], dtype=np.int64, mode="r+", shape=(self.world,))
+        dist.barrier(group=group)
+        if self.rank == 0:
+            os.unlink(path[0])
+
+    def publish(self, k: int) -> None:
+        self.counters[self.rank] = k
+
+    def wait_for(self, q: int, k: int, timeout: float) -> None:
+        import time
+
+        deadline = time.monotonic() + timeout
+        while self.counters[q] < k:
+            if time.monotonic() > deadline:
+                raise RuntimeError(f"rank {q} did not reach hand-shake {k - 1} within {timeout} s (its counter is {int(self.counters[q])})")
+
+
 class PeerExchange:
     """Node-feature exchange between the ranks of one node without taking SMs from the kernels.
 
@@ -281,36 +319,20 @@ class PeerExchange:
     # it was meant to overlap.  Interprocess CUDA events need no SM: rank r records event E[r][k % S] on its
     # exchange stream and the others make their exchange streams wait for it.  A stream wait captures the
     # event's latest record *at the time of the call*, so a waiter must not call before the record has been
-    # issued: every rank publishes the number of records it has issued in a page of host shared memory and a
-    # waiter polls that counter (on the host, bounded) first.  An event slot is recorded again S hand-shakes
+    # issued: every rank publishes the number of records it has issued in a page of host shared memory
+    # (`HandshakeBoard`) and a waiter polls that counter (on the host, bounded) first.  An event slot is recorded again S hand-shakes
     # later; by then every rank has issued its waits for the earlier record, because nobody starts hand-shake
     # k + 1 before everybody has published hand-shake k.
     _SLOTS = 8
 
     def _setup_event_handshake(self):
-        import os
-        import tempfile
-
-        import numpy as np
-
         dev = self.device
         with torch.cuda.device(dev):
             self._ev_local = [torch.cuda.Event(enable_timing=False, interprocess=True) for _ in range(self._SLOTS)]
             for ev in self._ev_local:
                 ev.record(self.exch)               # an event must have been recorded before its handle is exported
             handles = [ev.ipc_handle() for ev in self._ev_local]
-        # the counter page: a small file in shared memory that every rank maps; rank 0 removes the name again as
-        # soon as everybody has it open (the mappings stay valid), so nothing is left behind whatever happens later
-        path = [None]
-        if self.rank == 0:
-            fd, path[0] = tempfile.mkstemp(prefix="cueq_b200_handshake_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
-            os.write(fd, bytes(8 * self.world))
-            os.close(fd)
-        dist.broadcast_object_list(path, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
-        self._issued = np.memmap(path[0], dtype=np.int64, mode="r+", shape=(self.world,))
-        dist.barrier(group=self.group)
-        if self.rank == 0:
-            os.unlink(path[0])
+        self._board = HandshakeBoard(self.group)
         all_handles = [None] * self.world
         dist.all_gather_object(all_handles, handles, group=self.group)
         self._ev_peer = []
@@ -323,20 +345,14 @@ class PeerExchange:
         dist.barrier(group=self.group)             # nobody polls a counter page that does not exist yet
 
     def _event_handshake(self, s):
-        import time
-
         k = self._count
         slot = k % self._SLOTS
         self._ev_local[slot].record(s)
-        self._issued[self.rank] = k + 1
-        deadline = time.monotonic() + HANDSHAKE_TIMEOUT_S
+        self._board.publish(k + 1)                 # the record has been issued: peers may issue their waits
         for q in range(self.world):
-            if q == self.rank:
-                continue
-            while self._issued[q] < k + 1:
-                if time.monotonic() > deadline:
-                    raise RuntimeError(f"peer exchange: rank {q} did not reach hand-shake {k} within {HANDSHAKE_TIMEOUT_S} s")
-            s.wait_event(self._ev_peer[q][slot])
+            if q != self.rank:
+                self._board.wait_for(q, k + 1, HANDSHAKE_TIMEOUT_S)
+                s.wait_event(self._ev_peer[q][slot])
         self._count = k + 1
 
     def _view(self, flat, slot, rows, width):

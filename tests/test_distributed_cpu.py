@@ -98,3 +98,47 @@ def test_exchange_bundles_cover_every_block_once():
         assert P._bundles(SimpleNamespace(groups=gap)) == [(0, 1, 0, 128), (1, 2, 256, 128)]
     finally:
         distributed.BUNDLES = old
+
+
+def _board_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import random
+        import time
+
+        from cuequivariance_b200.distributed import HandshakeBoard
+
+        board = HandshakeBoard()
+        rng = random.Random(rank)
+        ok = True
+        for k in range(40):                       # the peer-exchange protocol: publish, then wait for everybody
+            time.sleep(rng.random() * 0.003)
+            board.publish(k + 1)
+            for q in range(world):
+                if q != rank:
+                    board.wait_for(q, k + 1, 20.0)
+                    ok = ok and int(board.counters[q]) >= k + 1        # nobody is let through early
+                    ok = ok and int(board.counters[q]) <= k + 2        # and nobody runs more than one hand-shake ahead
+        dist.barrier()
+        # a rank that never arrives ends the wait with an error on the host, it does not hang
+        if rank == 0:
+            t0 = time.monotonic()
+            try:
+                board.wait_for(1, 1000, 0.2)
+                ok = False
+            except RuntimeError as e:
+                ok = ok and "did not reach" in str(e) and time.monotonic() - t0 < 5.0
+        dist.barrier()
+        results[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_handshake_board_world2():
+    """The host half of the kernel-free hand-shake of the peer exchange (counter page in shared memory)."""
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_board_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world and all(results.values())
