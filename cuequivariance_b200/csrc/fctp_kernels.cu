@@ -24,6 +24,8 @@ namespace {
 
 constexpr int kMaxD = 7;            // irrep dimension up to l = 3
 constexpr int kThreadsF = 256;
+constexpr int kThreadsFast = 128;   // compile-time kernels: smaller blocks, more of them per SM (the phases of a sample - load,
+                                    // per-sample tables, main loop, write-back - are serial inside a block and overlap across blocks)
 
 struct FctpParams {
   const void* x1;
@@ -80,9 +82,9 @@ __device__ __forceinline__ void store_pair(float* dst, float a0, float a1) { *re
 
 template <typename TX, typename TZ>
 __global__ void __launch_bounds__(kThreadsF) fctp_build_z_kernel(const __grid_constant__ FctpParams p) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* xs1 = sm;
-  float* xs2 = xs1 + p.d1 * p.U;
+  float* xs2 = xs1 + ((p.d1 * p.U + 1) & ~1);   // T below is read in pairs: keep it on an 8-byte boundary (V is even)
   float* T = xs2 + p.d2 * p.V;
   TZ* Z = reinterpret_cast<TZ*>(p.z);
   for (int64_t z = blockIdx.x; z < p.batch; z += gridDim.x) {
@@ -197,8 +199,8 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_kernel(const __grid
 // multiply-adds for the unused part of the 7-wide unrolling, load one 4-byte element of Z / gZ per
 // thread at a time and spend as many instructions on index arithmetic as on the contraction.  For
 // the float32 route (x and Z both float32, V a power of two) the kernels below are instantiated per
-// (d1, d2, d3): a thread owns four consecutive v (one 16-byte access to Z / gZ per (k, u), all d3
-// rows of a u requested before the first is used), groups of V/4 threads share a u, and the sums
+// (d1, d2, d3): a thread owns 4 x 4 tiles of (u, v) (16-byte accesses to Z / gZ, 128-bit reads of the
+// per-sample tables for 16 multiply-adds each), groups of V/4 threads share a u tile, and the sums
 // over v are taken by shuffles inside such a group.
 __host__ __device__ constexpr int pad4(int n) { return (n + 3) & ~3; }
 
@@ -245,11 +247,14 @@ __device__ __forceinline__ void fast_prologue(const FctpParams& p, int64_t z, fl
 }
 
 template <int D1, int D2, int D3>
-__global__ void __launch_bounds__(kThreadsF) fctp_build_z_f32_kernel(const __grid_constant__ FctpParams p) {
+__global__ void __launch_bounds__(kThreadsFast) fctp_build_z_f32_kernel(const __grid_constant__ FctpParams p) {
   using L = FastSmem<D1, D2, D3>;
   extern __shared__ __align__(16) float sm[];
-  const int vshift = __ffs(p.V) - 1, gshift = vshift - 2;     // V = 1 << vshift; a u is shared by V/4 threads
-  const int vq = threadIdx.x & ((1 << gshift) - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsF >> gshift;
+  // a thread owns a 4 x 4 tile of (u, v): per k it reads d1 128-bit rows of T (its four v, kept over all its u
+  // tiles) and per tile d1 128-bit pieces of x1 (its four u) for 16 d1 multiply-adds and four 16-byte stores
+  const int vshift = __ffs(p.V) - 1, gshift = vshift - 2;     // V = 1 << vshift; a u tile is shared by V/4 threads
+  const int vq = threadIdx.x & ((1 << gshift) - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsFast >> gshift;
+  const int utiles = p.U >> 2;
   for (int t = threadIdx.x; t < D1 * D2 * D3; t += blockDim.x) sm[L::cg(p.U, p.V) + t] = p.cg[t];
   const float* xs1 = sm + L::xs1(p.U, p.V);
   const float* T = sm + L::T(p.U, p.V);
@@ -264,27 +269,37 @@ __global__ void __launch_bounds__(kThreadsF) fctp_build_z_f32_kernel(const __gri
 #pragma unroll
       for (int i = 0; i < D1; ++i) tt[i] = *reinterpret_cast<const float4*>(T + (k * D1 + i) * p.V + 4 * vq);
       float* zrow = Z + (z * D3 + k) * p.ldz + 4 * vq;
-      for (int u = ug; u < p.U; u += ugroups) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int uq = ug; uq < utiles; uq += ugroups) {
+        float4 a[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < D1; ++i) {
-          const float xi = xs1[i * p.U + u];
-          a.x = fmaf(tt[i].x, xi, a.x); a.y = fmaf(tt[i].y, xi, a.y);
-          a.z = fmaf(tt[i].z, xi, a.z); a.w = fmaf(tt[i].w, xi, a.w);
+          const float4 x4 = *reinterpret_cast<const float4*>(xs1 + i * p.U + 4 * uq);
+          const float xr[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            a[r].x = fmaf(tt[i].x, xr[r], a[r].x); a[r].y = fmaf(tt[i].y, xr[r], a[r].y);
+            a[r].z = fmaf(tt[i].z, xr[r], a[r].z); a[r].w = fmaf(tt[i].w, xr[r], a[r].w);
+          }
         }
-        *reinterpret_cast<float4*>(zrow + (int64_t)u * p.V) = a;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) *reinterpret_cast<float4*>(zrow + (int64_t)(4 * uq + r) * p.V) = a[r];
       }
     }
   }
 }
 
 template <int D1, int D2, int D3>
-__global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_f32_kernel(const __grid_constant__ FctpParams p) {
+__global__ void __launch_bounds__(kThreadsFast, 4) fctp_consume_gz_f32_kernel(const __grid_constant__ FctpParams p) {
   using L = FastSmem<D1, D2, D3>;
   extern __shared__ __align__(16) float sm[];
+  // the same 4 x 4 tiles: per k four 16-byte loads of gZ, d1 128-bit rows of T and d2 128-bit pieces of S feed
+  // 16 (d1 + d2) multiply-adds; the x1-gradient partials are summed over v by shuffles in a group of V/4 threads
   const int vshift = __ffs(p.V) - 1, gshift = vshift - 2;
   const int gsize = 1 << gshift;
-  const int vq = threadIdx.x & (gsize - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsF >> gshift;
+  const int vq = threadIdx.x & (gsize - 1), ug = threadIdx.x >> gshift, ugroups = kThreadsFast >> gshift;
+  const int utiles = p.U >> 2;
   for (int t = threadIdx.x; t < D1 * D2 * D3; t += blockDim.x) sm[L::cg(p.U, p.V) + t] = p.cg[t];
   const float* T = sm + L::T(p.U, p.V);
   const float* S = sm + L::S(p.U, p.V);
@@ -302,37 +317,49 @@ __global__ void __launch_bounds__(kThreadsF) fctp_consume_gz_f32_kernel(const __
 #pragma unroll
       for (int c = 0; c < 4; ++c) a2[j][c] = 0.f;
     // every thread makes the same number of trips, so the shuffles below always see the full warp
-    for (int u0 = 0; u0 < p.U; u0 += ugroups) {
-      const int u = u0 + ug;
-      const bool ok = u < p.U;
-      float4 g[D3];
+    for (int q0 = 0; q0 < utiles; q0 += ugroups) {
+      const int uq = q0 + ug;
+      const bool ok = uq < utiles;
+      const int us = ok ? 4 * uq : 0;
+      float a1[D1][4];
 #pragma unroll
-      for (int k = 0; k < D3; ++k)
-        g[k] = ok ? __ldcs(reinterpret_cast<const float4*>(GZ + (z * D3 + k) * p.ldz + (int64_t)u * p.V + 4 * vq))
-                  : make_float4(0.f, 0.f, 0.f, 0.f);
-      float a1[D1];
+      for (int i = 0; i < D1; ++i)
 #pragma unroll
-      for (int i = 0; i < D1; ++i) a1[i] = 0.f;
-      const int us = ok ? u : 0;
+        for (int r = 0; r < 4; ++r) a1[i][r] = 0.f;
 #pragma unroll
       for (int k = 0; k < D3; ++k) {
+        float4 g[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          g[r] = ok ? __ldcs(reinterpret_cast<const float4*>(GZ + (z * D3 + k) * p.ldz + (int64_t)(us + r) * p.V + 4 * vq))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < D1; ++i) {
           const float4 t4 = *reinterpret_cast<const float4*>(T + (k * D1 + i) * p.V + 4 * vq);
-          a1[i] = fmaf(g[k].x, t4.x, fmaf(g[k].y, t4.y, fmaf(g[k].z, t4.z, fmaf(g[k].w, t4.w, a1[i]))));
+#pragma unroll
+          for (int r = 0; r < 4; ++r)
+            a1[i][r] = fmaf(g[r].x, t4.x, fmaf(g[r].y, t4.y, fmaf(g[r].z, t4.z, fmaf(g[r].w, t4.w, a1[i][r]))));
         }
 #pragma unroll
         for (int j = 0; j < D2; ++j) {
-          const float s = S[(k * D2 + j) * p.U + us];
-          a2[j][0] = fmaf(g[k].x, s, a2[j][0]); a2[j][1] = fmaf(g[k].y, s, a2[j][1]);
-          a2[j][2] = fmaf(g[k].z, s, a2[j][2]); a2[j][3] = fmaf(g[k].w, s, a2[j][3]);
+          const float4 s4 = *reinterpret_cast<const float4*>(S + (k * D2 + j) * p.U + us);
+          const float sr[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            a2[j][0] = fmaf(g[r].x, sr[r], a2[j][0]); a2[j][1] = fmaf(g[r].y, sr[r], a2[j][1]);
+            a2[j][2] = fmaf(g[r].z, sr[r], a2[j][2]); a2[j][3] = fmaf(g[r].w, sr[r], a2[j][3]);
+          }
         }
       }
 #pragma unroll
       for (int i = 0; i < D1; ++i) {
-        float tot = a1[i];
-        for (int o = gsize >> 1; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-        if (ok && vq == 0) g1[i * p.U + u] = tot;       // one group per u: a plain store
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          float tot = a1[i][r];
+          for (int o = gsize >> 1; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+          a1[i][r] = tot;
+        }
+        if (ok && vq == 0) *reinterpret_cast<float4*>(g1 + i * p.U + us) = make_float4(a1[i][0], a1[i][1], a1[i][2], a1[i][3]);   // one group per u tile
       }
     }
 #pragma unroll
@@ -379,11 +406,11 @@ bool fast_pick2(int d2, int d3, FastKernel& b, FastKernel& c, int U, int V, size
   return false;
 }
 
-// The compile-time kernels apply to float32 x and Z, odd irrep dimensions up to 7, V a power of two in
-// 16..128 and 16-byte aligned rows of Z; everything else takes the generic kernels.
+// The compile-time kernels apply to float32 x and Z, odd irrep dimensions up to 7, U a multiple of 4, V a power
+// of two in 16..128 and 16-byte aligned rows of Z; everything else takes the generic kernels.
 bool fast_lookup(const cueq_fctp_args* a, const FctpParams& p, FastKernel& b, FastKernel& c, size_t& sb, size_t& sc) {
   if (a->x_dtype != CUEQ_F32 || a->z_dtype != CUEQ_F32) return false;
-  if (p.V < 16 || p.V > 128 || (p.V & (p.V - 1))) return false;
+  if (p.V < 16 || p.V > 128 || (p.V & (p.V - 1)) || (p.U & 3)) return false;
   if ((p.ldz & 3) || (reinterpret_cast<uintptr_t>(p.z) & 15)) return false;
   switch (p.d1) {
     case 1: return fast_pick2<1>(p.d2, p.d3, b, c, p.U, p.V, sb, sc);
@@ -396,7 +423,7 @@ bool fast_lookup(const cueq_fctp_args* a, const FctpParams& p, FastKernel& b, Fa
 
 int launch_fast(FastKernel k, size_t smem, const FctpParams& p, cudaStream_t st) {
   if (smem > 48 * 1024) CUEQ_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k<<<(unsigned)(p.batch < 148 * 16 ? p.batch : 148 * 16), kThreadsF, smem, st>>>(p);
+  k<<<(unsigned)(p.batch < 148 * 32 ? p.batch : 148 * 32), kThreadsFast, smem, st>>>(p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -427,7 +454,7 @@ extern "C" int cueq_b200_fctp_build_z(const cueq_fctp_args* a, void* stream) {
   if (int rc = fill(a, p)) return rc;
   if (p.batch == 0) return 0;
   if (a->x_dtype != CUEQ_F32 && a->x_dtype != CUEQ_BF16) return cueq::fail("fctp: x must be float32 or bfloat16");
-  const size_t smem = sizeof(float) * (p.d1 * p.U + p.d2 * p.V + p.d3 * p.d1 * p.V);
+  const size_t smem = sizeof(float) * (((p.d1 * p.U + 1) & ~1) + p.d2 * p.V + p.d3 * p.d1 * p.V);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   {
     FastKernel fb, fc;
