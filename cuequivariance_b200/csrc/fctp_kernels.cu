@@ -24,7 +24,7 @@ namespace {
 
 constexpr int kMaxD = 7;            // irrep dimension up to l = 3
 constexpr int kThreadsF = 256;
-constexpr int kThreadsFast = 128;   // compile-time kernels: smaller blocks, more of them per SM (the phases of a sample - load,
+constexpr int kThreadsFast = 64;    // compile-time kernels: small blocks, more of them per SM (the phases of a sample - load,
                                     // per-sample tables, main loop, write-back - are serial inside a block and overlap across blocks)
 
 struct FctpParams {
@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(kThreadsFast) fctp_build_z_f32_kernel(const __
 }
 
 template <int D1, int D2, int D3>
-__global__ void __launch_bounds__(kThreadsFast, 4) fctp_consume_gz_f32_kernel(const __grid_constant__ FctpParams p) {
+__global__ void __launch_bounds__(kThreadsFast, 8) fctp_consume_gz_f32_kernel(const __grid_constant__ FctpParams p) {
   using L = FastSmem<D1, D2, D3>;
   extern __shared__ __align__(16) float sm[];
   // the same 4 x 4 tiles: per k four 16-byte loads of gZ, d1 128-bit rows of T and d2 128-bit pieces of S feed
@@ -423,7 +423,7 @@ bool fast_lookup(const cueq_fctp_args* a, const FctpParams& p, FastKernel& b, Fa
 
 int launch_fast(FastKernel k, size_t smem, const FctpParams& p, cudaStream_t st) {
   if (smem > 48 * 1024) CUEQ_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k<<<(unsigned)(p.batch < 148 * 32 ? p.batch : 148 * 32), kThreadsFast, smem, st>>>(p);
+  k<<<(unsigned)(p.batch < 148 * 64 ? p.batch : 148 * 64), kThreadsFast, smem, st>>>(p);
   CUEQ_CUDA_OK(cudaGetLastError());
   return 0;
 }
