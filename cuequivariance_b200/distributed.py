@@ -395,10 +395,23 @@ class PeerExchange:
             if ev is not None:
                 s.wait_event(ev)
         if PUSH_MODE == "memcpy" and not _DIAG_SKIP_COPY:   # copy engines instead of the push kernel
+            # one stream per peer: the copies of a block go out over all links at once instead of one after the other
+            # (a single copy engine does not fill a link, and a single stream uses a single engine at a time)
+            start = torch.cuda.Event()
+            start.record(s)
+            used = []
             with torch.cuda.device(self.device):
-                for dst, src in pieces:
+                for k, (dst, src) in enumerate(pieces):
+                    sk = self.copy_streams[k % len(self.copy_streams)]
+                    if sk is not s and sk not in used:
+                        sk.wait_event(start)
+                        used.append(sk)
                     _lib.check(_lib.lib().cueq_b200_copy_async(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()),
-                                                               C.c_size_t(src.numel() * src.element_size()), C.c_void_p(s.cuda_stream)))
+                                                               C.c_size_t(src.numel() * src.element_size()), C.c_void_p(sk.cuda_stream)))
+            for sk in used:                                  # the returned event covers every stream
+                e = torch.cuda.Event()
+                e.record(sk)
+                s.wait_event(e)
             pieces = []
         for i in range(0, len(pieces), 8):
             a = _lib.PushArgs()
