@@ -34,10 +34,11 @@ def _rows_view_ok(t: torch.Tensor) -> bool:
 
 
 def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = "gemm_f32x3",
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, b_split=None) -> torch.Tensor:
     """``a [M, K] @ b[N, K].T (+ bias[N])`` in float32 accuracy on the tensor cores; K a multiple of 32,
     N a multiple of 4.  ``a`` and ``out`` may be column slices of wider row-major tensors (unit stride
-    along the row, 16-byte aligned); ``out`` is overwritten."""
+    along the row, 16-byte aligned); ``out`` is overwritten.  ``b_split = split_tf32(b)`` may be passed by a
+    caller that multiplies by the same ``b`` several times."""
     import ctypes as C
 
     from . import _lib, profiling
@@ -49,7 +50,7 @@ def gemm_f32x3(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = 
     if b.shape[0] % 4:
         raise ValueError("gemm_f32x3: the number of output columns must be a multiple of 4")
     ac = a if _rows_view_ok(a) else a.contiguous()
-    hi, lo = split_tf32(b)
+    hi, lo = b_split if b_split is not None else split_tf32(b)
     if out is None:
         out = torch.empty((a.shape[0], b.shape[0]), dtype=torch.float32, device=a.device)
     elif not (_rows_view_ok(out) and out.shape == (a.shape[0], b.shape[0]) and out.dtype == torch.float32):

@@ -533,7 +533,7 @@ class DenseUVW:
     def map_out(self, w, x1, x2):
         """out = F(w, x1, x2): per output irrep one coupled operand [(z, k), sum of the paths' (u, v)] and one
         GEMM per component k against the stacked weight blocks."""
-        from .dense import gemm_f32x3
+        from .dense import gemm_f32x3, split_tf32
 
         d, off = self.d, self.offsets
         B, dev = x1.shape[0], x1.device
@@ -550,6 +550,7 @@ class DenseUVW:
                 U, V, _ = d.operands[0].segments[sw]
                 WT[:Wd, c0 : c0 + U * V] = w[0, off[0][sw] : off[0][sw] + U * V * Wd].reshape(U * V, Wd).t()
                 c0 += ck
+            WT_split = split_tf32(WT)                                        # one split for every component and chunk
             step = self._chunk(B, d3 * K)
             for b0 in range(0, B, step):
                 b1 = min(B, b0 + step)
@@ -563,9 +564,9 @@ class DenseUVW:
                 for kk in range(d3):
                     o = off[3][so] + kk * Wd
                     if Wp == Wd:
-                        gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward", out=out[b0:b1, o : o + Wd])
+                        gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward", out=out[b0:b1, o : o + Wd], b_split=WT_split)
                     else:
-                        out[b0:b1, o : o + Wd] = gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward")[:, :Wd]
+                        out[b0:b1, o : o + Wd] = gemm_f32x3(Z3[:, kk, :], WT, name="fctp_f32_forward", b_split=WT_split)[:, :Wd]
                 del Z, Z3
         return out
 
@@ -604,7 +605,7 @@ class DenseUVW:
         import ctypes as C
 
         from . import _lib, profiling
-        from .dense import gemm_f32x3
+        from .dense import gemm_f32x3, split_tf32
 
         d, off = self.d, self.offsets
         B, dev = x1.shape[0], x1.device
@@ -620,6 +621,7 @@ class DenseUVW:
             if Kw != Wd or N != U * V:
                 Wk = torch.nn.functional.pad(Wk, (0, Kw - Wd, 0, N - U * V))
             Wk = Wk.contiguous()
+            Wk_split = split_tf32(Wk)                                        # one split for every component and chunk
             step = self._chunk(B, d3 * N)
             for b0 in range(0, B, step):
                 b1 = min(B, b0 + step)
@@ -630,7 +632,7 @@ class DenseUVW:
                     gk = g[b0:b1, o : o + Wd]
                     if Kw != Wd:
                         gk = torch.nn.functional.pad(gk, (0, Kw - Wd))
-                    gemm_f32x3(gk, Wk, name="fctp_f32_gx", out=gZ3[:, kk, :])
+                    gemm_f32x3(gk, Wk, name="fctp_f32_gx", out=gZ3[:, kk, :], b_split=Wk_split)
                 a = self._fctp_args(k, x1[b0:b1], x2[b0:b1], b1 - b0)
                 a.z, a.z_dtype, a.ldz = gZ.data_ptr(), _lib.F32, N
                 a.gx1, a.gx2 = gx1[b0:b1].data_ptr(), gx2[b0:b1].data_ptr()
