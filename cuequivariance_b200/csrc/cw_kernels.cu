@@ -835,7 +835,9 @@ int launch_bwd_block_t(const CwParams& p, const CwCoef& coef, cudaStream_t st) {
     CUEQ_CUDA_OK(cudaFuncSetAttribute(cw_bwd_block_kernel<G, A, BULK, GX2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured.set();
   }
-  const int cap = 148 * 24;
+  // blocks walk the receivers with a grid stride; many short-lived blocks (a few receivers each) let the hardware
+  // balance the uneven edge counts better than eight waves of long ones (l = 3 launch 3.48 -> 3.40 ms)
+  const int cap = 148 * 96;
   dim3 grid(p.num_receivers < cap ? p.num_receivers : cap, (p.extent + 127) / 128);
   cw_bwd_block_kernel<G, A, BULK, GX2><<<grid, kWarps * 32, smem, st>>>(p, coef);
   CUEQ_CUDA_OK(cudaGetLastError());
