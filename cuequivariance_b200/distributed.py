@@ -97,16 +97,6 @@ def all_gather_rows(x: torch.Tensor, group=None) -> torch.Tensor:
 BUNDLES = 0   # exchanges per direction in the pipelined path (0: one per irrep, 1: one collective, 2: two bundles)
 
 
-_SIDE_STREAMS: dict = {}
-
-
-def _side_stream(dev):
-    s = _SIDE_STREAMS.get(dev)
-    if s is None:
-        s = _SIDE_STREAMS[dev] = torch.cuda.Stream(device=dev)
-    return s
-
-
 class _PipelinedShardedChannelwise(torch.autograd.Function):
     """Sharded channelwise product with the node-feature exchange pipelined against the
     per-irrep kernel launches.
@@ -157,21 +147,11 @@ class _PipelinedShardedChannelwise(torch.autograd.Function):
         csr = (order, rowptr, n_local)
         bundles = _PipelinedShardedChannelwise._bundles(plan)
         wide, works = [], []
-        # the contiguous send copies and the collectives are issued from a side stream: on the launching stream the
-        # copies of the later blocks would sit in front of the first kernel, which only needs the first block
-        main = torch.cuda.current_stream(dev)
-        side = _side_stream(dev)
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
-            for (a, b, off, width) in bundles:  # irrep blocks in ascending size
-                loc = x1_local[:, off : off + width].contiguous()
-                full = torch.empty((n_local * world, width), dtype=loc.dtype, device=dev)
-                works.append(dist.all_gather_into_tensor(full, loc, group=group, async_op=True))
-                wide.append(full)
-                loc.record_stream(side)
-        for full in wide:
-            full.record_stream(main)
-        x1_local.record_stream(side)
+        for (a, b, off, width) in bundles:  # irrep blocks in ascending size
+            loc = x1_local[:, off : off + width].contiguous()
+            full = torch.empty((n_local * world, width), dtype=loc.dtype, device=dev)
+            works.append(dist.all_gather_into_tensor(full, loc, group=group, async_op=True))
+            wide.append(full)
         out = torch.empty((n_local, plan.row_sizes[3]), dtype=torch.float32, device=dev)
         for bi, (a, b, off, width) in enumerate(bundles):
             works[bi].wait()
